@@ -1,0 +1,149 @@
+"""Generate the golden vectors of tests/golden/ by running the reference implementation itself.
+
+Run once, in a container that has the reference checked out:
+
+    PYTHONPATH=<reference>/src python tests/golden/make_golden.py
+
+It imports `bitexact` (pure Python, CPU paths only), feeds it small seeded inputs and stores inputs
+and outputs as compressed .npz files.  The tests never import the reference; they read these files.
+"""
+
+import os
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def n(t):
+    return t.detach().cpu().numpy()
+
+
+def bf16_bits(w):
+    return w.contiguous().view(torch.int16).numpy().astype(np.uint16)
+
+
+def limb_planes(c32, HD):
+    """int32 cache [nb, HKV, bs, 2 HD] (K | V) -> int8 limb planes [nb, HKV, bs, 8 HD]."""
+    from bitexact.intops import split_limbs
+    out = torch.zeros(*c32.shape[:3], 8 * HD, dtype=torch.int8)
+    for part, o in ((c32[..., :HD], 0), (c32[..., HD:], 3)):
+        for i, lo in enumerate(split_limbs(part, 3)[0]):
+            out[..., (o + i) * HD:(o + i + 1) * HD] = lo.to(torch.int8)
+    return out
+
+
+def exact_ops():
+    from bitexact.exact import ops, segs
+    from bitexact.exact.consts import FR, bf16_parts, decompose
+    from bitexact.exact.model import Lin
+    from bitexact.exact.segs import lin_y
+
+    out = {}
+    g = torch.Generator().manual_seed(11)
+    lut = torch.round(torch.pow(2.0, -torch.arange((1 << 14) + 1, dtype=torch.float64) / (1 << 14)) * 2.0 ** 60).long()
+
+    # --- linear with forced residual, ordinary and adversarial shifts ---
+    N, K, M = 80, 192, 9
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    w[0, :5] = torch.tensor([1e-9, -3e-8, 0.0, 2.0, -0.5]).to(torch.bfloat16)
+    w[7, 3] = torch.tensor(3e-7).to(torch.bfloat16)
+    w[33, :] = 0
+    dec = decompose(w)
+    c = {f"x.{k}": v for k, v in dec.items() if k != "stats"}
+    q = torch.randint(-(1 << 22), (1 << 22) + 1, (M, K), generator=g)
+    q[0, :] = 1 << 22
+    q[1, :] = -(1 << 22)
+    q[2, :] = 0
+    sh = torch.tensor([-20, -8, -14, -40, -70, 0, 12, 40, -97])
+    lin = Lin(c, "x", "cpu", "cpu", False)
+    y, flag = lin_y(*lin(q), sh, True)
+    rowflag = [bool(lin_y(*lin(q[m:m + 1]), sh[m:m + 1], True)[1]) for m in range(M)]
+    out.update(lin_w=bf16_bits(w), lin_q=n(q), lin_sh=n(sh), lin_y=n(y), lin_flag=np.array(bool(flag)),
+               lin_rowflag=np.array(rowflag), lin_limbs=n(dec["limbs"]), lin_g=n(dec["g"]), lin_d=n(dec["d"]),
+               lin_rr=n(dec["rr"]), lin_rc=n(dec["rc"]), lin_rv=n(dec["rv"]))
+
+    # --- rms norm + quant ---
+    D = 512
+    x = torch.randint(-(1 << 27), 1 << 27, (6, D), generator=g)
+    x[1] = torch.randint(-3, 4, (D,), generator=g)
+    x[2] = 0
+    x[3] = torch.randint(-(1 << 38), 1 << 38, (D,), generator=g)
+    x[4] = torch.randint(-(1 << 39), 1 << 39, (D,), generator=g)
+    gam = (1 + 0.3 * torch.randn(D, generator=g)).to(torch.bfloat16)
+    gm, ge = bf16_parts(gam)
+    qn, shn, _ = segs.norm_quant(x, gm, ge, torch.zeros((), dtype=torch.bool))
+    r, er = ops.rms(x)
+    out.update(norm_x=n(x), norm_gm=n(gm), norm_ge=n(ge), norm_q=n(qn), norm_sh=n(shn), norm_r=n(r), norm_er=n(er))
+
+    # --- rope + q quant + k / v ---
+    H, HKV, HD = 4, 2, 64
+    T = 5
+    yq = torch.randint(-(1 << 28), 1 << 28, (T, (H + 2 * HKV) * HD), generator=g)
+    yq[4] = torch.randint(-(1 << 10), 1 << 10, ((H + 2 * HKV) * HD,), generator=g)
+    pos = torch.tensor([0, 3, 17, 100, 255])
+    ang = torch.arange(256, dtype=torch.float64)[:, None] \
+        * (500000.0 ** (-torch.arange(0, HD, 2, dtype=torch.float64) / HD))[None]
+    cos, sin = torch.round(torch.cos(ang) * 2.0 ** 30).long(), torch.round(torch.sin(ang) * 2.0 ** 30).long()
+    Pq, k, v, _ = segs.rope_y(yq, pos.view(T, 1), cos, sin, T, 1, (H, HKV, HD))
+    qi, shq = ops.quant(Pq, -(FR + 30))
+    out.update(rope_y=n(yq), rope_pos=n(pos), rope_cos=n(cos), rope_sin=n(sin), rope_q=n(qi.view(T, H, HD)),
+               rope_sh=n(shq.view(T, H)), rope_k=n(k.view(T, HKV, HD)), rope_v=n(v.view(T, HKV, HD)))
+
+    # --- silu * up + quant ---
+    FF = 384
+    gu = torch.randint(-(12 << FR), 12 << FR, (4, 2 * FF), generator=g)
+    gu[1, :FF] = torch.randint(-(70 << FR), 70 << FR, (FF,), generator=g)
+    gu[2] = torch.randint(-(1 << 12), 1 << 12, (2 * FF,), generator=g)
+    P, ok = segs.silu_y(gu, lut)
+    qs, shs, errs = segs.quant_silu(P, ok, torch.zeros((), dtype=torch.bool))
+    out.update(silu_y=n(gu), silu_q=n(qs), silu_sh=n(shs), silu_err=np.array(bool(errs)))
+
+    # --- paged attention (the reference's unfused form: exact products + softmax_w) and attn_out ---
+    nb, bs, HKV, HD, G = 40, 16, 2, 64, 4
+    c32 = torch.randint(-8355711, 8355712, (nb, HKV, bs, 2 * HD), generator=g).to(torch.int32)
+    c32[5:20] = torch.randint(-(1 << 12), 1 << 12, (15, HKV, bs, 2 * HD), generator=g).to(torch.int32)
+    R = 4
+    bt = torch.stack([torch.randperm(nb - 1, generator=g)[:12] + 1 for _ in range(R)]).to(torch.int32)
+    bt[:2, :6] = torch.randint(5, 20, (2, 6), generator=g).to(torch.int32)
+    qpos = torch.tensor([[60, 60, 60, 60], [150, 150, 150, 150], [3, 0, 7, 5], [191, 100, 1, 64]])
+    qa = torch.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, G, HD), generator=g)
+    sha = torch.randint(-40, -10, (R, HKV, G), generator=g)
+    S = int(qpos.max()) + 1
+    s = torch.arange(S)
+    kv = c32[bt.long()[:, s // bs], :, (s % bs)[None].expand(R, -1)].long()
+    Kk, Vv = kv[..., :HD].permute(0, 2, 1, 3), kv[..., HD:].permute(0, 2, 1, 3)
+    raw = torch.einsum("rhmd,rhsd->rhms", qa, Kk)
+    ok = torch.arange(S)[None, None, None] <= qpos[:, None, :, None]
+    p, den = ops.softmax_w(raw, ok, sha[..., None], segs.FK, lut, segs.FP, ops.L2E28)
+    num = torch.einsum("rhms,rhsd->rhmd", p, Vv)
+    o = ops.div_round(num, FR - segs.FV, den)
+    qo, sho = ops.quant(o.reshape(R, -1), -FR)
+    out.update(attn_cache=n(limb_planes(c32, HD)), attn_bt=n(bt), attn_qpos=n(qpos), attn_q=n(qa), attn_sh=n(sha),
+               attn_num=n(num), attn_den=n(den), attn_qo=n(qo), attn_sho=n(sho))
+    np.savez_compressed(os.path.join(HERE, "exact_ops.npz"), **out)
+
+
+def sampler():
+    from bitexact import sampling
+    from bitexact.llama import ln_table
+    g = torch.Generator().manual_seed(5)
+    lnt = ln_table(40)
+    keys = [(0, 0), (1, 0), (7, 33), (123456, 255)]
+    raw = sampling.raw_rows(keys)[:, :2048].contiguous()
+    raw[0, :6] = torch.tensor([0, -1, 1 << 11, (1 << 63) - 1, -(1 << 63), 12345 << 11])
+    gum = sampling.gumbel(raw, lnt, 24)
+    logits = torch.randint(-(30 << 24), 30 << 24, (4, 2048), generator=g)
+    logits[2, 100] = logits[2].max() + 5
+    logits[2, 900] = logits[2, 100]
+    tok_g = sampling.sample(logits, 0, 1)
+    tok_t = sampling.sample(logits, 7, 10, gum)
+    np.savez_compressed(os.path.join(HERE, "sampler.npz"), keys=np.array(keys), raw=n(raw), gumbel=n(gum),
+                        logits=n(logits), tok_greedy=n(tok_g), tok_t07=n(tok_t))
+
+
+if __name__ == "__main__":
+    exact_ops()
+    sampler()
+    print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
