@@ -1,0 +1,65 @@
+"""ctypes binding of libbitexact_b200.so (C ABI in include/bitexact_b200.h).
+
+The library is built in-tree by `bitexact_llm_b200.build` (nvcc, sm_100a).  Loading fails loudly when it is
+missing: there is deliberately no fallback path.
+"""
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libbitexact_b200.so")
+
+BX_OK, BX_EARG, BX_ELAUNCH, BX_EDEVICE = 0, -1, -2, -3
+_ERR = {BX_EARG: "argument contract violated (shape / alignment / null pointer)",
+        BX_ELAUNCH: "CUDA launch or driver call failed", BX_EDEVICE: "a device-side wait timed out"}
+
+_lib = None
+
+P, I, L, Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+
+_SIGNATURES = {
+    "bx_version": (I, []),
+    "bx_device_status": (I, []),
+    "bx_clear_device_status": (I, []),
+    "bx_exact_linear_scratch_bytes": (Z, [I, I]),
+    "bx_exact_linear": (I, [P, L, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, P]),
+    "bx_split_limbs": (I, [P, L, P, I, I, P]),
+}
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m bitexact_llm_b200.build` "
+                               "(nvcc, sm_100a). There is no fallback path.")
+        h = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(h, name)                       # AttributeError if the library is stale
+            fn.restype, fn.argtypes = res, args
+        _lib = h
+    return _lib
+
+
+def exported_symbols():
+    return sorted(_SIGNATURES)
+
+
+def check(rc, what):
+    if rc != BX_OK:
+        raise RuntimeError(f"{what}: {_ERR.get(rc, rc)}")
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def device_status():
+    return lib().bx_device_status()

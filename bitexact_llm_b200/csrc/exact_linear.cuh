@@ -1,0 +1,109 @@
+// Exact-mode linear y = round((q @ W_bf16^T) * 2^(sh + 24)) as one kernel: 3x3 int8 limb products on tcgen05 into
+// five int32 TMEM accumulators, int64 join, sparse low-bit residual, one round-half-up, lost-bit flag.
+//
+// Replaces, with the same integers: FusedLin.__call__ / _lin_kernel (src/bitexact/vllm_plugin/exact_gemm.py:58-119,
+// 284-316) = wmm (src/bitexact/exact/wmm.py:31-121) + residual (:124-129) + epilogue (:132-150).
+#pragma once
+
+#include "bx_rules.cuh"
+#include "limb_gemm.cuh"
+
+namespace bx {
+
+struct ExactEpiParams {
+  const int32_t* q;      // [M, ldq] activations (residual gather)
+  int64_t ldq;
+  const int64_t* sh;     // [M] row exponents
+  const int64_t* d;      // [N] residual grid offset, 0..30
+  const int64_t* g;      // [N] row grid exponent
+  const int32_t* cnt;    // [N] residual entries per weight row (may be null: no residual)
+  const int32_t* ec;     // [N, R] residual columns
+  const int64_t* ev;     // [N, R] residual values
+  int R;
+  int64_t* y;            // [M, N]
+  int32_t* flag;         // sticky lost-bit / range flag (only ever set to 1)
+  int M, N;
+  int checked;
+};
+
+template <int TA>
+struct ExactEpilogue {
+  using Params = ExactEpiParams;
+
+  // One thread per weight row n (TMEM lane); walks the TA activation rows in chunks of 16 columns.
+  static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int lane, int n0, int m0, bool has_k,
+                                             const Params& p) {
+    const int n = n0 + quarter * 32 + lane;
+    const bool nok = n < p.N;
+    const int d = nok ? (int)p.d[n] : 0;
+    const i64 gd = nok ? p.g[n] - (i64)d + FR : 0;
+    const int cnt = (nok && p.cnt) ? p.cnt[n] : 0;
+    const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
+    bool any_bad = false;
+#pragma unroll 1
+    for (int c0 = 0; c0 < TA; c0 += 16) {
+      if (m0 + c0 >= p.M) break;                     // warp-uniform
+      uint32_t acc[5][16];
+#pragma unroll
+      for (int b = 0; b < 5; ++b) tmem_ld16(tbase + b * TA + c0, acc[b]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int m = m0 + c0 + i;
+        if (m < p.M && nok) {
+          i64 T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +
+                  shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
+          if (!has_k) T = 0;
+          i64 B = 0;
+          for (int j = 0; j < cnt; ++j)
+            B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
+          bool bad;
+          const i64 yv = round_shift_hl(T, B, d, p.sh[m] + gd, bad);
+          any_bad |= bad;
+          p.y[(i64)m * p.N + n] = yv;
+        }
+      }
+    }
+    if (p.checked && any_bad) *p.flag = 1;
+  }
+};
+
+template <int TA>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+exact_linear_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                    const ExactEpiParams ep, int K, int m_tiles) {
+  const int mt = blockIdx.x % m_tiles;
+  const int nt = blockIdx.x / m_tiles;
+  limb_gemm_tile<3, 3, TA, ExactEpilogue<TA>>(&tmap_w, &tmap_a, nt * WROWS, mt * TA, 0, (K + BKB - 1) / BKB, ep);
+}
+
+// q int32 [M, K] (row stride ldq) -> limb planes int8 [3, M, K] (signed base-256 digits, intops.py:62-70).
+__global__ void split_limbs_kernel(const int32_t* __restrict__ q, int64_t ldq, int8_t* __restrict__ a8, int M, int K) {
+  const int64_t per_row = K / 16;
+  const int64_t total = (int64_t)M * per_row;
+  const int64_t plane = (int64_t)M * K;
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = t / per_row, c = (t % per_row) * 16;
+    const int4* src = reinterpret_cast<const int4*>(q + m * ldq + c);
+    uint32_t out[3][4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int4 x = src[v];
+      int e[4] = {x.x, x.y, x.z, x.w};
+      uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int r = e[i];
+        w0 |= (uint32_t)(split8(r) & 255) << (8 * i);
+        w1 |= (uint32_t)(split8(r) & 255) << (8 * i);
+        w2 |= (uint32_t)(split8(r) & 255) << (8 * i);
+      }
+      out[0][v] = w0; out[1][v] = w1; out[2][v] = w2;
+    }
+#pragma unroll
+    for (int l = 0; l < 3; ++l)
+      *reinterpret_cast<uint4*>(a8 + l * plane + m * K + c) = make_uint4(out[l][0], out[l][1], out[l][2], out[l][3]);
+  }
+}
+
+}  // namespace bx

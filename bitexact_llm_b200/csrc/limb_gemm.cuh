@@ -1,0 +1,179 @@
+// Limb GEMM main loop on tcgen05 (kind::i8) with TMEM accumulators, shared by the exact-mode linear
+// (3 weight limbs x 3 activation limbs) and the int8-mode linear (1 weight limb x 2 activation limbs).
+//
+// Orientation: the WEIGHT rows are the MMA M side (128 rows per CTA = 128 TMEM lanes), the activation rows are
+// the MMA N side (TA rows per limb). The NA activation limb tiles of one K block sit back to back in shared
+// memory, so one MMA per weight limb j multiplies W_j [128 x 32] with all activation limbs [NA*TA x 32] at once and
+// adds into TMEM columns [j*TA, (j+NA)*TA): column block b = i + j collects every limb product of weight 2^(8b).
+// A decode batch of 1..16 rows therefore uses the same kernel with TA = 16.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue, warps 2..5 = epilogue
+// (each owns the 32 TMEM lanes its warp id modulo 4 may access). Stages of the shared-memory ring are handed
+// over with mbarriers; every wait is bounded and a timeout ends the CTA with an error status instead of a hang.
+#pragma once
+
+#include "bx_ptx.cuh"
+
+namespace bx {
+
+constexpr int GEMM_THREADS = 192;
+constexpr int WROWS = 128;   // weight rows per CTA (MMA M)
+constexpr int BKB = 128;     // K bytes per stage (one 128-byte swizzle atom per row)
+constexpr int UMMA_K = 32;   // int8 K per MMA
+
+__device__ int g_wait_timeouts;   // number of bounded waits that gave up (0 in a healthy run)
+
+template <int NW, int NA, int TA>
+struct GemmCfg {
+  static_assert(TA % 16 == 0 && TA >= 16, "activation tile: multiple of 16 rows");
+  static_assert(NA * TA <= 256, "MMA N limit");
+  static constexpr int NBLK = NW + NA - 1;                  // accumulator column blocks
+  static constexpr int COLS = NBLK * TA;                    // TMEM columns in use
+  static constexpr int TMEM_COLS = COLS <= 32 ? 32 : COLS <= 64 ? 64 : COLS <= 128 ? 128 : COLS <= 256 ? 256 : 512;
+  static_assert(COLS <= 512, "TMEM capacity");
+  static constexpr int W_BYTES = NW * WROWS * BKB;
+  static constexpr int A_BYTES = NA * TA * BKB;
+  static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+  static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;     // ring budget; the rest holds barriers + alignment slack
+  static constexpr int STAGES_MAX = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_MAX > 6 ? 6 : STAGES_MAX;
+  static_assert(STAGES >= 2, "at least two stages");
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+struct GemmShared {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+// Runs the main loop for the output tile (weight rows n0.., activation rows m0..) over k blocks [kb0, kb1).
+// On return, for warps 2..5, the accumulators are complete in TMEM (returns false after a timeout).
+// Epi::run(tmem_base, warp_quarter, lane, ...) is called by the epilogue warps.
+template <int NW, int NA, int TA, class Epi>
+__device__ __forceinline__ void limb_gemm_tile(const CUtensorMap* tmap_w, const CUtensorMap* tmap_a, int n0, int m0,
+                                               int kb0, int kb1, const typename Epi::Params& ep) {
+  using Cfg = GemmCfg<NW, NA, TA>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmShared* sh = reinterpret_cast<GemmShared*>(ring + Cfg::STAGES * Cfg::STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    mbar_init(&sh->acc_full, 1);
+    // A timeout anywhere earlier (sticky until the host clears it) makes every later CTA leave at once.
+    sh->abort_flag = *reinterpret_cast<volatile int*>(&g_wait_timeouts) != 0;
+    fence_barrier_init();
+    tma_prefetch_desc(tmap_w);
+    tma_prefetch_desc(tmap_a);
+  }
+  __syncthreads();
+  if (sh->abort_flag) return;
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer ----
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % Cfg::STAGES;
+        const int round = i / Cfg::STAGES;
+        if (round > 0) ok = mbar_wait(&sh->empty[s], (round - 1) & 1);
+        if (!ok) break;
+        uint8_t* st = ring + s * Cfg::STAGE_BYTES;
+        mbar_arrive_expect_tx(&sh->full[s], Cfg::STAGE_BYTES);
+        tma_load_3d(st, tmap_w, &sh->full[s], (kb0 + i) * BKB, n0, 0);
+        tma_load_3d(st + Cfg::W_BYTES, tmap_a, &sh->full[s], (kb0 + i) * BKB, m0, 0);
+        issued = i + 1;
+      }
+      if (!ok) {
+        atomicAdd(&g_wait_timeouts, 1);
+        sh->abort_flag = 1;
+        // let the copies already in flight land before the CTA can exit
+        for (int i = (issued > Cfg::STAGES ? issued - Cfg::STAGES : 0); i < issued; ++i)
+          mbar_wait(&sh->full[i % Cfg::STAGES], (i / Cfg::STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issue ----
+      constexpr uint32_t ID_ALL = umma_idesc_i8(NA * TA);
+      constexpr uint32_t ID_ONE = umma_idesc_i8(TA);
+      constexpr uint32_t ID_REST = umma_idesc_i8(NA > 1 ? (NA - 1) * TA : TA);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % Cfg::STAGES;
+        ok = mbar_wait(&sh->full[s], (i / Cfg::STAGES) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t wbase = smem_u32(ring + s * Cfg::STAGE_BYTES);
+        const uint32_t abase = wbase + Cfg::W_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BKB / UMMA_K; ++ks) {
+          const uint32_t koff = ks * UMMA_K;
+          const uint64_t adesc = umma_desc_sw128(abase + koff);
+          if (i == 0 && ks == 0) {
+            // First K slice: every column block is written exactly once without accumulation.
+            umma_i8(tmem, umma_desc_sw128(wbase + koff), adesc, ID_ALL, 0);
+#pragma unroll
+            for (int j = 1; j < NW; ++j) {
+              const uint64_t wdesc = umma_desc_sw128(wbase + j * (WROWS * BKB) + koff);
+              umma_i8(tmem + (j + NA - 1) * TA, wdesc, umma_desc_sw128(abase + (NA - 1) * TA * BKB + koff), ID_ONE, 0);
+              if (NA > 1) umma_i8(tmem + j * TA, wdesc, adesc, ID_REST, 1);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < NW; ++j)
+              umma_i8(tmem + j * TA, umma_desc_sw128(wbase + j * (WROWS * BKB) + koff), adesc, ID_ALL, 1);
+          }
+        }
+        umma_commit(&sh->empty[s]);        // stage free once these MMAs have read it
+      }
+      if (ok) {
+        umma_commit(&sh->acc_full);
+      } else {
+        atomicAdd(&g_wait_timeouts, 1);
+        sh->abort_flag = 1;
+      }
+    }
+  } else {
+    // ---- epilogue warps ----
+    bool ok = true;
+    if (nkb > 0) ok = mbar_wait(&sh->acc_full, 0);
+    ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sh->abort_flag) == 0);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      Epi::run(tmem, warp & 3, lane, n0, m0, nkb > 0, ep);
+    } else if (lane == 0) {
+      atomicAdd(&g_wait_timeouts, 1);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace bx

@@ -1,0 +1,98 @@
+"""Exact-mode fused linear on the GPU (through the C ABI) against the CPU oracle and the golden vectors.
+Modelled on the reference's tests/test_vllm_exact_gemm.py and tests/test_exact_ops.py:118-134."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import exact as ox
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _lin(dec, dev="cuda"):
+    from bitexact_llm_b200.exact.model import Lin
+    from bitexact_llm_b200.vllm_plugin.exact_gemm import FusedLin
+    return FusedLin(Lin({k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in dec.items()}, None, dev))
+
+
+def _run(fl, q, sh, checked=True, tile=None):
+    fl.cfg = tile
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = fl(torch.from_numpy(q.astype(np.int32)).cuda(), torch.from_numpy(sh.astype(np.int64)).cuda(), flag, checked)
+    torch.cuda.synchronize()
+    return y.cpu().numpy(), bool(flag.item())
+
+
+def test_golden_linear_with_residual_and_extreme_shifts():
+    from bitexact_llm_b200 import _native as nv
+    z = np.load(os.path.join(GOLD, "exact_ops.npz"))
+    dec = {k: z["lin_" + k] for k in ("limbs", "g", "d", "rr", "rc", "rv")}
+    fl = _lin(dec)
+    for tile in (None, 16, 32, 48, 64, 80):
+        y, flag = _run(fl, z["lin_q"], z["lin_sh"], True, tile)
+        assert np.array_equal(y, z["lin_y"]), tile
+        assert flag == bool(z["lin_flag"])
+    for m in range(len(z["lin_q"])):                      # row-local flag
+        y, flag = _run(fl, z["lin_q"][m:m + 1], z["lin_sh"][m:m + 1])
+        assert np.array_equal(y, z["lin_y"][m:m + 1]) and flag == bool(z["lin_rowflag"][m]), m
+    y, flag = _run(fl, z["lin_q"], z["lin_sh"], False)
+    assert not flag                                          # unchecked calls never touch the flag
+    assert nv.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 2048), (7, 3072, 2048), (37, 512, 8192), (300, 1024, 2048),
+                                   (17, 200, 272), (81, 136, 128)])
+def test_seeded_shapes_against_oracle(M, N, K):
+    rng = np.random.RandomState(M * 1000 + N)
+    W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
+    W[0, :] = 8355711                                        # adversarial: all extremes
+    q = rng.randint(-(1 << 22), (1 << 22) + 1, (M, K)).astype(np.int64)
+    q[0, :] = 1 << 22
+    limbs = np.stack([l.astype(np.int8) for l in ox.split_limbs(W, 3)[0]])
+    nres = max(1, N // 16)
+    rr = np.sort(rng.randint(0, N, nres))
+    dec = {"limbs": limbs, "g": rng.randint(-34, -24, N).astype(np.int64), "d": rng.randint(0, 31, N).astype(np.int64),
+           "rr": rr.astype(np.int64), "rc": rng.randint(0, K, nres).astype(np.int64),
+           "rv": rng.randint(-(1 << 20), 1 << 20, nres).astype(np.int64)}
+    sh = rng.randint(-45, -8, M).astype(np.int64)
+    want, wflag = ox.linear(q, sh, dec, checked=True)
+    fl = _lin(dec)
+    for tile in (None, 16, 80) if M > 16 else (None, 64):
+        y, flag = _run(fl, q, sh, True, tile)
+        assert np.array_equal(y, want), (tile, int((y != want).sum()))
+        assert flag == wflag
+
+
+def test_bf16_weights_config_one_shape():
+    """q_proj shape of Llama-3.2-1B, M = 64, seed-0 N(0, 0.02^2) bf16 weights, uniform |q| <= 2^22."""
+    from bitexact_llm_b200.exact.consts import decompose
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(2048, 2048, generator=g) * 0.02).to(torch.bfloat16)
+    q = torch.randint(-(1 << 22), (1 << 22) + 1, (64, 2048), generator=g)
+    sh = torch.randint(-20, -7, (64,), generator=g)
+    dec = {k: v.numpy() for k, v in decompose(w).items()}
+    assert len(dec["rr"]) > 0
+    want, wflag = ox.linear(q.numpy(), sh.numpy(), dec, checked=True)
+    y, flag = _run(_lin(dec), q.numpy(), sh.numpy())
+    assert np.array_equal(y, want) and flag == wflag
+
+
+def test_strided_rows_and_empty_batch():
+    rng = np.random.RandomState(5)
+    N, K = 128, 256
+    W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
+    dec = {"limbs": np.stack([l.astype(np.int8) for l in ox.split_limbs(W, 3)[0]]), "g": np.full(N, -30, np.int64),
+           "d": np.zeros(N, np.int64), "rr": np.zeros(0, np.int64), "rc": np.zeros(0, np.int64), "rv": np.zeros(0, np.int64)}
+    fl = _lin(dec)
+    big = torch.from_numpy(rng.randint(-(1 << 22), 1 << 22, (5, 2 * K)).astype(np.int32)).cuda()
+    q = big[:, :K]                                           # row stride 2K
+    sh = torch.full((5,), -12, dtype=torch.long, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = fl(q, sh, flag)
+    want = ox.linear(q.cpu().numpy(), sh.cpu().numpy(), dec, checked=False)
+    assert np.array_equal(y.cpu().numpy(), want)
+    assert fl(q[:0], sh[:0], flag).shape == (0, N)
