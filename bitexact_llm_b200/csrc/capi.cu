@@ -7,6 +7,9 @@
 
 #include "../../include/bitexact_b200.h"
 #include "exact_linear.cuh"
+#include "elementwise.cuh"
+#include "paged_attention.cuh"
+#include "sampler.cuh"
 
 namespace {
 
@@ -115,6 +118,148 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
     case 80: return launch_exact<80>(mw, ma, ep, K, st);
     default: return BX_EARG;
   }
+}
+
+int bx_exact_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gm,
+                  const int64_t* ge, int64_t* xo, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag, int M, int D,
+                  int do_norm, void* stream) {
+  if (!xin || !flag || M < 0 || D < 32 || D > 4096 || (D & (D - 1))) return BX_EARG;
+  if ((mode == 0 && !ids) || (mode == 1 && !yin) || mode < 0 || mode > 2) return BX_EARG;
+  if (do_norm && (!gm || !ge || !q || !sh)) return BX_EARG;
+  if (M == 0) return BX_OK;
+  int lg = 0;
+  while ((1 << lg) < D) ++lg;
+  cudaStream_t st = (cudaStream_t)stream;
+  const i64* y = (const i64*)yin; const i64* id = (const i64*)ids;
+  if (mode == 0) norm_kernel<0><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
+  else if (mode == 1) norm_kernel<1><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
+  else norm_kernel<2><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
+  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+}
+
+int bx_exact_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos,
+                 const int64_t* slot, int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, int32_t* q,
+                 int64_t* sh, int32_t* flag, int N, int H, int HKV, int HD, void* stream) {
+  if (!y || !cos || !sin || !pos || !q || !sh || !flag || N < 0) return BX_EARG;
+  if ((HD != 64 && HD != 128) || HKV <= 0 || H % HKV || (cache && (!slot || bs <= 0))) return BX_EARG;
+  if (N == 0) return BX_OK;
+  QkvParams p{(const i64*)y, (const i64*)cos, (const i64*)sin, (const i64*)pos, (const i64*)slot, cache, sc_nb, sc_h,
+              sc_bs, bs, q, (i64*)sh, flag, H, HKV, HD};
+  qkv_kernel<<<dim3(N, HKV), HD / 2, 0, (cudaStream_t)stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+}
+
+int bx_kv_store(int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const int64_t* slot,
+                const int64_t* k, int64_t skz, int64_t skh, const int64_t* v, int64_t svz, int64_t svh, int N,
+                int HKV, int HD, void* stream) {
+  if (!cache || !slot || !k || !v || bs <= 0 || N < 0 || HKV <= 0 || HD <= 0) return BX_EARG;
+  if (N == 0) return BX_OK;
+  kv_store_kernel<<<dim3(N, HKV), 64, 0, (cudaStream_t)stream>>>(cache, (const i64*)slot, (const i64*)k, (const i64*)v,
+                                                                 skz, skh, svz, svh, sc_nb, sc_h, sc_bs, bs, HD);
+  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+}
+
+int bx_exact_attn_out(const int64_t* num, const int64_t* den, int32_t* q, int64_t* sh, int8_t* a8, int N, int K2,
+                      int HD, void* stream) {
+  if (!num || !den || !q || !sh || N < 0 || K2 <= 0 || K2 > AO_THREADS * AO_EPT || HD <= 0 || K2 % HD ||
+      K2 / HD > AO_MAXH)
+    return BX_EARG;
+  if (N == 0) return BX_OK;
+  attn_out_kernel<<<N, AO_THREADS, 0, (cudaStream_t)stream>>>((const i64*)num, (const i64*)den, q, (i64*)sh, a8, N, K2, HD);
+  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+}
+
+int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag,
+                        int N, int FF, void* stream) {
+  if (!y || !lut || !q || !sh || !flag || N < 0 || FF <= 0 || FF > SILU_THREADS * 28) return BX_EARG;
+  if (N == 0) return BX_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int ept = (FF + SILU_THREADS - 1) / SILU_THREADS;
+  if (ept <= 4) silu_kernel<4><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
+  else if (ept <= 16) silu_kernel<16><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
+  else silu_kernel<28><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
+  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+}
+
+int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t sc_nb,
+                       int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
+                       const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num, int64_t* den, int R,
+                       int HKV, int M, int HD, int cluster_size, void* stream) {
+  if (!q || !sh || !qpos || !cache || !bt || !lut || !num || !den) return BX_EARG;
+  if (R < 0 || HKV <= 0 || M < 1 || M > 4 || HD != ATT_HD || bs <= 0 || nblk <= 0) return BX_EARG;
+  const int64_t max_keys = (int64_t)nblk * bs;
+  if (max_keys >= 43690) return BX_EARG;
+  if (R == 0) return BX_OK;
+  const int64_t smem_limit = 227 * 1024;
+  const int64_t cap_limit = (smem_limit - (int64_t)sizeof(AttnShared)) / 32 / 8 * 8;
+  int cs = cluster_size;
+  if (cs == 0) {
+    cs = 1;
+    const int64_t pairs = (int64_t)R * HKV;
+    while (cs < ATT_MAXCS && pairs * cs < 2 * 148) cs *= 2;               // fill the SMs
+    while (cs < ATT_MAXCS && (max_keys + cs - 1) / cs > 2048) cs *= 2;    // keep the score buffer small
+  }
+  if (cs != 1 && cs != 2 && cs != 4 && cs != 8) return BX_EARG;
+  while (cs < ATT_MAXCS && ((max_keys + cs - 1) / cs + 7) / 8 * 8 > cap_limit) cs *= 2;
+  const int chunk_cap = (int)(((max_keys + cs - 1) / cs + 7) / 8 * 8);
+  if (chunk_cap > cap_limit) return BX_EARG;
+  const size_t smem = sizeof(AttnShared) + (size_t)chunk_cap * 32;
+  static size_t smem_set = 0;
+  if (smem > smem_set) {
+    if (cudaFuncSetAttribute(exact_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit) !=
+        cudaSuccess)
+      return BX_ELAUNCH;
+    smem_set = smem_limit;
+  }
+  AttnParams p{q, (const i64*)sh, (const i64*)qpos, cache, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
+               (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, chunk_cap};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cs, R * HKV, 1);
+  cfg.blockDim = dim3(ATT_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, exact_attention_kernel, p) == cudaSuccess ? BX_OK : BX_ELAUNCH;
+}
+
+int bx_pcg_raw(const int64_t* keys, int64_t* out, int n, int V, void* stream) {
+  if (!keys || !out || n < 0 || V <= 0) return BX_EARG;
+  if (n == 0) return BX_OK;
+  const int run = 16;
+  const int blocks = (V + run * SAMPLE_THREADS - 1) / (run * SAMPLE_THREADS);
+  pcg_raw_kernel<<<dim3(blocks, n), SAMPLE_THREADS, 0, (cudaStream_t)stream>>>((const i64*)keys, (i64*)out, V, run);
+  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+}
+
+static int sample_chunks(int M, int V) {
+  int nch = (2 * 148 + (M > 0 ? M : 1) - 1) / (M > 0 ? M : 1);
+  const int maxch = (V + 2047) / 2048;
+  if (nch > maxch) nch = maxch;
+  return nch < 1 ? 1 : nch;
+}
+
+size_t bx_sample_scratch_bytes(int M, int V) { return (size_t)2 * 8 * (size_t)(M > 0 ? M : 0) * sample_chunks(M, V); }
+
+int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
+              int64_t* tok, int M, int V, int bits, void* stream) {
+  if (!logits || !rows || !lnt || !scratch || !tok || M < 0 || V <= 0 || ld < V) return BX_EARG;
+  if (M == 0) return BX_OK;
+  const int nch0 = sample_chunks(M, V);
+  const int ch = ((V + nch0 - 1) / nch0 + 1) / 2 * 2;
+  const int nch = (V + ch - 1) / ch;
+  i64* pmax = (i64*)scratch;
+  i64* pidx = pmax + (size_t)M * nch0;
+  cudaStream_t st = (cudaStream_t)stream;
+  sample_part_kernel<<<dim3(nch, M), SAMPLE_THREADS, 0, st>>>((const i64*)logits, ld, (const i64*)rows, (const i64*)lnt,
+                                                              pmax, pidx, V, ch, nch, bits);
+  sample_combine_kernel<<<(M + 127) / 128, 128, 0, st>>>(pmax, pidx, (i64*)tok, M, nch);
+  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
 }
 
 }  // extern "C"

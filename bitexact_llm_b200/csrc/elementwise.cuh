@@ -1,0 +1,369 @@
+// Row-local integer stages between the linears of exact mode: RMSNorm + quantisation, RoPE + per-head
+// quantisation + KV limb store, attention output division, SiLU * up + quantisation.
+// One CTA per row (or per token and KV head); row maxima and sums are exact integer reductions (warp shuffles,
+// then shared memory), so the thread count cannot change a bit. Bound violations set the sticky flag word.
+//
+// Same integers as src/bitexact/exact/segs.py:49-128 and the fused kernels of
+// src/bitexact/vllm_plugin/exact_fuse.py:136-334.
+#pragma once
+
+#include "bx_rules.cuh"
+
+namespace bx {
+
+// ---- exact division helpers ----
+// floor(x / d) and remainder for 0 <= x < 2^63 from inv = floor((2^64 - 1) / d): one high multiply, one fix-up.
+__device__ __forceinline__ u64 uqr_recip(u64 x, u64 d, u64 inv, u64& rem) {
+  u64 q = __umul64hi(x, inv);
+  u64 r = x - q * d;
+  if (r >= d) { q += 1; r -= d; }
+  rem = r;
+  return q;
+}
+
+// div_round (exact/ops.py:37-57) with the row-constant divisor r given with its reciprocal.
+template <int NIT>
+__device__ __forceinline__ i64 div_round_recip(i64 a, i64 p, u64 r, u64 inv) {
+  u64 rem;
+  const u64 mag = (u64)iabs(a);
+  const u64 q0 = uqr_recip(mag, r, inv, rem);
+  i64 Q, R;
+  if (a < 0) { Q = -(i64)q0 - (rem != 0 ? 1 : 0); R = rem != 0 ? (i64)(r - rem) : 0; }
+  else { Q = (i64)q0; R = (i64)rem; }
+  i64 left = imax(p, 0);
+#pragma unroll
+  for (int i = 0; i < NIT; ++i) {
+    const int c = (int)imin(left, 28);
+    const u64 q1 = uqr_recip((u64)R << c, r, inv, rem);
+    Q = shl(Q, c) + (i64)q1;
+    R = (i64)rem;
+    left -= c;
+  }
+  if (p >= 0) return Q + (2 * R >= (i64)r ? 1 : 0);
+  const int k = (int)iclamp(-p, 1, 62);
+  return (Q + (1ll << (k - 1))) >> k;
+}
+
+// floor(num / den) for 0 <= num < 2^62, 1 <= den <= 2^33: float64 estimate, exact integer fix-up.
+__device__ __forceinline__ i64 fdiv_pos_est(i64 num, i64 den) {
+  i64 q = (i64)((double)num / (double)den);
+  i64 r = num - q * den;
+  if (r < 0) { q -= 1; r += den; }
+  if (r < 0) { q -= 1; r += den; }
+  if (r >= den) { q += 1; r -= den; }
+  if (r >= den) { q += 1; }
+  return q;
+}
+
+// ---- block reductions (exact, order free) ----
+__device__ __forceinline__ i64 warp_max(i64 v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = imax(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ i64 warp_sum(i64 v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// All threads of the CTA get the result. `buf` holds 33 i64 in shared memory.
+template <bool IS_MAX>
+__device__ __forceinline__ i64 block_reduce(i64 v, i64* buf) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  __syncthreads();                       // buf may still be read from a previous reduction
+  if (lane == 0) buf[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    i64 t = lane < nw ? buf[lane] : (IS_MAX ? (i64)0x8000000000000000ull : 0);
+    t = IS_MAX ? warp_max(t) : warp_sum(t);
+    if (lane == 0) buf[32] = t;
+  }
+  __syncthreads();
+  return buf[32];
+}
+
+// 2^-t at out_bits for t >= 0 at 26 fractional bits: table 2^-f at 2^60 (step 2^-14) + linear interpolation
+// (exact/ops.py:108-116).
+__device__ __forceinline__ i64 exp2neg_lut(i64 t, const i64* __restrict__ lut, int out_bits) {
+  const i64 n = t >> FT2;
+  const i64 f = t & ((1ll << FT2) - 1);
+  const int idx = (int)(f >> (FT2 - EXP2_BITS));
+  const i64 rr = f & ((1ll << (FT2 - EXP2_BITS)) - 1);
+  const i64 a = __ldg(lut + idx);
+  const i64 b = __ldg(lut + idx + 1);
+  const i64 v = a + rshs<FT2 - EXP2_BITS>((b - a) * rr);
+  return rshc(v, (i64)(EXP2_ONE - out_bits) + n);
+}
+
+// Activation row -> limb planes a8[l][row][col] (optional), one element.
+__device__ __forceinline__ void store_limb_planes(int8_t* a8, int64_t plane, int64_t off, int q) {
+  int r = q;
+  a8[off] = (int8_t)split8(r);
+  a8[plane + off] = (int8_t)split8(r);
+  a8[2 * plane + off] = (int8_t)split8(r);
+}
+
+// ---- RMSNorm + quant (segs.add_y + norm_q; exact_fuse._norm_kernel) ----
+// MODE 0: x = emb[ids[row]] (int32 table); 1: x = xin + yin; 2: x = xin.
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_EPT = 16;     // D <= 4096
+
+template <int MODE>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_kernel(const void* __restrict__ xin, const i64* __restrict__ yin, const i64* __restrict__ ids,
+            const i64* __restrict__ gm, const i64* __restrict__ ge, i64* __restrict__ xo, int32_t* __restrict__ q,
+            i64* __restrict__ sh_out, int8_t* __restrict__ a8, int32_t* flag, int M, int D, int lg, int do_norm) {
+  __shared__ i64 red[33];
+  const int64_t row = blockIdx.x;
+  i64 x[NORM_EPT];
+  i64 ax = 0;
+#pragma unroll
+  for (int k = 0; k < NORM_EPT; ++k) {
+    const int c = threadIdx.x + k * NORM_THREADS;
+    x[k] = 0;
+    if (c < D) {
+      if (MODE == 0) x[k] = (i64) reinterpret_cast<const int32_t*>(xin)[ids[row] * D + c];
+      else if (MODE == 1) x[k] = reinterpret_cast<const i64*>(xin)[row * D + c] + yin[row * D + c];
+      else x[k] = reinterpret_cast<const i64*>(xin)[row * D + c];
+      if (xo) xo[row * D + c] = x[k];
+      ax = imax(ax, iabs(x[k]));
+    }
+  }
+  ax = block_reduce<true>(ax, red);
+  if (threadIdx.x == 0 && ax >= (1ll << 40)) *flag = 1;
+  if (!do_norm) return;
+  // rms (exact/ops.py:92-105)
+  const i64 amax = imax(ax, 1);
+  const i64 shx = imax((i64)bitlen(amax) - 25, -6);
+  i64 S = 0;
+#pragma unroll
+  for (int k = 0; k < NORM_EPT; ++k) {
+    const i64 xs = rshc(x[k], shx);
+    S += xs * xs;
+  }
+  S = block_reduce<false>(S, red);
+  const i64 T = S + rshc(EPS60 * D, 60 - 2 * (FR - shx));
+  const i64 m = (62 + lg - (i64)bitlen(T)) >> 1;
+  const i64 s = 2 * m - lg;
+  const i64 V = s >= 0 ? (s >= 64 ? 0 : shl(T, (int)s)) : (T >> (int)imin(-s, 63));
+  const i64 r = isqrt(V);
+  const i64 er = shx - FR - m;
+  const u64 inv = ~0ull / (u64)r;
+  // ndiv + quant(., -FN)
+  i64 pmax = 0;
+#pragma unroll
+  for (int k = 0; k < NORM_EPT; ++k) {
+    const int c = threadIdx.x + k * NORM_THREADS;
+    if (c < D) {
+      x[k] = div_round_recip<3>(x[k] * gm[c], ge[c] - FR - er + FN, (u64)r, inv);
+      pmax = imax(pmax, iabs(x[k]));
+    }
+  }
+  pmax = block_reduce<true>(pmax, red);
+  const i64 sh = quant_sh(pmax, -FN);
+  if (threadIdx.x == 0) sh_out[row] = sh;
+  const int64_t plane = (int64_t)M * D;
+#pragma unroll
+  for (int k = 0; k < NORM_EPT; ++k) {
+    const int c = threadIdx.x + k * NORM_THREADS;
+    if (c < D) {
+      const int qv = (int)rshc(x[k], sh + FN);
+      q[row * D + c] = qv;
+      if (a8) store_limb_planes(a8, plane, row * D + c, qv);
+    }
+  }
+}
+
+// ---- RoPE + per-head q quant + K / V limb store (segs.rope_y + q_group + tri_paged.store; _qkv_kernel) ----
+// One CTA per (token, KV head); G query heads, head_dim HD (HD / 2 threads, each owning one rotation pair).
+struct QkvParams {
+  const i64* y;        // [N, (H + 2 HKV) HD] at FR
+  const i64* cos;      // [max_pos, HD / 2] at 30 bits
+  const i64* sin;
+  const i64* pos;      // [N]
+  const i64* slot;     // [N] flat cache slot, < 0: not stored (may be null with cache null)
+  int8_t* cache;       // limb planes [nb, HKV, bs, 8 HD] or null
+  int64_t sc_nb, sc_h, sc_bs;
+  int bs;
+  int32_t* q;          // [N, H HD]
+  i64* sh;             // [N, H]
+  int32_t* flag;
+  int H, HKV, HD;
+};
+
+__global__ void qkv_kernel(const QkvParams p) {
+  __shared__ i64 red[33];
+  const int64_t row = blockIdx.x;
+  const int h = blockIdx.y;
+  const int HH = p.HD / 2;
+  const int G = p.H / p.HKV;
+  const int dd = threadIdx.x;              // 0 .. HH-1
+  const int64_t NT = (int64_t)(p.H + 2 * p.HKV) * p.HD;
+  const i64 pos = p.pos[row];
+  const i64 cs = p.cos[pos * HH + dd];
+  const i64 sn = p.sin[pos * HH + dd];
+  const i64* yr = p.y + row * NT;
+  i64 big = 0;
+  i64 shmax = NEG_BIG;
+  for (int g = 0; g < G; ++g) {
+    const int64_t qc = (int64_t)(h * G + g) * p.HD + dd;
+    const i64 x1 = yr[qc], x2 = yr[qc + HH];
+    big = imax(big, imax(iabs(x1), iabs(x2)));
+    const i64 p1 = x1 * cs - x2 * sn;
+    const i64 p2 = x2 * cs + x1 * sn;
+    const i64 amax = block_reduce<true>(imax(iabs(p1), iabs(p2)), red);
+    const i64 sh = quant_sh(amax, -(FR + FT));
+    shmax = imax(shmax, sh);
+    int32_t* qo = p.q + row * ((int64_t)p.H * p.HD) + qc;
+    qo[0] = (int32_t)rshc(p1, sh + (FR + FT));
+    qo[HH] = (int32_t)rshc(p2, sh + (FR + FT));
+    if (threadIdx.x == 0) p.sh[row * p.H + h * G + g] = sh;
+  }
+  const int64_t kc = (int64_t)p.H * p.HD + (int64_t)h * p.HD + dd;
+  const int64_t vc = (int64_t)(p.H + p.HKV) * p.HD + (int64_t)h * p.HD + dd;
+  const i64 k1 = yr[kc], k2 = yr[kc + HH];
+  const i64 v1r = yr[vc], v2r = yr[vc + HH];
+  big = imax(big, imax(imax(iabs(k1), iabs(k2)), imax(iabs(v1r), iabs(v2r))));
+  const i64 k1o = rshs<FR + FT - FK>(k1 * cs - k2 * sn);
+  const i64 k2o = rshs<FR + FT - FK>(k2 * cs + k1 * sn);
+  const i64 v1 = rshs<FR - FV>(v1r);
+  const i64 v2 = rshs<FR - FV>(v2r);
+  const i64 kvbig = imax(imax(iabs(k1o), iabs(k2o)), imax(iabs(v1), iabs(v2)));
+  big = block_reduce<true>(big, red);
+  const i64 kvmax = block_reduce<true>(kvbig, red);
+  if (threadIdx.x == 0 && (big >= (1ll << 31) || kvmax > LIM3 || shmax > FK + 3 - FZ)) *p.flag = 1;
+  if (p.cache) {
+    const i64 slot = p.slot[row];
+    if (slot >= 0) {
+      int8_t* base = p.cache + (slot / p.bs) * p.sc_nb + (int64_t)h * p.sc_h + (slot % p.bs) * p.sc_bs;
+      int kk1 = (int)k1o, kk2 = (int)k2o, vv1 = (int)v1, vv2 = (int)v2;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        base[i * p.HD + dd] = (int8_t)split8(kk1);
+        base[i * p.HD + HH + dd] = (int8_t)split8(kk2);
+        base[(3 + i) * p.HD + dd] = (int8_t)split8(vv1);
+        base[(3 + i) * p.HD + HH + dd] = (int8_t)split8(vv2);
+      }
+    }
+  }
+}
+
+// K / V int64 [N, HKV, HD] -> limb planes at flat slots (tri_paged.store, src/bitexact/vllm_plugin/tri_paged.py:311-335).
+__global__ void kv_store_kernel(int8_t* cache, const i64* __restrict__ slot, const i64* __restrict__ k,
+                                const i64* __restrict__ v, int64_t skz, int64_t skh, int64_t svz, int64_t svh,
+                                int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, int HD) {
+  const int64_t n = blockIdx.x;
+  const int h = blockIdx.y;
+  const i64 s = slot[n];
+  if (s < 0) return;
+  int8_t* base = cache + (s / bs) * sc_nb + (int64_t)h * sc_h + (s % bs) * sc_bs;
+  for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
+    int kk = (int)k[n * skz + h * skh + dd], vv = (int)v[n * svz + h * svh + dd];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      base[i * HD + dd] = (int8_t)split8(kk);
+      base[(3 + i) * HD + dd] = (int8_t)split8(vv);
+    }
+  }
+}
+
+// ---- attention output: o = div_round(num, 5, den), quant(o, -FR) (segs.attn_div + quant; _attn_out_kernel) ----
+constexpr int AO_THREADS = 256;
+constexpr int AO_EPT = 16;     // H * HD <= 4096
+constexpr int AO_MAXH = 64;
+
+__global__ void __launch_bounds__(AO_THREADS)
+attn_out_kernel(const i64* __restrict__ num, const i64* __restrict__ den, int32_t* __restrict__ q,
+                i64* __restrict__ sh_out, int8_t* __restrict__ a8, int M, int K2, int HD) {
+  __shared__ i64 red[33];
+  __shared__ u64 dens[AO_MAXH], invs[AO_MAXH];
+  const int64_t row = blockIdx.x;
+  const int nh = K2 / HD;
+  if (threadIdx.x < nh) {
+    const u64 dv = (u64)den[row * nh + threadIdx.x];
+    dens[threadIdx.x] = dv;
+    invs[threadIdx.x] = dv ? ~0ull / dv : 0;
+  }
+  __syncthreads();
+  i64 o[AO_EPT];
+  i64 omax = 0;
+#pragma unroll
+  for (int k = 0; k < AO_EPT; ++k) {
+    const int c = threadIdx.x + k * AO_THREADS;
+    o[k] = 0;
+    if (c < K2) {
+      const int hd = c / HD;
+      o[k] = dens[hd] ? div_round_recip<1>(num[row * K2 + c], FR - FV, dens[hd], invs[hd]) : 0;
+      omax = imax(omax, iabs(o[k]));
+    }
+  }
+  omax = block_reduce<true>(omax, red);
+  const i64 sh = quant_sh(omax, -FR);
+  if (threadIdx.x == 0) sh_out[row] = sh;
+  const int64_t plane = (int64_t)M * K2;
+#pragma unroll
+  for (int k = 0; k < AO_EPT; ++k) {
+    const int c = threadIdx.x + k * AO_THREADS;
+    if (c < K2) {
+      const int qv = (int)rshc(o[k], sh + FR);
+      q[row * K2 + c] = qv;
+      if (a8) store_limb_planes(a8, plane, row * K2 + c, qv);
+    }
+  }
+}
+
+// ---- SiLU(g) * u + quant(., -2 FR) (segs.silu_y + quant_silu; exact/ops.py:119-130; _silu_kernel) ----
+constexpr int SILU_THREADS = 512;
+
+__device__ __forceinline__ i64 silu_p(i64 g, i64 u, const i64* __restrict__ lut, bool& bad) {
+  const i64 a = imin(iabs(g), 64ll << FR);
+  const i64 t = rshs<FR + 30 - FT2>(a * L2E30);
+  const i64 E = exp2neg_lut(t, lut, 30);
+  const i64 den = (1ll << 30) + E;
+  const i64 nume = g >= 0 ? (1ll << 60) : shl(E, 30);
+  const i64 sig = fdiv_pos_est(2 * nume + den, 2 * den);          // rdiv
+  const i64 gc = iclamp(g, -(1ll << 32), 1ll << 32);
+  const i64 s = rshs<30>(gc * sig);
+  bad = (bitlen(iabs(s)) + bitlen(iabs(u)) > 62) | (iabs(g) > (1ll << 32));
+  return (i64)((u64)s * (u64)u);
+}
+
+template <int EPT>
+__global__ void __launch_bounds__(SILU_THREADS)
+silu_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, int32_t* __restrict__ q, i64* __restrict__ sh_out,
+            int8_t* __restrict__ a8, int32_t* flag, int M, int FF) {
+  __shared__ i64 red[33];
+  const int64_t row = blockIdx.x;
+  const i64* yr = y + row * (2 * (int64_t)FF);
+  i64 P[EPT];
+  i64 pmax = 0;
+  bool anybad = false;
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) {
+    const int c = threadIdx.x + k * SILU_THREADS;
+    P[k] = 0;
+    if (c < FF) {
+      bool bad;
+      P[k] = silu_p(yr[c], yr[FF + c], lut, bad);
+      anybad |= bad;
+      pmax = imax(pmax, iabs(P[k]));
+    }
+  }
+  if (anybad) *flag = 1;
+  pmax = block_reduce<true>(pmax, red);
+  const i64 sh = quant_sh(pmax, -2 * FR);
+  if (threadIdx.x == 0) sh_out[row] = sh;
+  const int64_t plane = (int64_t)M * FF;
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) {
+    const int c = threadIdx.x + k * SILU_THREADS;
+    if (c < FF) {
+      const int qv = (int)rshc(P[k], sh + 2 * FR);
+      q[row * FF + c] = qv;
+      if (a8) store_limb_planes(a8, plane, row * FF + c, qv);
+    }
+  }
+}
+
+}  // namespace bx

@@ -1,0 +1,298 @@
+// Exact-mode integer attention over the paged int8 limb-plane KV cache, for M <= 4 query rows per (request,
+// KV head): the G query heads of one decode token, or one prefill token.
+//
+//   raw[i, s] = sum_d q[i, d] K[s, d]                 exact (int8 limb products, int32 partials, int64 join)
+//   mx[i]     = max over s <= qpos[i] of raw[i, s]
+//   p[i, s]   = 2^-t at 22 bits, t from (mx - raw) by the row-shift / log2(e) / table + interpolation rule
+//   den[i]    = sum_s p,  num[i, d] = sum_s p V[s, d]  exact int64
+//
+// The weights need the FINAL row maximum (the quantised table does not satisfy exp(a) exp(b) = exp(a + b)), so the
+// keys are swept twice. Here the first sweep keeps the exact scores in shared memory and the second sweep never
+// touches K again: each key's 384 cache bytes are read from HBM exactly once. A (request, head) pair is split
+// over a thread-block CLUSTER: each CTA owns a contiguous key range, the row maxima and the partial sums are
+// exchanged through distributed shared memory; no atomics, no zero fills, no second kernel.
+//
+// Same integers as tri_exact_attn.attend (src/bitexact/vllm_plugin/tri_exact_attn.py:67-165) and as the unfused
+// bmm + softmax_w + bmm of src/bitexact/exact/model.py:114-119: all reductions are exact integer sums / maxima.
+// Cache row (512 bytes per block, head, slot): K limbs at [0, 192), V limbs at [192, 384)
+// (src/bitexact/vllm_plugin/tri_paged.py:22-25).
+#pragma once
+
+#include <cooperative_groups.h>
+
+#include "bx_rules.cuh"
+
+namespace bx {
+
+namespace cg = cooperative_groups;
+
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+constexpr int ATT_HD = 64;
+constexpr int ATT_MAXCS = 8;
+constexpr i64 ATT_NEG = -(1ll << 62);
+constexpr i64 ZMAX = 48ll << FZ;
+
+struct AttnParams {
+  const int32_t* q;     // [R, HKV, M, 64]
+  const i64* sh;        // [R, HKV, M]
+  const i64* qpos;      // [R, M]
+  const int8_t* cache;  // [nb, HKV, bs, 512]
+  int64_t sc_nb, sc_h, sc_bs;
+  int bs;
+  const void* bt;       // block table [*, nblk], int32 or int64
+  int bt64;
+  int64_t sbt;
+  int nblk;
+  const i64* rmap;      // [R] block-table row of each q row (null: identity)
+  const i64* lut;       // 2^-f table, 16385 entries at 2^60
+  i64 l2e;
+  i64* num;             // [R, HKV, M, 64]
+  i64* den;             // [R, HKV, M]
+  int M, HKV;
+  int chunk_cap;        // score slots per query row in shared memory (multiple of 8)
+};
+
+struct AttnShared {
+  i64 pnum[ATT_WARPS][4][ATT_HD];
+  i64 cnum[4][ATT_HD];
+  i64 pden[ATT_WARPS][4];
+  i64 cden[4];
+  i64 wmax[ATT_WARPS][4];
+  i64 cmax[4];
+  int pw[ATT_WARPS][8][4];
+};
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ i64 attn_weight(i64 raw, i64 mx, i64 rowshift, i64 l2e, const i64* __restrict__ lut) {
+  const i64 z = mx - raw;
+  const i64 zf = imin(rshc(z, rowshift), ZMAX);
+  const i64 t = (zf * l2e + (1ll << (FZ + 28 - FT2 - 1))) >> (FZ + 28 - FT2);
+  const i64 n = t >> FT2;
+  const i64 f = t & ((1ll << FT2) - 1);
+  const int idx = (int)(f >> (FT2 - EXP2_BITS));
+  const i64 rr = f & ((1ll << (FT2 - EXP2_BITS)) - 1);
+  const i64 a = __ldg(lut + idx);
+  const i64 b = __ldg(lut + idx + 1);
+  const i64 v = a + rshs<FT2 - EXP2_BITS>((b - a) * rr);
+  const int s = (int)imin((i64)(EXP2_ONE - FP) + n, 62);
+  return (v + (1ll << (s - 1))) >> s;
+}
+
+__global__ void __launch_bounds__(ATT_THREADS)
+exact_attention_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) uint8_t att_smem[];
+  AttnShared* sm = reinterpret_cast<AttnShared*>(att_smem);
+  i64* scores = reinterpret_cast<i64*>(att_smem + sizeof(AttnShared));     // [4][chunk_cap]
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CS = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  const int64_t pz = blockIdx.y;                 // (request, KV head)
+  const int64_t r = pz / p.HKV;
+  const int h = (int)(pz % p.HKV);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // Key range of this CTA.
+  i64 kend = 0;
+  for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[r * p.M + g] + 1);
+  kend = imin(kend, (i64)p.nblk * p.bs);
+  const i64 per = (kend + CS - 1) / CS;
+  i64 chunk = (per + 7) / 8 * 8;
+  if (chunk > p.chunk_cap) chunk = p.chunk_cap;   // cannot happen for kend <= nblk * bs; keeps indices in range
+  const i64 lo = imin((i64)rank * chunk, kend);
+  const i64 hi = imin(lo + chunk, kend);
+  const i64 brow = p.rmap ? p.rmap[r] : r;
+  const int8_t* cbase = p.cache + (int64_t)h * p.sc_h;
+
+  auto key_offset = [&](i64 key) -> int64_t {     // byte offset of the key's cache row (key < hi)
+    const i64 bi = key / p.bs;
+    const i64 blk = p.bt64 ? reinterpret_cast<const i64*>(p.bt)[brow * p.sbt + bi]
+                           : (i64) reinterpret_cast<const int32_t*>(p.bt)[brow * p.sbt + bi];
+    return blk * p.sc_nb + (key % p.bs) * p.sc_bs;
+  };
+
+  // ---- A fragments: the 3 limbs of the M query rows stacked as 16 MMA rows (limb i of query g at row 4 i + g) ----
+  uint32_t afrag[2][4];
+  {
+    const int row_lo = lane >> 2;
+    const int g = row_lo & 3;
+    const int limb_lo = row_lo >> 2;                        // 0 or 1
+    const bool hi_used = row_lo < 4;                        // rows 8..11 = limb 2
+    const int32_t* qrow = p.q + (pz * p.M + g) * ATT_HD;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int d0 = 32 * t + 16 * half + (lane & 3) * 4;
+        uint32_t wl = 0, wh = 0;
+        if (g < p.M) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            int v = qrow[d0 + b];
+            const int l0 = split8(v), l1 = split8(v), l2 = split8(v);
+            wl |= (uint32_t)((limb_lo ? l1 : l0) & 255) << (8 * b);
+            wh |= (uint32_t)(l2 & 255) << (8 * b);
+          }
+        }
+        afrag[t][2 * half] = wl;
+        afrag[t][2 * half + 1] = hi_used ? wh : 0u;
+      }
+    }
+  }
+
+  // ---- sweep 1: exact scores into shared memory, row maxima ----
+  i64 mymax[2] = {ATT_NEG, ATT_NEG};                        // lanes 0..15: query g = lane / 4
+  const i64 qp_s1 = (lane < 16 && (lane >> 2) < p.M) ? p.qpos[r * p.M + (lane >> 2)] : -1;
+  for (i64 kb = lo + 8 * warp; kb < hi; kb += 8 * ATT_WARPS) {
+    const i64 key = kb + (lane >> 2);
+    int acc[3][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+    uint32_t bfrag[3][2][2];
+    if (key < hi) {
+      const int8_t* kp = cbase + key_offset(key) + (lane & 3) * 4;
+#pragma unroll
+      for (int j = 0; j < 3; ++j)
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          bfrag[j][t][0] = *reinterpret_cast<const uint32_t*>(kp + j * ATT_HD + 32 * t);
+          bfrag[j][t][1] = *reinterpret_cast<const uint32_t*>(kp + j * ATT_HD + 32 * t + 16);
+        }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 3; ++j)
+#pragma unroll
+        for (int t = 0; t < 2; ++t) bfrag[j][t][0] = bfrag[j][t][1] = 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+#pragma unroll
+      for (int t = 0; t < 2; ++t) mma_s8(acc[j], afrag[t], bfrag[j][t][0], bfrag[j][t][1]);
+    // join the K limbs; the row's own limb weight is applied below
+    i64 slo[2], shi[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      slo[c] = (i64)acc[0][c] + shl((i64)acc[1][c], 8) + shl((i64)acc[2][c], 16);
+      shi[c] = (i64)acc[0][2 + c] + shl((i64)acc[1][2 + c], 8) + shl((i64)acc[2][2 + c], 16);
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const i64 mid = __shfl_down_sync(0xffffffffu, slo[c], 16);      // limb 1 of the same query and key
+      if (lane < 16) {
+        const i64 raw = slo[c] + shl(mid, 8) + shl(shi[c], 16);
+        const i64 kk = kb + (lane & 3) * 2 + c;
+        const int g = lane >> 2;
+        if (kk < hi) {
+          scores[(int64_t)g * p.chunk_cap + (kk - lo)] = raw;
+          if (kk <= qp_s1) mymax[c] = imax(mymax[c], raw);
+        }
+      }
+    }
+  }
+  {
+    i64 m = imax(mymax[0], mymax[1]);
+    m = imax(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = imax(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    if (lane < 16 && (lane & 3) == 0) sm->wmax[warp][lane >> 2] = m;
+  }
+  __syncthreads();
+  if (threadIdx.x < 4) {
+    i64 m = ATT_NEG;
+    for (int w = 0; w < ATT_WARPS; ++w) m = imax(m, sm->wmax[w][threadIdx.x]);
+    sm->cmax[threadIdx.x] = m;
+  }
+  cluster.sync();
+
+  // ---- sweep 2: weights from the global maxima, den and num = p V ----
+  const int g2 = lane & 3;
+  i64 mx = ATT_NEG;
+  for (int c = 0; c < CS; ++c) mx = imax(mx, cluster.map_shared_rank(sm->cmax, c)[g2]);
+  const bool gok = g2 < p.M;
+  const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
+  const i64 rowshift = gok ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
+  i64 den = 0;
+  i64 nacc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) nacc[a][b] = 0;
+  const int half = lane >> 4, dg = lane & 15;
+  for (i64 kb = lo + 8 * warp; kb < hi; kb += 8 * ATT_WARPS) {
+    const i64 mykey = kb + (lane >> 2);
+    i64 pv = 0;
+    if (mykey < hi && mykey <= qp2) pv = attn_weight(scores[(int64_t)g2 * p.chunk_cap + (mykey - lo)], mx, rowshift, p.l2e, p.lut);
+    den += pv;
+    const i64 kfor = kb + (lane & 7);
+    const int64_t off = kfor < hi ? key_offset(kfor) : 0;
+    __syncwarp();
+    sm->pw[warp][lane >> 2][g2] = (int)pv;
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int kk = 2 * it + half;
+      const int64_t voff = __shfl_sync(0xffffffffu, off, kk);
+      if (kb + kk < hi) {
+        const int8_t* vp = cbase + voff + 3 * ATT_HD + 4 * dg;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vp);
+        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vp + ATT_HD);
+        const uint32_t w2 = *reinterpret_cast<const uint32_t*>(vp + 2 * ATT_HD);
+        const int4 pq = *reinterpret_cast<const int4*>(&sm->pw[warp][kk][0]);
+        const int pg[4] = {pq.x, pq.y, pq.z, pq.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int v = (int)(int8_t)(w0 >> (8 * c)) + ((int)(int8_t)(w1 >> (8 * c)) << 8) +
+                        ((int)(int8_t)(w2 >> (8 * c)) << 16);
+#pragma unroll
+          for (int a = 0; a < 4; ++a) nacc[a][c] += (i64)pg[a] * (i64)v;
+        }
+      }
+    }
+  }
+  // combine the two key parities, then warps, then the cluster
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      nacc[a][c] += __shfl_xor_sync(0xffffffffu, nacc[a][c], 16);
+      if (lane < 16) sm->pnum[warp][a][4 * dg + c] = nacc[a][c];
+    }
+  den += __shfl_xor_sync(0xffffffffu, den, 4);
+  den += __shfl_xor_sync(0xffffffffu, den, 8);
+  den += __shfl_xor_sync(0xffffffffu, den, 16);
+  if (lane < 4) sm->pden[warp][lane] = den;
+  __syncthreads();
+  {
+    const int g = threadIdx.x >> 6, d = threadIdx.x & 63;
+    i64 s = 0;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) s += sm->pnum[w][g][d];
+    sm->cnum[g][d] = s;
+    if (threadIdx.x < 4) {
+      i64 t = 0;
+      for (int w = 0; w < ATT_WARPS; ++w) t += sm->pden[w][threadIdx.x];
+      sm->cden[threadIdx.x] = t;
+    }
+  }
+  cluster.sync();
+  if (rank == 0) {
+    const int g = threadIdx.x >> 6, d = threadIdx.x & 63;
+    if (g < p.M) {
+      i64 s = 0;
+      for (int c = 0; c < CS; ++c) s += cluster.map_shared_rank(&sm->cnum[0][0], c)[g * ATT_HD + d];
+      p.num[(pz * p.M + g) * ATT_HD + d] = s;
+    }
+    if (threadIdx.x < p.M) {
+      i64 t = 0;
+      for (int c = 0; c < CS; ++c) t += cluster.map_shared_rank(sm->cden, c)[threadIdx.x];
+      p.den[pz * p.M + threadIdx.x] = t;
+    }
+  }
+  cluster.sync();                                   // remote shared memory stays valid until rank 0 has read it
+}
+
+}  // namespace bx

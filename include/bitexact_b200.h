@@ -52,6 +52,79 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
  * src/bitexact/intops.py:62-70). */
 int bx_split_limbs(const int32_t* q, int64_t ldq, int8_t* a8, int M, int K, void* stream);
 
+/* ---- exact-mode element-wise stages (one launch each) ---------------------------------------------------
+ * Shared conventions: rows are independent; `flag` is the sticky int32 bound flag; `a8` (may be NULL) receives
+ * the int8 limb planes [3, M, K] of the quantised row q next to q itself, so a following bx_exact_linear_planes
+ * call needs no splitting pass.
+ */
+
+/* RMSNorm + power-of-two quantisation. mode 0: x = emb[ids[m]] (emb int32 [V, D]); 1: x = xin + yin; 2: x = xin
+ * (int64 [M, D]). xo (may be NULL) receives x. With do_norm: q int32 [M, D], sh int64 [M] of
+ * quant(div_round(x * gamma, ...), -40); gm / ge int64 [D] are gamma's exact bf16 significand and exponent.
+ * D a power of two, 32 <= D <= 4096. Sets flag when max |x| >= 2^40.
+ * Replaces exact_fuse.embed_norm / add_norm / pre_norm (src/bitexact/vllm_plugin/exact_fuse.py:136-175, 342-373)
+ * = segs.add_y + Segs.norm_q (src/bitexact/exact/segs.py:44-68, 150-155). */
+int bx_exact_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gm,
+                  const int64_t* ge, int64_t* xo, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag, int M, int D,
+                  int do_norm, void* stream);
+
+/* RoPE (30-bit cos / sin) of q and k, v >> 5, per-(token, head) quantisation of q, K / V limb planes stored at
+ * `slot` of the paged cache (cache NULL: no store; slot < 0: token skipped).
+ *   y int64 [N, (H + 2 HKV) HD] at 24 bits; cos, sin int64 [max_pos, HD / 2]; pos, slot int64 [N]
+ *   cache int8 [nb, HKV, bs, 8 HD] with element strides sc_nb, sc_h, sc_bs (last dimension contiguous)
+ *   q int32 [N, H HD], sh int64 [N, H].  HD in {64, 128}.
+ * Replaces exact_fuse.qkv (src/bitexact/vllm_plugin/exact_fuse.py:178-236, 376-391) = segs.rope_y + q_group
+ * (src/bitexact/exact/segs.py:78-99) + tri_paged.store. */
+int bx_exact_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos,
+                 const int64_t* slot, int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, int32_t* q,
+                 int64_t* sh, int32_t* flag, int N, int H, int HKV, int HD, void* stream);
+
+/* K / V int64 [N, HKV, HD] (element strides skz, skh / svz, svh) -> limb planes at flat slots.
+ * Replaces tri_paged.store (src/bitexact/vllm_plugin/tri_paged.py:311-335). */
+int bx_kv_store(int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const int64_t* slot,
+                const int64_t* k, int64_t skz, int64_t skh, const int64_t* v, int64_t svz, int64_t svh, int N,
+                int HKV, int HD, void* stream);
+
+/* o = div_round(num, 5, den) per head, then row quantisation at 24 bits. num int64 [N, K2], den int64
+ * [N, K2 / HD]; q int32 [N, K2], sh int64 [N]. K2 <= 4096.
+ * Replaces exact_fuse.attn_out (src/bitexact/vllm_plugin/exact_fuse.py:239-248, 394-404) = segs.attn_div + quant. */
+int bx_exact_attn_out(const int64_t* num, const int64_t* den, int32_t* q, int64_t* sh, int8_t* a8, int N, int K2,
+                      int HD, void* stream);
+
+/* silu(gate) * up and row quantisation at 48 bits. y int64 [N, 2 FF] (gate | up), lut = 2^-f table int64 [16385]
+ * at 2^60; q int32 [N, FF], sh int64 [N]. FF <= 14336. Sets flag on the reference's product-bound violation.
+ * Replaces exact_fuse.silu_quant (src/bitexact/vllm_plugin/exact_fuse.py:266-309, 407-414) = segs.silu_y +
+ * quant_silu, ops.silu_mul (src/bitexact/exact/ops.py:119-130). */
+int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag,
+                        int N, int FF, void* stream);
+
+/* ---- exact-mode paged attention -------------------------------------------------------------------------
+ * q int32 [R, HKV, M, 64] (M <= 4), sh int64 [R, HKV, M], qpos int64 [R, M] (key s visible to row i iff
+ * s <= qpos[r, i]), cache int8 limb planes [nb, HKV, bs, 512], bt [*, nblk] block table (int32, or int64 when
+ * bt_is_int64) with row stride sbt, rmap int64 [R] block-table row per request (NULL: identity), lut = 2^-f table,
+ * l2e = round(log2(e) * 2^28) for head_dim 64. Outputs num int64 [R, HKV, M, 64], den int64 [R, HKV, M].
+ * nblk * bs < 43690. cluster_size: CTAs per (request, head) splitting the keys, 0 = automatic, else 1, 2, 4 or 8
+ * (no effect on results).
+ * Replaces tri_exact_attn.attend (src/bitexact/vllm_plugin/tri_exact_attn.py:138-165). */
+int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t sc_nb,
+                       int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
+                       const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num, int64_t* den, int R,
+                       int HKV, int M, int HD, int cluster_size, void* stream);
+
+/* ---- integer sampler ------------------------------------------------------------------------------------
+ * Raw PCG64 words of numpy's default_rng([20261022, seed, t]): keys int64 [n, 2] -> out int64 [n, V].
+ * Replaces gpu_pcg.raw_rows (src/bitexact/vllm_plugin/gpu_pcg.py:94-108; CPU: src/bitexact/sampling.py:27-37). */
+int bx_pcg_raw(const int64_t* keys, int64_t* out, int n, int V, void* stream);
+
+/* Token per row: rows int64 [M, 4] = (seed, t, tn, td); tn == 0 -> first argmax of the logits row, else first
+ * argmax of round(l * td / tn) + gumbel(seed, t) at `bits` fractional bits. logits int64 [M, V], row stride ld;
+ * lnt = ln table int64 [65537] at 40 bits; scratch: bx_sample_scratch_bytes(M, V) bytes; tok int64 [M].
+ * Replaces sampler.integer_sample / tri_logits.first_argmax (src/bitexact/vllm_plugin/sampler.py:57-88,
+ * vllm_plugin/tri_logits.py:77-100) = sampling.sample(gumbel(raw_rows(.))) (src/bitexact/sampling.py:50-67). */
+size_t bx_sample_scratch_bytes(int M, int V);
+int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
+              int64_t* tok, int M, int V, int bits, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
