@@ -1,0 +1,95 @@
+"""A minimal decode loop over `ExactEngine`: paged-cache bookkeeping, chunked prompt processing, greedy /
+Gumbel-max sampling and per-position logits hashes (the reference's `generate` / `logits_sha`,
+src/bitexact/generate.py:21-50, on a batch of sequences with one block-table row each)."""
+
+import hashlib
+
+import torch
+
+from .vllm_plugin import sampler
+
+
+def logits_sha(row):
+    """SHA-256 (hex) of one int64 logits row: equal hashes <=> bit-identical logits."""
+    return hashlib.sha256(row.contiguous().cpu().numpy().tobytes()).hexdigest()
+
+
+class Session:
+    """B sequences, each with a contiguous run of cache blocks (block 0 is the null block)."""
+
+    def __init__(self, eng, B, max_len, bs=16, perm_seed=None):
+        self.eng, self.B, self.bs = eng, B, bs
+        self.nblk = (max_len + bs - 1) // bs
+        nb = 1 + B * self.nblk
+        dev = eng.dev
+        self.kvs = [torch.zeros(nb, eng.HKV, bs, 8 * eng.HD, dtype=torch.int8, device=dev) for _ in range(eng.L)]
+        blocks = torch.arange(1, nb, dtype=torch.int64)
+        if perm_seed is not None:                                  # scattered pages
+            g = torch.Generator().manual_seed(perm_seed)
+            blocks = blocks[torch.randperm(nb - 1, generator=g)]
+        self.bt = blocks.view(B, self.nblk).to(torch.int32).to(dev)
+        self.lens = torch.zeros(B, dtype=torch.long, device=dev)
+        self.rows = torch.arange(B, device=dev)
+
+    def _slots(self, seq, pos):
+        return self.bt[seq, pos // self.bs].long() * self.bs + pos % self.bs
+
+    @torch.no_grad()
+    def prefill(self, prompts, lens=None, chunk_rows=4096):
+        """prompts: int64 [B, P] right-padded, lens [B] the true lengths (default: all P). Token rows are processed
+        in position chunks so that every row's keys are in the cache before it attends. Returns the final residual
+        row of each sequence [B, D]."""
+        B, P = prompts.shape
+        dev = self.eng.dev
+        prompts = prompts.to(dev)
+        lens = torch.full((B,), P, dtype=torch.long, device=dev) if lens is None else lens.to(dev).long()
+        step = max(1, chunk_rows // B)
+        last = torch.zeros(B, self.eng.D, dtype=torch.long, device=dev)
+        for p0 in range(0, P, step):
+            p1 = min(P, p0 + step)
+            grid = torch.arange(p0, p1, device=dev).expand(B, -1)
+            live = grid < lens[:, None]
+            if not bool(live.any()):
+                break
+            pos = grid[live]                                                      # sequence-major rows
+            seq = self.rows[:, None].expand(-1, p1 - p0)[live]
+            x = self.eng.forward(self.kvs, prompts[:, p0:p1][live], pos, self._slots(seq, pos), self.bt, seq)
+            fin = pos == lens[seq] - 1
+            last[seq[fin]] = x[fin]
+        self.lens += lens
+        return last
+
+    @torch.no_grad()
+    def step(self, tokens):
+        """One decode step: tokens int64 [B] at positions lens. Returns the residual rows [B, D]."""
+        pos = self.lens.clone()
+        x = self.eng.forward(self.kvs, tokens, pos, self._slots(self.rows, pos), self.bt, self.rows)
+        self.lens += 1
+        return x
+
+
+@torch.no_grad()
+def generate(eng, prompts, max_new, tn=0, td=1, seeds=None, hashes=True, max_len=None, perm_seed=None, lens=None):
+    """prompts int64 [B, P] (right-padded, true lengths `lens`); generated token t of sequence b uses the noise
+    keyed (seeds[b], t). Returns (tokens [B, max_new] on the host, list of per-position hash lists or None)."""
+    B, P = prompts.shape
+    dev = eng.dev
+    seeds = list(range(B)) if seeds is None else seeds
+    ses = Session(eng, B, max_len or (P + max_new), perm_seed=perm_seed)
+    h = ses.prefill(prompts, lens)
+    rows = torch.zeros(B, 4, dtype=torch.long, device=dev)
+    rows[:, 0] = torch.tensor(seeds, device=dev)
+    rows[:, 2], rows[:, 3] = tn, td
+    toks, shas = [], [[] for _ in range(B)]
+    for t in range(max_new):
+        lg = eng.logits(h)
+        rows[:, 1] = t
+        y = sampler.sample_rows(lg, rows, eng.ln, eng.FR)
+        toks.append(y)
+        if hashes:
+            for b in range(B):
+                shas[b].append(logits_sha(lg[b]))
+        if t + 1 < max_new:
+            h = ses.step(y)
+    eng.check()
+    return torch.stack(toks, 1).cpu(), (shas if hashes else None)

@@ -74,7 +74,8 @@ def decompose(w, row_chunk=4096):
             raise ValueError("residual grid too fine")
         rr, rc = has.nonzero(as_tuple=True)
         s_ = ex[rr, rc] - gf[rr]
-        rv = lost[rr, rc] << s_.clamp(min=0)                     # s_ >= 0: gf <= every residual bit's exponent
+        lv = lost[rr, rc]                                        # exact either way: gf <= the lowest lost bit
+        rv = torch.where(s_ >= 0, lv << s_.clamp(min=0), lv >> (-s_).clamp(min=0))
         rv = torch.where(sm[rr, rc] < 0, -rv, rv)
         rem = W
         for i in range(3):
@@ -98,3 +99,132 @@ def ln_table(bits=FL, device="cpu"):
     """ln(1 + i / 2^16) at `bits` fractional bits (src/bitexact/llama.py:72-75)."""
     i = torch.arange((1 << 16) + 1, dtype=torch.float64)
     return torch.round(torch.log1p(i / (1 << 16)) * 2.0 ** bits).long().to(device)
+
+
+# ---- whole-model constants (same keys as the reference's consts.build, src/bitexact/exact/consts.py:118-149) ----
+
+LLAMA_1B = dict(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=64, rope_theta=500000.0,
+                rms_norm_eps=1e-5, tie_word_embeddings=True,
+                rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=8192))
+
+
+def rope_inv_freq(cfg):
+    """Llama-3 scaled inverse frequencies, float32 arithmetic as transformers' "llama3" rule, returned as float64
+    (what src/bitexact/llama.py:52-62 obtains from transformers)."""
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+    base = cfg["rope_theta"]
+    inv = 1.0 / (base ** (torch.arange(0, hd, 2, dtype=torch.int64).to(torch.float) / hd))
+    rs = cfg.get("rope_scaling")
+    if rs:
+        factor, lo, hi, old = rs["factor"], rs["low_freq_factor"], rs["high_freq_factor"], \
+            rs["original_max_position_embeddings"]
+        low_wl, high_wl = old / lo, old / hi
+        wl = 2 * torch.pi / inv
+        inv_l = torch.where(wl > low_wl, inv / factor, inv)
+        smooth = (old / wl - lo) / (hi - lo)
+        smoothed = (1 - smooth) * inv_l / factor + smooth * inv_l
+        medium = ~(wl < high_wl) * ~(wl > low_wl)
+        inv = torch.where(medium, smoothed, inv_l)
+    return inv.double()
+
+
+def rope_tables(cfg, n_pos=MAX_POS, bits=FT):
+    """Integer cos / sin [n_pos, HD / 2] at `bits` fractional bits (float64, rounded once; llama.py:64-69)."""
+    ang = torch.arange(n_pos, dtype=torch.float64)[:, None] * rope_inv_freq(cfg)[None, :]
+    return torch.round(torch.cos(ang) * 2.0 ** bits).long(), torch.round(torch.sin(ang) * 2.0 ** bits).long()
+
+
+def embedding_table(emb):
+    """bf16 embedding -> int32 at 2^-24, each entry rounded once (consts.py:130-135)."""
+    sm, ex = bf16_parts(emb)
+    s = ex + FR
+    e = torch.where(s >= 0, sm << s.clamp(min=0), (sm + (1 << (-s - 1).clamp(min=0, max=62))) >> (-s).clamp(max=63))
+    if int(e.abs().max()) >= 1 << 31:
+        raise ValueError("embedding out of int32 range")
+    return e.to(torch.int32)
+
+
+def build(cfg, sd, n_layers=None, tables=None, n_pos=MAX_POS):
+    """Constants dict from a HF Llama config dict and state dict (bf16 tensors, any device).
+    tables: optional dict with "cos" / "sin" to use instead of computing them."""
+    L = cfg["num_hidden_layers"] if n_layers is None else n_layers
+    c = {"n_layers": L, "cfg": dict(cfg)}
+
+    def put(name, w):
+        for k, v in decompose(w).items():
+            c[f"{name}.{k}"] = v
+
+    emb = sd["model.embed_tokens.weight"]
+    c["emb"] = embedding_table(emb)
+    for i in range(L):
+        p = f"model.layers.{i}."
+        cat = lambda *ks: torch.cat([sd[p + k] for k in ks])
+        put(f"{i}.wqkv", cat("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight"))
+        put(f"{i}.wo", sd[p + "self_attn.o_proj.weight"])
+        put(f"{i}.wgu", cat("mlp.gate_proj.weight", "mlp.up_proj.weight"))
+        put(f"{i}.wd", sd[p + "mlp.down_proj.weight"])
+        for n, k in (("ga", "input_layernorm.weight"), ("gm", "post_attention_layernorm.weight")):
+            c[f"{i}.{n}.m"], c[f"{i}.{n}.e"] = bf16_parts(sd[p + k])
+    c["gf.m"], c["gf.e"] = bf16_parts(sd["model.norm.weight"])
+    put("lm", sd.get("lm_head.weight", emb))
+    if tables is None:
+        c["cos"], c["sin"] = rope_tables(cfg, n_pos)
+    else:
+        c["cos"], c["sin"] = tables["cos"], tables["sin"]
+    dev = emb.device
+    c["cos"], c["sin"] = c["cos"].to(dev), c["sin"].to(dev)
+    c["exp2"], c["ln"] = exp2_table(dev), ln_table(FL, dev)
+    return c
+
+
+def digest(c, skip=("cfg", "stats", "sha256")):
+    """SHA-256 over every tensor and scalar in key order: the model identity of src/bitexact/llama.py:77-92."""
+    import hashlib
+    h = hashlib.sha256()
+    for k in sorted(c):
+        if k in skip:
+            continue
+        v = c[k]
+        h.update(k.encode())
+        if torch.is_tensor(v):
+            h.update(str(v.dtype).encode())
+            h.update(v.contiguous().cpu().numpy().tobytes())
+        else:
+            h.update(repr(v).encode())
+    return h.hexdigest()
+
+
+def random_state_dict(cfg, seed=0, device="cpu", std=0.02, n_layers=None, gamma_jitter=0.0):
+    """Random-init Llama weights as bf16 (N(0, std^2) matrices, gamma = 1 (+ jitter)), generated with numpy's
+    legacy RandomState on the host when device == "cpu" (stable across machines) or torch's generator on a GPU."""
+    import numpy as np
+    D, FF, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, HKV = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    HD = cfg.get("head_dim") or D // H
+    L = cfg["num_hidden_layers"] if n_layers is None else n_layers
+    if str(device) == "cpu":
+        rng = np.random.RandomState(seed)
+        mat = lambda n, k: torch.from_numpy((rng.standard_normal((n, k)) * std).astype(np.float32)).to(torch.bfloat16)
+        vec = lambda n: torch.from_numpy((1.0 + gamma_jitter * rng.standard_normal(n)).astype(np.float32)).to(torch.bfloat16)
+    else:
+        g = torch.Generator(device=device).manual_seed(seed)
+        mat = lambda n, k: (torch.randn(n, k, generator=g, device=device) * std).to(torch.bfloat16)
+        vec = lambda n: (1.0 + gamma_jitter * torch.randn(n, generator=g, device=device)).to(torch.bfloat16)
+    sd = {"model.embed_tokens.weight": mat(V, D)}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        sd[p + "self_attn.q_proj.weight"] = mat(H * HD, D)
+        sd[p + "self_attn.k_proj.weight"] = mat(HKV * HD, D)
+        sd[p + "self_attn.v_proj.weight"] = mat(HKV * HD, D)
+        sd[p + "self_attn.o_proj.weight"] = mat(D, H * HD)
+        sd[p + "mlp.gate_proj.weight"] = mat(FF, D)
+        sd[p + "mlp.up_proj.weight"] = mat(FF, D)
+        sd[p + "mlp.down_proj.weight"] = mat(D, FF)
+        sd[p + "input_layernorm.weight"] = vec(D)
+        sd[p + "post_attention_layernorm.weight"] = vec(D)
+    sd["model.norm.weight"] = vec(D)
+    if not cfg.get("tie_word_embeddings", True):
+        sd["lm_head.weight"] = mat(V, D)
+    return sd

@@ -10,10 +10,13 @@ and outputs as compressed .npz files.  The tests never import the reference; the
 
 import os
 
+import sys
+
 import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))       # this repository (weight preparation only)
 
 
 def n(t):
@@ -143,7 +146,59 @@ def sampler():
                         logits=n(logits), tok_greedy=n(tok_g), tok_t07=n(tok_t))
 
 
+TINY = dict(vocab_size=128256, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+            num_key_value_heads=1, head_dim=64, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+            rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                              original_max_position_embeddings=8192))
+TINY_PROMPTS = [[3, 500, 17, 128255, 9], list(range(100000, 100017)), [(7919 * i * i + 3) % 128256 for i in range(40)]]
+
+
+def tiny_state_dict():
+    """The tiny model's weights: numpy RandomState(0) (stable across machines), q / k scaled up so that the
+    attention scores matter."""
+    from bitexact_llm_b200.exact.consts import random_state_dict
+    sd = random_state_dict(TINY, seed=0, std=0.05, gamma_jitter=0.2)
+    for i in range(TINY["num_hidden_layers"]):
+        for k in ("q_proj", "k_proj"):
+            n_ = f"model.layers.{i}.self_attn.{k}.weight"
+            sd[n_] = (sd[n_].float() * 4).to(torch.bfloat16)
+    return sd
+
+
+def tiny_model():
+    """A 2-layer GQA Llama (head_dim 64, llama3 RoPE scaling) through the reference's constants build and CPU
+    engine: tokens and logits hashes for three prompts, greedy and T = 0.7."""
+    import tempfile
+
+    from safetensors.torch import save_file
+    from transformers import LlamaConfig
+
+    from bitexact.exact.consts import build
+    from bitexact.exact.model import ExactLlama
+    from bitexact.generate import generate
+    from bitexact_llm_b200.exact import consts as myc
+    sd = tiny_state_dict()
+    with tempfile.TemporaryDirectory() as d:
+        LlamaConfig(max_position_embeddings=4096, **TINY).save_pretrained(d)
+        save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(d, "model.safetensors"))
+        c = build(d)
+    mine = myc.build(TINY, sd)
+    for k, v in c.items():                                    # this repo's weight preparation == the reference's
+        if torch.is_tensor(v):
+            assert torch.equal(v, mine[k]), k
+    assert myc.digest(mine) == c["sha256"]
+    m = ExactLlama(c, "cpu")
+    out = {"sha256": np.array(c["sha256"]), "cos": n(c["cos"][:128]), "sin": n(c["sin"][:128])}
+    for pi, prompt in enumerate(TINY_PROMPTS):
+        for name, (tn, td) in (("greedy", (0, 1)), ("t07", (7, 10))):
+            toks, hashes = generate(m, prompt, 8, tn, td, seed=pi)
+            out[f"p{pi}_{name}_tok"] = np.array(toks)
+            out[f"p{pi}_{name}_sha"] = np.array(hashes)
+    np.savez_compressed(os.path.join(HERE, "tiny_model.npz"), **out)
+
+
 if __name__ == "__main__":
     exact_ops()
     sampler()
+    tiny_model()
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
