@@ -1,0 +1,347 @@
+#!/usr/bin/env python
+"""Benchmark of the exact-mode decode path: random-init Llama-3.2-1B, 512-token prompts, batched decode.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--prompt P] [--impl reference]
+
+A step is one decode step of the whole batch: 16 layers (4 limb GEMMs, RoPE/KV store, paged attention, attention
+division, two RMSNorms, SiLU per layer), final norm, LM head and the integer Gumbel-max sampler at T = 0.7.
+One process per GPU; with N > 1 (torchrun) every rank decodes its own B sequences (sequence sharding, no
+collective on the data path), the timed region is bracketed by a barrier and the time is the max over ranks.
+Prints ONE JSON line. `--impl reference` times the CPU restatement of the reference's float64-GEMM path (the
+oracle) on the host cores for the same metric.
+"""
+
+import argparse
+import contextlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "Llama-3.2-1B exact-mode decode tok/s (bit-exact)"
+SUM_NK = 16 * 60817408 + 262668288          # weight entries touched per generated token (16 layers + LM head)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU leg: the oracle (numpy restatement of the reference's CPU path) on a bounded sample of the workload.
+
+def cpu_decode_sample(args, rows=64, ctx=640, reps=2):
+    """Times one decoder layer and the LM head of the 1B geometry on `rows` token rows at context `ctx` with the
+    oracle, and scales to a whole 16-layer step: tok/s = rows / (L * t_layer + t_head)."""
+    import numpy as np
+    import torch
+
+    from bitexact_llm_b200.exact import consts
+    from oracle import exact as ox
+    from oracle.model import OracleModel
+    cfg = dict(consts.LLAMA_1B)
+    cfg["num_hidden_layers"] = 1
+    dev = "cuda" if torch.cuda.is_available() else "cpu"           # weight preparation only
+    sd = consts.random_state_dict(cfg, seed=0, device=dev)
+    c = consts.build(cfg, sd, n_pos=ctx + 8)
+    c = {k: (v.cpu().numpy() if torch.is_tensor(v) else v) for k, v in c.items()}
+    m = OracleModel(c)
+    for lin in list(m.lin.values()) + [m.lm]:
+        lin["keep_w64"] = True                                     # the reference keeps its float64 weight copy
+    rng = np.random.RandomState(0)
+    ids = rng.randint(0, cfg["vocab_size"], rows).tolist()
+
+    def fresh_cache():
+        cache = m.new_cache(rows)
+        for r in range(rows):
+            kv = cache[r][0]
+            kv["k"] = [rng.randint(-(1 << 18), 1 << 18, (m.HKV, m.HD)) for _ in range(ctx)]
+            kv["v"] = [rng.randint(-(1 << 18), 1 << 18, (m.HKV, m.HD)) for _ in range(ctx)]
+        return cache
+
+    m.forward(fresh_cache(), ids, [ctx] * rows, list(range(rows)))          # warm-up: builds the float64 copies
+    m.logits(np.zeros((rows, m.D), dtype=np.int64) + 12345)
+    t_layer = t_head = 0.0
+    for _ in range(reps):
+        cache = fresh_cache()
+        t0 = time.perf_counter()
+        x = m.forward(cache, ids, [ctx] * rows, list(range(rows)))
+        t1 = time.perf_counter()
+        m.logits(x)
+        t2 = time.perf_counter()
+        t_layer += (t1 - t0) / reps
+        t_head += (t2 - t1) / reps
+    L = args.layers
+    step_s = L * t_layer + t_head
+    return {"value": rows / step_s, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"oracle (numpy float64-GEMM port of the reference CPU path): 1 decoder layer + LM head on "
+                      f"{rows} token rows at context {ctx}, 1B geometry, scaled to {L} layers "
+                      f"(layer {t_layer * 1e3:.1f} ms, head {t_head * 1e3:.1f} ms)"}, step_s
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    base, step_s = cpu_decode_sample(args, reps=max(1, min(args.steps, 3)))
+    line = {"metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int64 (float64 GEMM of int8 limbs)", "data": "synthetic",
+            "impl": "reference",
+            "config": {"workload": "exact-mode decode step, random-init Llama-3.2-1B, CPU sample", "rows": 64,
+                       "context": 640},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([f.strip() for f in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.th.join(timeout=2)
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+class LinTimer:
+    """CUDA-event pairs around every fused-linear call of the timed region (on the launching stream)."""
+
+    def __init__(self):
+        self.pairs, self.on = [], False
+
+    @contextlib.contextmanager
+    def __call__(self, M, N, K):
+        import torch
+        if not self.on:
+            yield
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        yield
+        e1.record()
+        self.pairs.append((e0, e1, M, N, K))
+
+    def totals(self):
+        ms = sum(a.elapsed_time(b) for a, b, *_ in self.pairs)
+        ops = sum(18.0 * M * N * K for *_, M, N, K in self.pairs)
+        return ms, ops, len(self.pairs)
+
+
+def run_b200(args, rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from bitexact_llm_b200 import _native as nv
+    from bitexact_llm_b200.decode import Session
+    from bitexact_llm_b200.exact import consts
+    from bitexact_llm_b200.vllm_plugin import sampler
+    from bitexact_llm_b200.vllm_plugin.exact_run import ExactEngine
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU leg")
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    lib = nv.lib()
+    B, P, K, W = args.batch, args.prompt, args.steps, args.warmup
+
+    cfg = dict(consts.LLAMA_1B)
+    cfg["num_hidden_layers"] = args.layers
+    sd = consts.random_state_dict(cfg, seed=0, device=dev)          # same weights on every rank
+    c = consts.build(cfg, sd, n_pos=P + 2 * (K + W) + 64)
+    del sd
+    eng = ExactEngine(c, dev)
+    del c
+    timer = LinTimer()
+    for ly in eng.layers:
+        for n in ("wqkv", "wo", "wgu", "wd"):
+            ly[n].timer = timer
+    eng.lm.timer = timer
+
+    g = torch.Generator().manual_seed(1000 + rank)                  # every rank its own sequences
+    prompts = torch.randint(0, cfg["vocab_size"], (B, P), generator=g)
+    total_steps = 2 * (K + W) + 8
+    ses = Session(eng, B, P + total_steps, perm_seed=rank)
+    h = ses.prefill(prompts, chunk_rows=8192)
+    rows = torch.zeros(B, 4, dtype=torch.long, device=dev)
+    rows[:, 0] = torch.arange(B, device=dev) + rank * B             # noise key (seed = global sequence index, t)
+    rows[:, 2], rows[:, 3] = 7, 10                                  # T = 0.7
+
+    state = {"h": h, "t": 0}
+
+    def step():
+        lg = eng.logits(state["h"])
+        rows[:, 1] = state["t"]
+        tok = sampler.sample_rows(lg, rows, eng.ln, eng.FR)
+        state["h"] = ses.step(tok)
+        state["t"] += 1
+        return tok
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step()
+    barrier()
+    n0 = lib.bx_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    timer.on = True
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(K):
+            step()
+        e1.record()
+        barrier()
+    timer.on = False
+    launches = lib.bx_launch_count() - n0
+    ms = e0.elapsed_time(e1)
+    lin_ms, lin_ops, lin_calls = timer.totals()
+
+    # end to end: the step's inputs (token ids, positions, sampler keys) come from pinned host memory every step
+    # and the sampled tokens are read back to the host every step.
+    host_tok = torch.zeros(B, dtype=torch.long).pin_memory()
+    host_pos = torch.zeros(B, dtype=torch.long).pin_memory()
+    host_rows = rows.cpu().pin_memory()
+    host_tok.copy_(step())
+    torch.cuda.synchronize()
+    host_pos.copy_(ses.lens)
+
+    def step_e2e():
+        tok_dev = host_tok.to(dev, non_blocking=True)
+        pos_dev = host_pos.to(dev, non_blocking=True)
+        host_rows[:, 1] = state["t"]
+        rows_dev = host_rows.to(dev, non_blocking=True)
+        lg = eng.logits(ses.step(tok_dev, pos_dev))
+        tok = sampler.sample_rows(lg, rows_dev, eng.ln, eng.FR)
+        host_tok.copy_(tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()                    # the host has the tokens
+        host_pos.add_(1)
+        state["t"] += 1
+
+    for _ in range(W):
+        step_e2e()
+    barrier()
+    t_e2e0 = torch.cuda.Event(enable_timing=True)
+    t_e2e1 = torch.cuda.Event(enable_timing=True)
+    t_e2e0.record()
+    for _ in range(K):
+        step_e2e()
+    t_e2e1.record()
+    barrier()
+    ms_e2e = t_e2e0.elapsed_time(t_e2e1)
+    eng.check()
+    if lib.bx_device_status() != 0:
+        raise SystemExit("device-side wait timed out during the benchmark")
+
+    times = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = times.tolist()
+    if rank != 0:
+        return
+
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    bf16 = peaks.get("bf16_tflops_sustained")
+    peak_int8 = 2.0 * bf16 if bf16 else 2.0 * 1400.0
+    achieved = lin_ops / (lin_ms * 1e-3) / 1e12 if lin_ms > 0 else None
+    line = {
+        "metric": METRIC, "value": world * B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 limbs -> int32 -> int64", "data": "synthetic",
+        "config": {"workload": "BASELINE config 4: random-init Llama-3.2-1B exact-mode decode, "
+                               f"{P}-token uniform random prompts, batch {B} per GPU, T=0.7 integer Gumbel sampler",
+                   "batch_per_gpu": B, "prompt": P, "layers": args.layers, "page": 16,
+                   "parallelism": f"sequence-sharded x{world}, no data-path collective",
+                   "l2": "inputs larger than L2 (3.7 GB of weight limbs + KV pages read per step)"},
+        "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 48 * B,
+                "d2h_bytes_per_step": 8 * B, "ms_per_step": ms_e2e / K},
+        "gpu_launches": int(launches),
+        "clocks": clk.summary(),
+        "roofline": {"bound": "tensor", "kernel": "exact_linear_kernel (tcgen05 kind::i8 limb GEMM + fused epilogue)",
+                     "achieved": achieved, "peak": peak_int8, "unit": "TFLOP/s", "ops": "int8 (2*9*M*N*K per call)",
+                     "frac": achieved / peak_int8 if achieved else None,
+                     "peak_source": ("2 x measured sustained bf16 (MEASURED_PEAKS.json); int8 runs at twice the bf16 "
+                                     "rate on the tensor pipe" if bf16 else "2 x fallback bf16 1.4 PFLOP/s"),
+                     "frac_of_nominal_4500": achieved / 4500.0 if achieved else None,
+                     "calls": lin_calls, "ms_per_step": lin_ms / K, "traffic": None},
+        "extra": {"limb_gemm_int8_tops": achieved, "limb_gemm_share_of_step": lin_ms / ms if ms else None},
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"], _ = cpu_decode_sample(args)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+        dist.init_process_group("nccl")
+    try:
+        run_b200(args, rank, world)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

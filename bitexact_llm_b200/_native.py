@@ -20,6 +20,7 @@ P, I, L, Z = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
 
 _SIGNATURES = {
     "bx_version": (I, []),
+    "bx_launch_count": (ctypes.c_longlong, []),
     "bx_device_status": (I, []),
     "bx_clear_device_status": (I, []),
     "bx_exact_linear_scratch_bytes": (Z, [I, I]),

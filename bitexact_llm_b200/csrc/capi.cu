@@ -15,6 +15,14 @@ namespace {
 
 using namespace bx;
 
+long long g_launches = 0;   // kernels launched through this library (host-side count)
+
+inline int launched(int n) {
+  if (cudaGetLastError() != cudaSuccess) return BX_ELAUNCH;
+  g_launches += n;
+  return BX_OK;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -61,7 +69,7 @@ int launch_exact(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiPar
   const int m_tiles = (ep.M + TA - 1) / TA;
   const int n_tiles = (ep.N + WROWS - 1) / WROWS;
   exact_linear_kernel<TA><<<m_tiles * n_tiles, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, m_tiles);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 }  // namespace
@@ -69,6 +77,8 @@ int launch_exact(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiPar
 extern "C" {
 
 int bx_version(void) { return 1; }
+
+long long bx_launch_count(void) { return g_launches; }
 
 int bx_device_status(void) {
   int v = 0;
@@ -90,7 +100,7 @@ int bx_split_limbs(const int32_t* q, int64_t ldq, int8_t* a8, int M, int K, void
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   split_limbs_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, ldq, a8, M, K);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
@@ -134,7 +144,7 @@ int bx_exact_norm(int mode, const void* xin, const int64_t* yin, const int64_t* 
   if (mode == 0) norm_kernel<0><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
   else if (mode == 1) norm_kernel<1><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
   else norm_kernel<2><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 int bx_exact_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos,
@@ -146,7 +156,7 @@ int bx_exact_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const
   QkvParams p{(const i64*)y, (const i64*)cos, (const i64*)sin, (const i64*)pos, (const i64*)slot, cache, sc_nb, sc_h,
               sc_bs, bs, q, (i64*)sh, flag, H, HKV, HD};
   qkv_kernel<<<dim3(N, HKV), HD / 2, 0, (cudaStream_t)stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 int bx_kv_store(int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const int64_t* slot,
@@ -156,7 +166,7 @@ int bx_kv_store(int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int b
   if (N == 0) return BX_OK;
   kv_store_kernel<<<dim3(N, HKV), 64, 0, (cudaStream_t)stream>>>(cache, (const i64*)slot, (const i64*)k, (const i64*)v,
                                                                  skz, skh, svz, svh, sc_nb, sc_h, sc_bs, bs, HD);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 int bx_exact_attn_out(const int64_t* num, const int64_t* den, int32_t* q, int64_t* sh, int8_t* a8, int N, int K2,
@@ -166,7 +176,7 @@ int bx_exact_attn_out(const int64_t* num, const int64_t* den, int32_t* q, int64_
     return BX_EARG;
   if (N == 0) return BX_OK;
   attn_out_kernel<<<N, AO_THREADS, 0, (cudaStream_t)stream>>>((const i64*)num, (const i64*)den, q, (i64*)sh, a8, N, K2, HD);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag,
@@ -178,7 +188,7 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
   if (ept <= 4) silu_kernel<4><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
   else if (ept <= 16) silu_kernel<16><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
   else silu_kernel<28><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t sc_nb,
@@ -214,7 +224,7 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
   AttnParams p{q, (const i64*)sh, (const i64*)qpos, cache, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
                (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, chunk_cap};
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(cs, R * HKV, 1);
+  cfg.gridDim = dim3((unsigned)((int64_t)cs * R * HKV), 1, 1);
   cfg.blockDim = dim3(ATT_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = (cudaStream_t)stream;
@@ -225,7 +235,8 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, exact_attention_kernel, p) == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  if (cudaLaunchKernelEx(&cfg, exact_attention_kernel, p) != cudaSuccess) return BX_ELAUNCH;
+  return launched(1);
 }
 
 int bx_pcg_raw(const int64_t* keys, int64_t* out, int n, int V, void* stream) {
@@ -234,7 +245,7 @@ int bx_pcg_raw(const int64_t* keys, int64_t* out, int n, int V, void* stream) {
   const int run = 16;
   const int blocks = (V + run * SAMPLE_THREADS - 1) / (run * SAMPLE_THREADS);
   pcg_raw_kernel<<<dim3(blocks, n), SAMPLE_THREADS, 0, (cudaStream_t)stream>>>((const i64*)keys, (i64*)out, V, run);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(1);
 }
 
 static int sample_chunks(int M, int V) {
@@ -259,7 +270,7 @@ int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int6
   sample_part_kernel<<<dim3(nch, M), SAMPLE_THREADS, 0, st>>>((const i64*)logits, ld, (const i64*)rows, (const i64*)lnt,
                                                               pmax, pidx, V, ch, nch, bits);
   sample_combine_kernel<<<(M + 127) / 128, 128, 0, st>>>(pmax, pidx, (i64*)tok, M, nch);
-  return cudaGetLastError() == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  return launched(2);
 }
 
 }  // extern "C"

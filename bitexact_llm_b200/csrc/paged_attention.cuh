@@ -94,7 +94,7 @@ exact_attention_kernel(const AttnParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int CS = (int)cluster.num_blocks();
   const int rank = (int)cluster.block_rank();
-  const int64_t pz = blockIdx.y;                 // (request, KV head)
+  const int64_t pz = blockIdx.x / CS;            // (request, KV head); the cluster lies along x
   const int64_t r = pz / p.HKV;
   const int h = (int)(pz % p.HKV);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -60,9 +60,10 @@ class Session:
         return last
 
     @torch.no_grad()
-    def step(self, tokens):
-        """One decode step: tokens int64 [B] at positions lens. Returns the residual rows [B, D]."""
-        pos = self.lens.clone()
+    def step(self, tokens, pos=None):
+        """One decode step: tokens int64 [B] at positions `pos` (default: the lengths tracked on the device).
+        Returns the residual rows [B, D]."""
+        pos = self.lens.clone() if pos is None else pos
         x = self.eng.forward(self.kvs, tokens, pos, self._slots(self.rows, pos), self.bt, self.rows)
         self.lens += 1
         return x

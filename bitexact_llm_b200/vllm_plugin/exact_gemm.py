@@ -30,6 +30,7 @@ class FusedLin:
         else:
             self.R, self.cnt, self.ec, self.ev = 0, None, None, None
         self.cfg = cfg                                           # tile rows (16..80) or None = automatic
+        self.timer = None                                        # optional callable(M, N, K) -> context manager
 
     def __call__(self, q, sh, flag, checked=True):
         M, K = q.shape
@@ -38,6 +39,12 @@ class FusedLin:
         y = torch.empty((M, self.N), dtype=torch.long, device=q.device)
         if M == 0:
             return y
+        if self.timer is not None:
+            with self.timer(M, self.N, K):
+                return self._run(q, sh, flag, checked, y, M, K)
+        return self._run(q, sh, flag, checked, y, M, K)
+
+    def _run(self, q, sh, flag, checked, y, M, K):
         scratch = torch.empty(3 * M * K, dtype=torch.int8, device=q.device)
         rc = nv.lib().bx_exact_linear(q.data_ptr(), q.stride(0), sh.data_ptr(), self.limbs.data_ptr(),
                                       self.d.data_ptr(), self.g.data_ptr(), nv.ptr(self.cnt), nv.ptr(self.ec),

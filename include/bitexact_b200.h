@@ -24,6 +24,7 @@ extern "C" {
 /* Library / device state. bx_device_status: number of device-side waits that timed out since the last clear
  * (0 in a healthy run; synchronises the device). */
 int bx_version(void);
+long long bx_launch_count(void);   /* kernels launched through this library so far (host-side count) */
 int bx_device_status(void);
 int bx_clear_device_status(void);
 

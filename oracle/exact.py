@@ -222,11 +222,19 @@ def decompose(bits):
             "rr": i64(rr), "rc": i64(rc), "rv": rv}
 
 
-def dense_product(q, limbs):
+def dense_product(q, limbs, cache=None):
     """T = q @ W^T exactly, as the reference's CPU path does it: the three activation limbs against
-    the float64 weight, every partial sum < 2^53 (exact/wmm.py:117-121, exact/model.py:56-58)."""
-    L = limbs.astype(I64)
-    w64 = (L[0] + (L[1] << 8) + (L[2] << 16)).astype(np.float64).T
+    the float64 weight, every partial sum < 2^53 (exact/wmm.py:117-121, exact/model.py:56-58).
+    cache: optional dict that keeps the float64 weight copy between calls (the reference's Lin.w64)."""
+    if cache is not None and "w64" in cache:
+        w64 = cache["w64"]
+    else:
+        w64 = limbs[0].astype(np.float64)
+        w64 += 256.0 * limbs[1]
+        w64 += 65536.0 * limbs[2]
+        w64 = np.ascontiguousarray(w64.T)
+        if cache is not None and cache.get("keep_w64"):
+            cache["w64"] = w64
     M = q.shape[0]
     A = np.concatenate(split_limbs(q, 3)[0]).astype(np.float64)
     C = (A @ w64).astype(I64)
@@ -245,7 +253,7 @@ def linear(q, sh, w, checked=True):
     """The exact linear y = round((q @ W_bf16) 2^(sh + FR)): dense limbs + residual + one rounding
     (exact/model.py:61-70 + exact/segs.py:25-32).  w = decompose(...) dict."""
     N = w["limbs"].shape[1]
-    T = dense_product(i64(q), w["limbs"])
+    T = dense_product(i64(q), w["limbs"], w if isinstance(w, dict) else None)
     B = residual(q, w["rr"], w["rc"], w["rv"], N)
     return epilogue(T, B, w["d"], w["g"], sh, checked)
 
