@@ -115,7 +115,11 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
   int rc = bx_split_limbs(q, ldq, scratch, M, K, stream);
   if (rc != BX_OK) return rc;
   int ta = tile_rows;
-  if (ta == 0) ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 48 ? 48 : M <= 64 ? 64 : 80;
+  if (ta == 0) {
+    // Activation rows per CTA: 64 when that still gives most SMs a tile, else 32 (more, smaller tiles).
+    const long n_tiles = (N + WROWS - 1) / WROWS;
+    ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 48 ? 48 : (n_tiles * ((M + 63) / 64) >= 90 ? 64 : 32);
+  }
   CUtensorMap mw, ma;
   if (!make_map(&mw, limbs, (uint64_t)K, (uint64_t)N, 3, WROWS)) return BX_ELAUNCH;
   if (!make_map(&ma, scratch, (uint64_t)K, (uint64_t)M, 3, (uint32_t)ta)) return BX_ELAUNCH;

@@ -30,9 +30,10 @@ template <int TA>
 struct ExactEpilogue {
   using Params = ExactEpiParams;
 
-  // One thread per weight row n (TMEM lane); walks the TA activation rows in chunks of 16 columns.
-  static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int lane, int n0, int m0, bool has_k,
-                                             const Params& p) {
+  // One thread per weight row n (TMEM lane) and column group; walks its share of the TA activation rows in chunks
+  // of 8 accumulator columns.
+  static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
+                                             bool has_k, const Params& p) {
     const int n = n0 + quarter * 32 + lane;
     const bool nok = n < p.N;
     const int d = nok ? (int)p.d[n] : 0;
@@ -41,14 +42,14 @@ struct ExactEpilogue {
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
-    for (int c0 = 0; c0 < TA; c0 += 16) {
+    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
       if (m0 + c0 >= p.M) break;                     // warp-uniform
-      uint32_t acc[5][16];
+      uint32_t acc[5][8];
 #pragma unroll
-      for (int b = 0; b < 5; ++b) tmem_ld16(tbase + b * TA + c0, acc[b]);
+      for (int b = 0; b < 5; ++b) tmem_ld8(tbase + b * TA + c0, acc[b]);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < 8; ++i) {
         const int m = m0 + c0 + i;
         if (m < p.M && nok) {
           i64 T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +

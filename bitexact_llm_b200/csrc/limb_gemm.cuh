@@ -7,16 +7,19 @@
 // adds into TMEM columns [j*TA, (j+NA)*TA): column block b = i + j collects every limb product of weight 2^(8b).
 // A decode batch of 1..16 rows therefore uses the same kernel with TA = 16.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue, warps 2..5 = epilogue
-// (each owns the 32 TMEM lanes its warp id modulo 4 may access). Stages of the shared-memory ring are handed
-// over with mbarriers; every wait is bounded and a timeout ends the CTA with an error status instead of a hang.
+// Warp roles (576 threads): warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue, warps 2..17 = epilogue:
+// four groups of four warps; a warp may only access the 32 TMEM lanes of its warp id modulo 4, so the four warps of
+// a group cover the 128 lanes and the groups share the accumulator columns (the epilogue is integer-ALU latency
+// bound, one warp per scheduler would leave the ALUs idle). Stages of the shared-memory ring are handed over with
+// mbarriers; every wait is bounded and a timeout ends the CTA with an error status instead of a hang.
 #pragma once
 
 #include "bx_ptx.cuh"
 
 namespace bx {
 
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_GROUPS = 4;
+constexpr int GEMM_THREADS = 64 + 128 * EPI_GROUPS;
 constexpr int WROWS = 128;   // weight rows per CTA (MMA M)
 constexpr int BKB = 128;     // K bytes per stage (one 128-byte swizzle atom per row)
 constexpr int UMMA_K = 32;   // int8 K per MMA
@@ -51,7 +54,7 @@ struct GemmShared {
 
 // Runs the main loop for the output tile (weight rows n0.., activation rows m0..) over k blocks [kb0, kb1).
 // On return, for warps 2..5, the accumulators are complete in TMEM (returns false after a timeout).
-// Epi::run(tmem_base, warp_quarter, lane, ...) is called by the epilogue warps.
+// Epi::run(tmem_base, lane_quarter, group, lane, ...) is called by the epilogue warps.
 template <int NW, int NA, int TA, class Epi>
 __device__ __forceinline__ void limb_gemm_tile(const CUtensorMap* tmap_w, const CUtensorMap* tmap_a, int n0, int m0,
                                                int kb0, int kb1, const typename Epi::Params& ep) {
@@ -161,7 +164,7 @@ __device__ __forceinline__ void limb_gemm_tile(const CUtensorMap* tmap_w, const 
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
-      Epi::run(tmem, warp & 3, lane, n0, m0, nkb > 0, ep);
+      Epi::run(tmem, warp & 3, (warp - 2) >> 2, lane, n0, m0, nkb > 0, ep);
     } else if (lane == 0) {
       atomicAdd(&g_wait_timeouts, 1);
     }
