@@ -26,6 +26,8 @@ _SIGNATURES = {
     "bx_exact_linear_scratch_bytes": (Z, [I, I]),
     "bx_exact_linear": (I, [P, L, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, P]),
     "bx_split_limbs": (I, [P, L, P, I, I, P]),
+    "bx_int8_mm": (I, [P, P, P, I, I, I, I, P]),
+    "bx_int8_linear_post": (I, [P, P, P, L, P, P, P, P, I, I, I, I, I, P]),
     "bx_exact_norm": (I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, P]),
     "bx_exact_qkv": (I, [P, P, P, P, P, P, L, L, L, I, P, P, P, I, I, I, I, P]),
     "bx_kv_store": (I, [P, L, L, L, I, P, P, L, L, P, L, L, I, I, I, P]),

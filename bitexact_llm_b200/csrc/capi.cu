@@ -7,6 +7,7 @@
 
 #include "../../include/bitexact_b200.h"
 #include "exact_linear.cuh"
+#include "int8_linear.cuh"
 #include "elementwise.cuh"
 #include "paged_attention.cuh"
 #include "sampler.cuh"
@@ -70,6 +71,44 @@ int launch_exact(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiPar
   const int n_tiles = (ep.N + WROWS - 1) / WROWS;
   exact_linear_kernel<TA><<<m_tiles * n_tiles, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, m_tiles);
   return launched(1);
+}
+
+template <int TA, bool POST>
+int launch_int8(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParams& ep, int K, cudaStream_t st) {
+  using Cfg = GemmCfg<1, 2, TA>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(int8_linear_kernel<TA, POST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return BX_ELAUNCH;
+    configured = true;
+  }
+  const int m_tiles = (ep.M + TA - 1) / TA;
+  const int n_tiles = (ep.N + WROWS - 1) / WROWS;
+  int8_linear_kernel<TA, POST><<<m_tiles * n_tiles, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, m_tiles);
+  return launched(1);
+}
+
+template <bool POST>
+int run_int8(const int8_t* a, const int8_t* w, const Int8EpiParams& ep, int K, int tile_rows, cudaStream_t st) {
+  const int M = ep.M, N = ep.N;
+  if (!a || !w || M < 0 || N <= 0 || K <= 0 || K % 16 || K >= 65536 || !aligned16(a) || !aligned16(w)) return BX_EARG;
+  if (M == 0) return BX_OK;
+  int ta = tile_rows;
+  if (ta == 0) {
+    const long n_tiles = (N + WROWS - 1) / WROWS;
+    ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : (n_tiles * ((M + 127) / 128) >= 90 ? 128 : 64);
+  }
+  CUtensorMap mw, ma;
+  if (!make_map(&mw, w, (uint64_t)K, (uint64_t)N, 1, WROWS)) return BX_ELAUNCH;
+  if (!make_map(&ma, a, (uint64_t)K, (uint64_t)M, 2, (uint32_t)ta)) return BX_ELAUNCH;
+  switch (ta) {
+    case 16: return launch_int8<16, POST>(mw, ma, ep, K, st);
+    case 32: return launch_int8<32, POST>(mw, ma, ep, K, st);
+    case 64: return launch_int8<64, POST>(mw, ma, ep, K, st);
+    case 128: return launch_int8<128, POST>(mw, ma, ep, K, st);
+    default: return BX_EARG;
+  }
 }
 
 }  // namespace
@@ -275,6 +314,20 @@ int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int6
                                                               pmax, pidx, V, ch, nch, bits);
   sample_combine_kernel<<<(M + 127) / 128, 128, 0, st>>>(pmax, pidx, (i64*)tok, M, nch);
   return launched(2);
+}
+
+int bx_int8_mm(const int8_t* a, const int8_t* w, int32_t* c, int M, int N, int K, int tile_rows, void* stream) {
+  if (!c) return BX_EARG;
+  Int8EpiParams ep{c, nullptr, 0, nullptr, nullptr, nullptr, nullptr, M, N, 0};
+  return run_int8<false>(a, w, ep, K, tile_rows, (cudaStream_t)stream);
+}
+
+int bx_int8_linear_post(const int8_t* a, const int8_t* w, const int64_t* mul, int64_t fmsh, const int64_t* mant,
+                        const int64_t* e, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
+                        void* stream) {
+  if (!mul || !mant || !e || !y || !flag) return BX_EARG;
+  Int8EpiParams ep{nullptr, mul, fmsh, mant, e, y, flag, M, N, checked};
+  return run_int8<true>(a, w, ep, K, tile_rows, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,88 @@
+// int8-mode linear on the same tcgen05 main loop: ONE weight limb (int8 weights, per-channel multiplier) against
+// TWO activation limbs (|q| <= 127 * 256). One MMA per 32-deep K slice with N = 2 TA: TMEM column block 0 holds
+// the limb-0 products, block 1 the limb-1 products; acc = c0 + (c1 << 8).
+//
+// Two epilogues:
+//   Int8RawEpilogue   stores the int32 limb products like torch._int_mm on stacked limbs
+//                     (int_mm, src/bitexact/int8/gemm_skinny.py:80-97): c[i * M + m, n] = block i.
+//   Int8PostEpilogue  fuses segs.post (src/bitexact/int8/segs.py:62-67; fused copy _y,
+//                     src/bitexact/vllm_plugin/tri_fuse.py:74-79): t = rsh(acc * m_c, fmsh),
+//                     y = rsh(t * mant_r, 8 - e_r); flag when |t| >= 2^38.
+#pragma once
+
+#include "bx_rules.cuh"
+#include "limb_gemm.cuh"
+
+namespace bx {
+
+// torch's shift rules for int64 tensors, as the reference's kernels restate them
+// (src/bitexact/vllm_plugin/tri_mlp.py:36-54): x >> s saturates at 63, x << s gives 0 from 64 on.
+__device__ __forceinline__ i64 shr_t(i64 x, i64 s) { return x >> (int)imin(s, 63); }
+__device__ __forceinline__ i64 shl_t(i64 x, i64 s) { return s >= 64 ? 0 : shl(x, (int)s); }
+// intops.rsh with a tensor shift (src/bitexact/intops.py:24-34): round half up for s > 0, multiply for s <= 0.
+__device__ __forceinline__ i64 rsh_t(i64 x, i64 s) {
+  const i64 pos = imax(s, 0), neg = imax(-s, 0);
+  const i64 half = pos > 0 ? shl_t(1, pos - 1) : 0;
+  return shl_t(shr_t(x + half, pos), neg);
+}
+
+struct Int8EpiParams {
+  int32_t* c;            // raw: [R, N] int32, limb i of row m at row i * M + m
+  const int64_t* mul;    // post: [N] per-channel multipliers
+  int64_t fmsh;          // post: scalar shift
+  const int64_t* mant;   // post: [M] row scale mantissa in [2^23, 2^24]
+  const int64_t* e;      // post: [M] row scale exponent
+  int64_t* y;            // post: [M, N] at 16 fractional bits
+  int32_t* flag;         // post: sticky |t| >= 2^38 flag
+  int M, N;
+  int checked;
+};
+
+template <int TA, bool POST>
+struct Int8Epilogue {
+  using Params = Int8EpiParams;
+  static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
+                                             bool has_k, const Params& p) {
+    const int n = n0 + quarter * 32 + lane;
+    const bool nok = n < p.N;
+    const i64 mc = (POST && nok) ? p.mul[n] : 0;
+    const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
+    bool any_bad = false;
+#pragma unroll 1
+    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
+      if (m0 + c0 >= p.M) break;
+      uint32_t a0[8], a1[8];
+      tmem_ld8(tbase + c0, a0);
+      tmem_ld8(tbase + TA + c0, a1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = m0 + c0 + i;
+        if (m < p.M && nok) {
+          const int32_t v0 = has_k ? (int32_t)a0[i] : 0, v1 = has_k ? (int32_t)a1[i] : 0;
+          if (POST) {
+            const i64 acc = (i64)v0 + shl((i64)v1, 8);
+            const i64 t = rsh_t((i64)((u64)acc * (u64)mc), p.fmsh);
+            any_bad |= iabs(t) >= (1ll << 38);
+            p.y[(i64)m * p.N + n] = rsh_t((i64)((u64)t * (u64)p.mant[m]), 8 - p.e[m]);
+          } else {
+            p.c[(i64)m * p.N + n] = v0;
+            p.c[((i64)p.M + m) * p.N + n] = v1;
+          }
+        }
+      }
+    }
+    if (POST && p.checked && any_bad) *p.flag = 1;
+  }
+};
+
+template <int TA, bool POST>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+int8_linear_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                   const Int8EpiParams ep, int K, int m_tiles) {
+  const int mt = blockIdx.x % m_tiles;
+  const int nt = blockIdx.x / m_tiles;
+  limb_gemm_tile<1, 2, TA, Int8Epilogue<TA, POST>>(&tmap_w, &tmap_a, nt * WROWS, mt * TA, 0, (K + BKB - 1) / BKB, ep);
+}
+
+}  // namespace bx

@@ -49,6 +49,23 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
                     int8_t* scratch, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
                     void* stream);
 
+/* ---- int8-mode linear ----------------------------------------------------------------------------------
+ * a: the two activation limbs stacked along rows as the reference's stack_limbs(q, 2) lays them out
+ * (src/bitexact/intops.py:73-79): int8 [R, K], limb i of row m at row i * M + m (R >= 2 M; rows beyond 2 M are
+ * padding and are not read). w: int8 [N, K]. Both 16-byte aligned, K % 16 == 0.
+ *
+ * bx_int8_mm: c int32 [R, N]: rows [0, M) = limb-0 products, rows [M, 2 M) = limb-1 products (padding rows are
+ * not written). Replaces int_mm (src/bitexact/int8/gemm_skinny.py:80-97; CPU: imm, src/bitexact/int8/ops.py:87-90).
+ *
+ * bx_int8_linear_post: the same product with segs.post fused (src/bitexact/int8/segs.py:62-67; fused copy
+ * tri_fuse._y, src/bitexact/vllm_plugin/tri_fuse.py:74-79): acc = c0 + (c1 << 8); t = rsh(acc * mul[n], fmsh);
+ * y[m, n] = rsh(t * mant[m], 8 - e[m]) at 16 fractional bits; flag set when `checked` and some |t| >= 2^38.
+ * tile_rows: 0 = automatic, else 16, 32, 64 or 128 (no effect on results). */
+int bx_int8_mm(const int8_t* a, const int8_t* w, int32_t* c, int M, int N, int K, int tile_rows, void* stream);
+int bx_int8_linear_post(const int8_t* a, const int8_t* w, const int64_t* mul, int64_t fmsh, const int64_t* mant,
+                        const int64_t* e, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
+                        void* stream);
+
 /* Activation limb planes only: q int32 [M, K] -> a8 int8 [3, M, K] (signed base-256 digits,
  * src/bitexact/intops.py:62-70). */
 int bx_split_limbs(const int32_t* q, int64_t ldq, int8_t* a8, int M, int K, void* stream);

@@ -146,6 +146,29 @@ def sampler():
                         logits=n(logits), tok_greedy=n(tok_g), tok_t07=n(tok_t))
 
 
+def int8_ops():
+    """int8-mode linear through the reference's CPU path: quant_rows -> imm -> post."""
+    from bitexact.int8 import ops as iops
+    from bitexact.int8 import segs as isegs
+    from bitexact.int8.consts import _q_linear
+    from bitexact.intops import stack_limbs
+    g = torch.Generator().manual_seed(21)
+    N, K, M = 200, 320, 13
+    w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).double()
+    wq, m, fm = _q_linear(w)
+    x = torch.round(torch.randn(M, K, generator=g, dtype=torch.float64) * 2 ** 16).long()
+    x[0] = 0
+    x[1] = torch.randint(-3, 4, (K,), generator=g)
+    x[2] = x[2] << 20
+    q, mant, e = isegs.pre_plain(x, 2)
+    fmsh = fm + 8 - 24
+    acc = iops.imm(q, wq.double().t().contiguous())
+    y, flag = isegs.post(acc, m, torch.tensor(fmsh), mant, e, True)
+    out = dict(w=n(w), wq=n(wq), m=n(m), fm=np.array(fm), x=n(x), q=n(q), mant=n(mant), e=n(e), acc=n(acc), y=n(y),
+               flag=np.array(bool(flag)), stacked=n(stack_limbs(q, 2)))
+    np.savez_compressed(os.path.join(HERE, "int8_ops.npz"), **out)
+
+
 TINY = dict(vocab_size=128256, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
             num_key_value_heads=1, head_dim=64, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
             rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
@@ -200,5 +223,6 @@ def tiny_model():
 if __name__ == "__main__":
     exact_ops()
     sampler()
+    int8_ops()
     tiny_model()
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))

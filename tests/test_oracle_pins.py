@@ -171,3 +171,16 @@ def test_golden_sampler_and_numpy_words():
     assert np.array_equal(osamp.sample(z["logits"], 0, 1), z["tok_greedy"])
     assert np.array_equal(osamp.sample(z["logits"], 7, 10, g), z["tok_t07"])
     assert int(z["tok_greedy"][2]) == 100                # first of two equal maxima
+
+
+def test_golden_int8_linear():
+    from oracle import int8 as o8
+    z = np.load(os.path.join(GOLD, "int8_ops.npz"))
+    wq, m, fm = o8.q_linear(z["w"])
+    assert np.array_equal(wq, z["wq"]) and np.array_equal(m, z["m"]) and fm == int(z["fm"])
+    q, mant, e = o8.pre_plain(z["x"], 2)
+    assert np.array_equal(q, z["q"]) and np.array_equal(mant, z["mant"]) and np.array_equal(e, z["e"])
+    assert np.array_equal(o8.stack_limbs(q, 2), z["stacked"])
+    acc = o8.imm(q, wq)
+    y, flag = o8.post(acc, m, fm + 8 - 24, mant, e)
+    assert np.array_equal(acc, z["acc"]) and np.array_equal(y, z["y"]) and flag == bool(z["flag"])
