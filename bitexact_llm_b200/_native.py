@@ -10,9 +10,10 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_lib", "libbitexact_b200.so")
 
-BX_OK, BX_EARG, BX_ELAUNCH, BX_EDEVICE = 0, -1, -2, -3
+BX_OK, BX_EARG, BX_ELAUNCH, BX_EDEVICE, BX_ELIMIT = 0, -1, -2, -3, -4
 _ERR = {BX_EARG: "argument contract violated (shape / alignment / null pointer)",
-        BX_ELAUNCH: "CUDA launch or driver call failed", BX_EDEVICE: "a device-side wait timed out"}
+        BX_ELAUNCH: "CUDA launch or driver call failed", BX_EDEVICE: "a device-side wait timed out",
+        BX_ELIMIT: "request exceeds the fixed capacity of this entry point"}
 
 _lib = None
 
@@ -25,6 +26,8 @@ _SIGNATURES = {
     "bx_clear_device_status": (I, []),
     "bx_exact_linear_scratch_bytes": (Z, [I, I]),
     "bx_exact_linear": (I, [P, L, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, P]),
+    "bx_exact_linear_static_max_bytes": (Z, []),
+    "bx_exact_linear_static": (I, [P, L, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, P]),
     "bx_split_limbs": (I, [P, L, P, I, I, P]),
     "bx_int8_mm": (I, [P, P, P, I, I, I, I, P]),
     "bx_int8_linear_post": (I, [P, P, P, L, P, P, P, P, I, I, I, I, I, P]),

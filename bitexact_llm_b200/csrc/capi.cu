@@ -330,4 +330,30 @@ int bx_int8_linear_post(const int8_t* a, const int8_t* w, const int64_t* mul, in
   return run_int8<true>(a, w, ep, K, tile_rows, (cudaStream_t)stream);
 }
 
+// ---- allocation-free variant of the exact linear ----
+// Scratch for the activation limb planes lives in the library image instead of caller memory.
+#define BX_STATIC_SCRATCH_BYTES (3u * 256u * 8192u)
+static __device__ __align__(256) int8_t g_static_planes[BX_STATIC_SCRATCH_BYTES];
+
+size_t bx_exact_linear_static_max_bytes(void) { return (size_t)BX_STATIC_SCRATCH_BYTES; }
+
+int bx_exact_linear_static(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
+                           const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
+                           int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows, void* stream) {
+  if (M < 0 || K <= 0) return BX_EARG;
+  if ((size_t)3 * (size_t)M * (size_t)K > (size_t)BX_STATIC_SCRATCH_BYTES) return BX_ELIMIT;
+  // The host-side name of a __device__ array is not a device address; resolve it once per device, with that
+  // device current, and hand the real address to the kernels.
+  static int8_t* dev_ptr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BX_ELAUNCH;
+  if (!dev_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_planes) != cudaSuccess || !p) return BX_ELAUNCH;
+    dev_ptr[dev] = static_cast<int8_t*>(p);
+  }
+  return bx_exact_linear(q, ldq, sh, limbs, d, g, cnt, ec, ev, R, dev_ptr[dev], y, flag, M, N, K, checked, tile_rows,
+                         stream);
+}
+
 }  // extern "C"

@@ -20,6 +20,7 @@ extern "C" {
 #define BX_EARG (-1)     /* shape / alignment / null-pointer contract violated */
 #define BX_ELAUNCH (-2)  /* CUDA launch or driver call failed */
 #define BX_EDEVICE (-3)  /* a bounded device-side wait gave up (see bx_device_status) */
+#define BX_ELIMIT (-4)   /* the request exceeds a fixed capacity of the entry point (see its comment) */
 
 /* Library / device state. bx_device_status: number of device-side waits that timed out since the last clear
  * (0 in a healthy run; synchronises the device). */
@@ -48,6 +49,26 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
                     const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
                     int8_t* scratch, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
                     void* stream);
+
+/* bx_exact_linear for callers that must not allocate device memory. It has no counterpart in the reference.
+ *
+ * Some hosts of this library cannot provide the scratch buffer bx_exact_linear asks for: a plugin that is
+ * invoked while its host application is recording a CUDA graph or has frozen its memory pool, a runtime with a
+ * fixed arena and no allocator behind it, a service that forbids cudaMalloc after start-up to keep latency flat.
+ * For them the activation limb planes go into a fixed buffer that is part of the library image
+ * (bx_exact_linear_static_max_bytes() = 3 * 256 * 8192 bytes = 6 MiB; every GPU that loads the library keeps it
+ * until the process exits). Same arguments as bx_exact_linear without `scratch`; same results bit for bit.
+ *   - 3 * M * K must not exceed the buffer: larger requests return BX_ELIMIT and launch nothing.
+ *   - The first call on each device looks up the buffer's device address (one driver query, no allocation);
+ *     make that first call during start-up, before any stream capture begins.
+ *   - The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - All calls on a device share the one buffer and it keeps the previous call's contents. Nothing in it has to
+ *     start at zero (each call overwrites every byte it later reads), but two calls that run on the GPU at the
+ *     same time - different streams, or different host threads - race on it: serialise them on one stream. */
+size_t bx_exact_linear_static_max_bytes(void);
+int bx_exact_linear_static(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
+                           const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
+                           int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows, void* stream);
 
 /* ---- int8-mode linear ----------------------------------------------------------------------------------
  * a: the two activation limbs stacked along rows as the reference's stack_limbs(q, 2) lays them out
