@@ -36,7 +36,7 @@ _SIGNATURES = {
     "bx_kv_store": (I, [P, L, L, L, I, P, P, L, L, P, L, L, I, I, I, P]),
     "bx_exact_attn_out": (I, [P, P, P, P, P, I, I, I, P]),
     "bx_exact_silu_quant": (I, [P, P, P, P, P, P, I, I, P]),
-    "bx_exact_attention": (I, [P, P, P, P, L, L, L, I, P, I, L, I, P, P, L, P, P, I, I, I, I, I, P]),
+    "bx_exact_attention": (I, [P, P, P, P, L, L, L, L, I, P, I, L, I, P, P, L, P, P, I, I, I, I, I, I, P]),
     "bx_pcg_raw": (I, [P, P, I, I, P]),
     "bx_sample_scratch_bytes": (Z, [I, I]),
     "bx_sample": (I, [P, L, P, P, P, P, I, I, I, P]),

@@ -73,6 +73,30 @@ int launch_exact(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiPar
   return launched(1);
 }
 
+template <int TA>
+int launch_exact_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiParams& ep, int K,
+                            cudaStream_t st) {
+  using Cfg = GemmCfg<3, 3, TA>;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(exact_linear_persistent_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return BX_ELAUNCH;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return BX_ELAUNCH;
+    configured = true;
+  }
+  const int m_tiles = (ep.M + TA - 1) / TA;
+  const int n_tiles = (ep.N + WROWS - 1) / WROWS;
+  const int total = m_tiles * n_tiles;
+  const int grid = total < sms ? total : sms;
+  exact_linear_persistent_kernel<TA><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, n_tiles, m_tiles);
+  return launched(1);
+}
+
 template <int TA, bool POST>
 int launch_int8(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParams& ep, int K, cudaStream_t st) {
   using Cfg = GemmCfg<1, 2, TA>;
@@ -154,15 +178,30 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
   int rc = bx_split_limbs(q, ldq, scratch, M, K, stream);
   if (rc != BX_OK) return rc;
   int ta = tile_rows;
-  if (ta == 0) {
-    // Activation rows per CTA: 64 when that still gives most SMs a tile, else 32 (more, smaller tiles).
+  bool persistent = false;
+  if (ta < 0) {                       // negative: that tile size on the persistent kernel (16, 32, 48)
+    ta = -ta;
+    persistent = true;
+    if (ta != 16 && ta != 32 && ta != 48) return BX_EARG;
+  } else if (ta == 0) {
+    // Activation rows per CTA: 64 when that still gives most SMs a tile, else 32 (more, smaller tiles); a tile
+    // list of more than two waves goes to the persistent kernel (48 rows, overlapped epilogue).
     const long n_tiles = (N + WROWS - 1) / WROWS;
     ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 48 ? 48 : (n_tiles * ((M + 63) / 64) >= 90 ? 64 : 32);
+    if (ta <= 48 && n_tiles * ((M + ta - 1) / ta) > 2 * 148) persistent = true;
+    if (ta == 64 && K <= 4096 && n_tiles * ((M + 47) / 48) > 2 * 148) { ta = 48; persistent = true; }
   }
   CUtensorMap mw, ma;
   if (!make_map(&mw, limbs, (uint64_t)K, (uint64_t)N, 3, WROWS)) return BX_ELAUNCH;
   if (!make_map(&ma, scratch, (uint64_t)K, (uint64_t)M, 3, (uint32_t)ta)) return BX_ELAUNCH;
   ExactEpiParams ep{q, ldq, sh, d, g, cnt, ec, ev, R, y, flag, M, N, checked};
+  if (persistent) {
+    switch (ta) {
+      case 16: return launch_exact_persistent<16>(mw, ma, ep, K, st);
+      case 32: return launch_exact_persistent<32>(mw, ma, ep, K, st);
+      default: return launch_exact_persistent<48>(mw, ma, ep, K, st);
+    }
+  }
   switch (ta) {
     case 16: return launch_exact<16>(mw, ma, ep, K, st);
     case 32: return launch_exact<32>(mw, ma, ep, K, st);
@@ -234,17 +273,25 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
   return launched(1);
 }
 
-int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t sc_nb,
-                       int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
-                       const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num, int64_t* den, int R,
-                       int HKV, int M, int HD, int cluster_size, void* stream) {
+int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
+                       int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
+                       int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
+                       int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream) {
   if (!q || !sh || !qpos || !cache || !bt || !lut || !num || !den) return BX_EARG;
-  if (R < 0 || HKV <= 0 || M < 1 || M > 4 || HD != ATT_HD || bs <= 0 || nblk <= 0) return BX_EARG;
+  if (R < 0 || HKV <= 0 || M < 1 || M > 4 || HD != ATT_HD || bs <= 0 || nblk <= 0 || nb <= 0) return BX_EARG;
   const int64_t max_keys = (int64_t)nblk * bs;
   if (max_keys >= 43690) return BX_EARG;
   if (R == 0) return BX_OK;
   const int64_t smem_limit = 227 * 1024;
-  const int64_t cap_limit = (smem_limit - (int64_t)sizeof(AttnShared)) / 32 / 8 * 8;
+  // TMA-staged kernel when the cache layout allows a tensor map over it, else the direct-load kernel.
+  const bool tma_ok = (bs % 8 == 0) && (ATT2_STAGE_KEYS % bs == 0) && sc_bs % 16 == 0 && sc_h % 16 == 0 &&
+                      sc_nb % 16 == 0 && sc_bs >= 384 && aligned16(cache);
+  if (variant == 2 && !tma_ok) return BX_EARG;
+  const bool use_tma = variant == 2 || (variant == 0 && tma_ok);
+  const int64_t fixed = use_tma ? (int64_t)ATT2_NS * ATT2_STAGE_BYTES + (int64_t)sizeof(Attn2Small)
+                                : (int64_t)sizeof(AttnShared);
+  const int64_t gran = use_tma ? ATT2_STAGE_KEYS : 8;
+  const int64_t cap_limit = (smem_limit - fixed) / 32 / gran * gran;
   int cs = cluster_size;
   if (cs == 0) {
     cs = 1;
@@ -253,22 +300,16 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
     while (cs < ATT_MAXCS && (max_keys + cs - 1) / cs > 2048) cs *= 2;    // keep the score buffer small
   }
   if (cs != 1 && cs != 2 && cs != 4 && cs != 8) return BX_EARG;
-  while (cs < ATT_MAXCS && ((max_keys + cs - 1) / cs + 7) / 8 * 8 > cap_limit) cs *= 2;
-  const int chunk_cap = (int)(((max_keys + cs - 1) / cs + 7) / 8 * 8);
+  auto cap_of = [&](int c) { return ((max_keys + c - 1) / c + gran - 1) / gran * gran; };
+  while (cs < ATT_MAXCS && cap_of(cs) > cap_limit) cs *= 2;
+  const int chunk_cap = (int)cap_of(cs);
   if (chunk_cap > cap_limit) return BX_EARG;
-  const size_t smem = sizeof(AttnShared) + (size_t)chunk_cap * 32;
-  static size_t smem_set = 0;
-  if (smem > smem_set) {
-    if (cudaFuncSetAttribute(exact_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit) !=
-        cudaSuccess)
-      return BX_ELAUNCH;
-    smem_set = smem_limit;
-  }
+  const size_t smem = (size_t)fixed + (size_t)chunk_cap * 32;
   AttnParams p{q, (const i64*)sh, (const i64*)qpos, cache, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
                (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, chunk_cap};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)((int64_t)cs * R * HKV), 1, 1);
-  cfg.blockDim = dim3(ATT_THREADS, 1, 1);
+  cfg.blockDim = dim3(use_tma ? ATT2_THREADS : ATT_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];
@@ -278,7 +319,31 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, exact_attention_kernel, p) != cudaSuccess) return BX_ELAUNCH;
+  static bool configured[2] = {false, false};
+  if (!configured[use_tma]) {
+    cudaError_t e = use_tma ? cudaFuncSetAttribute(exact_attention_tma_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
+                            : cudaFuncSetAttribute(exact_attention_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
+    if (e != cudaSuccess) return BX_ELAUNCH;
+    configured[use_tma] = true;
+  }
+  if (use_tma) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return BX_ELAUNCH;
+    CUtensorMap tm;
+    cuuint64_t dims[4] = {512, (cuuint64_t)bs, (cuuint64_t)HKV, (cuuint64_t)nb};
+    cuuint64_t strides[3] = {(cuuint64_t)sc_bs, (cuuint64_t)sc_h, (cuuint64_t)sc_nb};
+    cuuint32_t box[4] = {ATT2_HALF, (cuuint32_t)bs, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(cache), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return BX_ELAUNCH;
+    if (cudaLaunchKernelEx(&cfg, exact_attention_tma_kernel, tm, p) != cudaSuccess) return BX_ELAUNCH;
+  } else {
+    if (cudaLaunchKernelEx(&cfg, exact_attention_kernel, p) != cudaSuccess) return BX_ELAUNCH;
+  }
   return launched(1);
 }
 

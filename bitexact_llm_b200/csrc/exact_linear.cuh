@@ -78,6 +78,14 @@ exact_linear_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   limb_gemm_tile<3, 3, TA, ExactEpilogue<TA>>(&tmap_w, &tmap_a, nt * WROWS, mt * TA, 0, (K + BKB - 1) / BKB, ep);
 }
 
+// Persistent form (one CTA per SM, double-buffered accumulators): used when the tile list is longer than one wave.
+template <int TA>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+exact_linear_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                               const ExactEpiParams ep, int K, int n_tiles, int m_tiles) {
+  limb_gemm_persistent<3, 3, TA, ExactEpilogue<TA>>(&tmap_w, &tmap_a, n_tiles, m_tiles, (K + BKB - 1) / BKB, ep);
+}
+
 // q int32 [M, K] (row stride ldq) -> limb planes int8 [3, M, K] (signed base-256 digits, intops.py:62-70).
 __global__ void split_limbs_kernel(const int32_t* __restrict__ q, int64_t ldq, int8_t* __restrict__ a8, int M, int K) {
   const int64_t per_row = K / 16;

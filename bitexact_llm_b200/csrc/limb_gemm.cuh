@@ -24,7 +24,6 @@ constexpr int WROWS = 128;   // weight rows per CTA (MMA M)
 constexpr int BKB = 128;     // K bytes per stage (one 128-byte swizzle atom per row)
 constexpr int UMMA_K = 32;   // int8 K per MMA
 
-__device__ int g_wait_timeouts;   // number of bounded waits that gave up (0 in a healthy run)
 
 template <int NW, int NA, int TA>
 struct GemmCfg {
@@ -176,6 +175,159 @@ __device__ __forceinline__ void limb_gemm_tile(const CUtensorMap* tmap_w, const 
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Persistent variant: one CTA per SM walks a list of output tiles; two TMEM accumulator buffers let the epilogue of
+// tile i run while the MMAs of tile i + 1 fill the other buffer, and the TMA producer runs ahead across tile
+// boundaries. Needs 2 * COLS <= 512 TMEM columns (exact mode: TA <= 48).
+struct GemmSharedP {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template <int NW, int NA, int TA, class Epi>
+__device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, const CUtensorMap* tmap_a, int n_tiles,
+                                                     int m_tiles, int nkb, const typename Epi::Params& ep) {
+  using Cfg = GemmCfg<NW, NA, TA>;
+  static_assert(2 * Cfg::COLS <= 512, "two accumulator buffers must fit in TMEM");
+  constexpr int TCOLS = 2 * Cfg::COLS <= 64 ? 64 : 2 * Cfg::COLS <= 128 ? 128 : 2 * Cfg::COLS <= 256 ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmSharedP* sh = reinterpret_cast<GemmSharedP*>(ring + Cfg::STAGES * Cfg::STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total = n_tiles * m_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->acc_full[b], 1);
+      mbar_init(&sh->acc_empty[b], 4 * EPI_GROUPS);
+    }
+    sh->abort_flag = *reinterpret_cast<volatile int*>(&g_wait_timeouts) != 0;
+    fence_barrier_init();
+    tma_prefetch_desc(tmap_w);
+    tma_prefetch_desc(tmap_a);
+  }
+  __syncthreads();
+  if (sh->abort_flag) return;
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, TCOLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer: one continuous stream of stages over all tiles of this CTA ----
+      int it = 0;            // global stage counter
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int n0 = (tile / m_tiles) * WROWS, m0 = (tile % m_tiles) * TA;
+        for (int i = 0; i < nkb && ok; ++i, ++it) {
+          const int s = it % Cfg::STAGES, round = it / Cfg::STAGES;
+          if (round > 0) ok = mbar_wait(&sh->empty[s], (round - 1) & 1);
+          if (!ok) break;
+          uint8_t* st = ring + s * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&sh->full[s], Cfg::STAGE_BYTES);
+          tma_load_3d(st, tmap_w, &sh->full[s], i * BKB, n0, 0);
+          tma_load_3d(st + Cfg::W_BYTES, tmap_a, &sh->full[s], i * BKB, m0, 0);
+        }
+      }
+      if (!ok) {
+        atomicAdd(&g_wait_timeouts, 1);
+        sh->abort_flag = 1;
+        for (int i = (it > Cfg::STAGES ? it - Cfg::STAGES : 0); i < it; ++i)
+          mbar_wait(&sh->full[i % Cfg::STAGES], (i / Cfg::STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issue ----
+      constexpr uint32_t ID_ALL = umma_idesc_i8(NA * TA);
+      constexpr uint32_t ID_ONE = umma_idesc_i8(TA);
+      constexpr uint32_t ID_REST = umma_idesc_i8(NA > 1 ? (NA - 1) * TA : TA);
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++tcount) {
+        const int buf = tcount & 1, use = tcount >> 1;
+        if (use > 0) ok = mbar_wait(&sh->acc_empty[buf], (use - 1) & 1);   // epilogue has drained this buffer
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc = tmem + buf * Cfg::COLS;
+        for (int i = 0; i < nkb && ok; ++i, ++it) {
+          const int s = it % Cfg::STAGES;
+          ok = mbar_wait(&sh->full[s], (it / Cfg::STAGES) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t wbase = smem_u32(ring + s * Cfg::STAGE_BYTES);
+          const uint32_t abase = wbase + Cfg::W_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < BKB / UMMA_K; ++ks) {
+            const uint32_t koff = ks * UMMA_K;
+            const uint64_t adesc = umma_desc_sw128(abase + koff);
+            if (i == 0 && ks == 0) {
+              umma_i8(acc, umma_desc_sw128(wbase + koff), adesc, ID_ALL, 0);
+#pragma unroll
+              for (int j = 1; j < NW; ++j) {
+                const uint64_t wdesc = umma_desc_sw128(wbase + j * (WROWS * BKB) + koff);
+                umma_i8(acc + (j + NA - 1) * TA, wdesc, umma_desc_sw128(abase + (NA - 1) * TA * BKB + koff), ID_ONE, 0);
+                if (NA > 1) umma_i8(acc + j * TA, wdesc, adesc, ID_REST, 1);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < NW; ++j)
+                umma_i8(acc + j * TA, umma_desc_sw128(wbase + j * (WROWS * BKB) + koff), adesc, ID_ALL, 1);
+            }
+          }
+          umma_commit(&sh->empty[s]);
+        }
+        if (ok) umma_commit(&sh->acc_full[buf]);
+      }
+      if (!ok) {
+        atomicAdd(&g_wait_timeouts, 1);
+        sh->abort_flag = 1;
+      }
+    }
+  } else {
+    // ---- epilogue warps ----
+    int tcount = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
+      const int buf = tcount & 1, use = tcount >> 1;
+      if (ok) ok = mbar_wait(&sh->acc_full[buf], use & 1);
+      ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sh->abort_flag) == 0);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      Epi::run(tmem + buf * Cfg::COLS, warp & 3, (warp - 2) >> 2, lane, (tile / m_tiles) * WROWS, (tile % m_tiles) * TA,
+               nkb > 0, ep);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
+    }
+    if (!ok && lane == 0) atomicAdd(&g_wait_timeouts, 1);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, TCOLS);
   }
 }
 

@@ -20,6 +20,7 @@
 
 #include <cooperative_groups.h>
 
+#include "bx_ptx.cuh"
 #include "bx_rules.cuh"
 
 namespace bx {
@@ -87,7 +88,7 @@ __device__ __forceinline__ i64 attn_weight(i64 raw, i64 mx, i64 rowshift, i64 l2
 
 __global__ void __launch_bounds__(ATT_THREADS)
 exact_attention_kernel(const AttnParams p) {
-  extern __shared__ __align__(16) uint8_t att_smem[];
+  extern __shared__ __align__(128) uint8_t att_smem[];
   AttnShared* sm = reinterpret_cast<AttnShared*>(att_smem);
   i64* scores = reinterpret_cast<i64*>(att_smem + sizeof(AttnShared));     // [4][chunk_cap]
 
@@ -293,6 +294,291 @@ exact_attention_kernel(const AttnParams p) {
     }
   }
   cluster.sync();                                   // remote shared memory stays valid until rank 0 has read it
+}
+
+}  // namespace bx
+
+// =====================================================================================================================
+// TMA-staged variant (page sizes 8, 16, 32, 64; 16-byte aligned cache strides). Same integers, same cluster layout.
+//
+// A producer warp streams the cache pages of the CTA's key range through a shared-memory ring with
+// cp.async.bulk.tensor (4-D map over the cache: byte, slot, head, block; box = 192 bytes x page): first the K halves
+// of the rows (sweep 1), then the V halves (sweep 2), 64 keys per stage. Eight consumer warps take 8 keys of every
+// stage each: q.K with mma.sync from shared-memory fragments (one 16-byte load per limb), exact scores into
+// shared memory, then weights and p.V from the staged V rows. Hand-over by full / empty mbarriers with bounded waits.
+namespace bx {
+
+constexpr int ATT2_STAGE_KEYS = 64;
+constexpr int ATT2_HALF = 192;                                  // bytes of K (or V) limbs per cache row
+constexpr int ATT2_STAGE_BYTES = ATT2_STAGE_KEYS * ATT2_HALF;   // 12288
+constexpr int ATT2_NS = 4;
+constexpr int ATT2_THREADS = ATT_THREADS + 32;                  // 8 consumer warps + 1 producer warp
+
+struct Attn2Small {
+  i64 cnum[4][ATT_HD];
+  i64 pden[ATT_WARPS][4];
+  i64 cden[4];
+  i64 wmax[ATT_WARPS][4];
+  i64 cmax[4];
+  int pw[ATT_WARPS][8][4];
+  uint64_t full[ATT2_NS];
+  uint64_t empty[ATT2_NS];
+  uint32_t abort_flag;
+};
+
+__global__ void __launch_bounds__(ATT2_THREADS, 2)
+exact_attention_tma_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t att_smem[];
+  uint8_t* ring = att_smem;                                                        // [NS][64 keys][192 B]
+  i64* scores = reinterpret_cast<i64*>(att_smem + ATT2_NS * ATT2_STAGE_BYTES);     // [chunk_cap][4]
+  Attn2Small* sm = reinterpret_cast<Attn2Small*>(att_smem + ATT2_NS * ATT2_STAGE_BYTES + (size_t)p.chunk_cap * 32);
+  i64 (*pnum)[4][ATT_HD] = reinterpret_cast<i64 (*)[4][ATT_HD]>(ring);             // aliases the ring after the sweeps
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CS = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  const int64_t pz = blockIdx.x / CS;
+  const int64_t r = pz / p.HKV;
+  const int h = (int)(pz % p.HKV);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  i64 kend = 0;
+  for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[r * p.M + g] + 1);
+  kend = imin(kend, (i64)p.nblk * p.bs);
+  const i64 per = (kend + CS - 1) / CS;
+  i64 chunk = (per + ATT2_STAGE_KEYS - 1) / ATT2_STAGE_KEYS * ATT2_STAGE_KEYS;
+  if (chunk > p.chunk_cap) chunk = p.chunk_cap;
+  const i64 lo = imin((i64)rank * chunk, kend);
+  const i64 hi = imin(lo + chunk, kend);
+  const int nst = (int)((hi - lo + ATT2_STAGE_KEYS - 1) / ATT2_STAGE_KEYS);
+  const i64 brow = p.rmap ? p.rmap[r] : r;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ATT2_NS; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], ATT_WARPS);
+    }
+    sm->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap);
+  }
+  __syncthreads();
+
+  if (warp == ATT_WARPS) {
+    // ---------------- producer warp ----------------
+    const int pages_per_stage = ATT2_STAGE_KEYS / p.bs;
+    bool ok = true;
+    for (int idx = 0; idx < 2 * nst; ++idx) {
+      if (idx == nst) cluster_arrive();                            // sweep-1 loads are all issued
+      const int sweep = idx >= nst, st = idx - sweep * nst;
+      const int slot = idx % ATT2_NS, round = idx / ATT2_NS;
+      if (ok && round > 0) ok = mbar_wait(&sm->empty[slot], (round - 1) & 1);
+      if (!ok) continue;                                           // keep the barrier protocol, load nothing more
+      const i64 key0 = lo + (i64)st * ATT2_STAGE_KEYS;
+      int npages = (int)((hi - key0 + p.bs - 1) / p.bs);
+      if (npages > pages_per_stage) npages = pages_per_stage;
+      if (lane == 0) mbar_arrive_expect_tx(&sm->full[slot], (uint32_t)(npages * p.bs * ATT2_HALF));
+      __syncwarp();
+      if (lane < npages) {
+        const i64 bi = key0 / p.bs + lane;
+        const i64 blk = p.bt64 ? reinterpret_cast<const i64*>(p.bt)[brow * p.sbt + bi]
+                               : (i64) reinterpret_cast<const int32_t*>(p.bt)[brow * p.sbt + bi];
+        tma_load_4d(ring + slot * ATT2_STAGE_BYTES + lane * p.bs * ATT2_HALF, &tmap, &sm->full[slot],
+                    sweep ? ATT2_HALF : 0, 0, h, (int)blk);
+      }
+    }
+    if (nst == 0) cluster_arrive();
+    if (!ok && lane == 0) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
+    cluster_wait();
+    cluster.sync();
+    cluster.sync();
+    return;
+  }
+
+  // ---------------- consumer warps ----------------
+  // A fragments: limb i of query g at MMA row 4 i + g; contraction slot (t, half, byte b) of lane c holds
+  // dim 16 c + 4 (2 t + half) + b, which matches one 16-byte shared-memory load per K limb on the B side.
+  uint32_t afrag[2][4];
+  {
+    const int row_lo = lane >> 2;
+    const int g = row_lo & 3;
+    const int limb_lo = row_lo >> 2;
+    const bool hi_used = row_lo < 4;
+    const int32_t* qrow = p.q + (pz * p.M + g) * ATT_HD;
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int d0 = 16 * (lane & 3) + 4 * (2 * t + half);
+        uint32_t wl = 0, wh = 0;
+        if (g < p.M) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            int v = qrow[d0 + b];
+            const int l0 = split8(v), l1 = split8(v), l2 = split8(v);
+            wl |= (uint32_t)((limb_lo ? l1 : l0) & 255) << (8 * b);
+            wh |= (uint32_t)(l2 & 255) << (8 * b);
+          }
+        }
+        afrag[t][2 * half] = wl;
+        afrag[t][2 * half + 1] = hi_used ? wh : 0u;
+      }
+  }
+
+  bool ok = true;
+  // ---- sweep 1 ----
+  i64 mymax[2] = {ATT_NEG, ATT_NEG};
+  const i64 qp_s1 = (lane < 16 && (lane >> 2) < p.M) ? p.qpos[r * p.M + (lane >> 2)] : -1;
+  for (int st = 0; st < nst; ++st) {
+    const int slot = st % ATT2_NS, round = st / ATT2_NS;
+    if (ok) ok = mbar_wait(&sm->full[slot], round & 1);
+    ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sm->abort_flag) == 0);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const i64 kb = lo + (i64)st * ATT2_STAGE_KEYS + 8 * warp;
+      if (kb < hi) {
+        const uint8_t* kp = ring + slot * ATT2_STAGE_BYTES + (8 * warp + (lane >> 2)) * ATT2_HALF + 16 * (lane & 3);
+        int acc[3][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+        const bool kvalid = kb + (lane >> 2) < hi;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          uint4 w = make_uint4(0, 0, 0, 0);
+          if (kvalid) w = *reinterpret_cast<const uint4*>(kp + j * ATT_HD);
+          mma_s8(acc[j], afrag[0], w.x, w.y);
+          mma_s8(acc[j], afrag[1], w.z, w.w);
+        }
+        i64 slo[2], shi[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          slo[c] = (i64)acc[0][c] + shl((i64)acc[1][c], 8) + shl((i64)acc[2][c], 16);
+          shi[c] = (i64)acc[0][2 + c] + shl((i64)acc[1][2 + c], 8) + shl((i64)acc[2][2 + c], 16);
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const i64 mid = __shfl_down_sync(0xffffffffu, slo[c], 16);
+          if (lane < 16) {
+            const i64 raw = slo[c] + shl(mid, 8) + shl(shi[c], 16);
+            const i64 kk = kb + (lane & 3) * 2 + c;
+            if (kk < hi) {
+              scores[(kk - lo) * 4 + (lane >> 2)] = raw;
+              if (kk <= qp_s1) mymax[c] = imax(mymax[c], raw);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->empty[slot]);
+  }
+  {
+    i64 m = imax(mymax[0], mymax[1]);
+    m = imax(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = imax(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    if (lane < 16 && (lane & 3) == 0) sm->wmax[warp][lane >> 2] = m;
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");        // the 8 consumer warps only
+  if (threadIdx.x < 4) {
+    i64 m = ATT_NEG;
+    for (int w = 0; w < ATT_WARPS; ++w) m = imax(m, sm->wmax[w][threadIdx.x]);
+    sm->cmax[threadIdx.x] = m;
+  }
+  cluster.sync();
+
+  // ---- sweep 2 ----
+  const int g2 = lane & 3;
+  i64 mx = ATT_NEG;
+  for (int c = 0; c < CS; ++c) mx = imax(mx, cluster.map_shared_rank(sm->cmax, c)[g2]);
+  const bool gok = g2 < p.M;
+  const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
+  const i64 rowshift = gok ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
+  i64 den = 0;
+  i64 nacc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) nacc[a][b] = 0;
+  const int half = lane >> 4, dg = lane & 15;
+  for (int st = 0; st < nst; ++st) {
+    const int idx = nst + st;
+    const int slot = idx % ATT2_NS, round = idx / ATT2_NS;
+    if (ok) ok = mbar_wait(&sm->full[slot], round & 1);
+    ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sm->abort_flag) == 0);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const i64 kb = lo + (i64)st * ATT2_STAGE_KEYS + 8 * warp;
+      if (kb < hi) {
+        const i64 mykey = kb + (lane >> 2);
+        i64 pv = 0;
+        if (mykey < hi && mykey <= qp2) pv = attn_weight(scores[(mykey - lo) * 4 + g2], mx, rowshift, p.l2e, p.lut);
+        den += pv;
+        sm->pw[warp][lane >> 2][g2] = (int)pv;
+        __syncwarp();
+        const uint8_t* vbase = ring + slot * ATT2_STAGE_BYTES + (8 * warp) * ATT2_HALF + 4 * dg;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int kk = 2 * it + half;
+          if (kb + kk < hi) {
+            const uint8_t* vp = vbase + kk * ATT2_HALF;
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(vp);
+            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(vp + ATT_HD);
+            const uint32_t w2 = *reinterpret_cast<const uint32_t*>(vp + 2 * ATT_HD);
+            const int4 pq = *reinterpret_cast<const int4*>(&sm->pw[warp][kk][0]);
+            const int pg[4] = {pq.x, pq.y, pq.z, pq.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int v = (int)(int8_t)(w0 >> (8 * c)) + ((int)(int8_t)(w1 >> (8 * c)) << 8) +
+                            ((int)(int8_t)(w2 >> (8 * c)) << 16);
+#pragma unroll
+              for (int a = 0; a < 4; ++a) nacc[a][c] += (i64)pg[a] * (i64)v;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->empty[slot]);
+  }
+  if (!ok && lane == 0) atomicAdd(&g_wait_timeouts, 1);
+  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");        // every stage is consumed: the ring is free
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      nacc[a][c] += __shfl_xor_sync(0xffffffffu, nacc[a][c], 16);
+      if (lane < 16) pnum[warp][a][4 * dg + c] = nacc[a][c];
+    }
+  den += __shfl_xor_sync(0xffffffffu, den, 4);
+  den += __shfl_xor_sync(0xffffffffu, den, 8);
+  den += __shfl_xor_sync(0xffffffffu, den, 16);
+  if (lane < 4) sm->pden[warp][lane] = den;
+  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  {
+    const int g = threadIdx.x >> 6, d = threadIdx.x & 63;
+    i64 s = 0;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) s += pnum[w][g][d];
+    sm->cnum[g][d] = s;
+    if (threadIdx.x < 4) {
+      i64 t = 0;
+      for (int w = 0; w < ATT_WARPS; ++w) t += sm->pden[w][threadIdx.x];
+      sm->cden[threadIdx.x] = t;
+    }
+  }
+  cluster.sync();
+  if (rank == 0) {
+    const int g = threadIdx.x >> 6, d = threadIdx.x & 63;
+    if (g < p.M) {
+      i64 s = 0;
+      for (int c = 0; c < CS; ++c) s += cluster.map_shared_rank(&sm->cnum[0][0], c)[g * ATT_HD + d];
+      p.num[(pz * p.M + g) * ATT_HD + d] = s;
+    }
+    if (threadIdx.x < p.M) {
+      i64 t = 0;
+      for (int c = 0; c < CS; ++c) t += cluster.map_shared_rank(sm->cden, c)[threadIdx.x];
+      p.den[pz * p.M + threadIdx.x] = t;
+    }
+  }
+  cluster.sync();
 }
 
 }  // namespace bx

@@ -88,10 +88,10 @@ def attn(args):
     st = torch.cuda.current_stream().cuda_stream
 
     def run():
-        rc = lib.bx_exact_attention(q.data_ptr(), sh.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.stride(0),
+        rc = lib.bx_exact_attention(q.data_ptr(), sh.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0], cache.stride(0),
                                     cache.stride(1), cache.stride(2), bs, bt.data_ptr(), 0, bt.stride(0), nblk, None,
                                     lut.data_ptr(), 387270501, num.data_ptr(), den.data_ptr(), B, HKV, G, HD,
-                                    args.cluster, st)
+                                    args.cluster, args.variant, st)
         nv.check(rc, "bx_exact_attention")
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(2):
@@ -122,6 +122,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=4128)
     ap.add_argument("--cluster", type=int, default=0)
+    ap.add_argument("--variant", type=int, default=0)
     args = ap.parse_args()
     {"gemm": gemm, "attn": attn}[args.what](args)
     if nv.device_status() != 0:

@@ -42,7 +42,8 @@ int bx_clear_device_status(void);
  *   scratch  int8, bx_exact_linear_scratch_bytes(M, K) bytes, 16-byte aligned (activation limb planes)
  *   y      int64 [M, N] contiguous;  flag int32 [1], set to 1 when `checked` and a result lost bits or left
  *          (-2^62, 2^62)
- *   tile_rows  activation rows per CTA tile: 0 = automatic, else one of 16, 32, 48, 64, 80 (no effect on results)
+ *   tile_rows  activation rows per CTA tile: 0 = automatic, else one of 16, 32, 48, 64, 80; -16, -32, -48 select
+ *              that tile size on the persistent kernel (one CTA per SM, overlapped epilogue). No effect on results.
  */
 size_t bx_exact_linear_scratch_bytes(int M, int K);
 int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
@@ -142,13 +143,14 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
  * s <= qpos[r, i]), cache int8 limb planes [nb, HKV, bs, 512], bt [*, nblk] block table (int32, or int64 when
  * bt_is_int64) with row stride sbt, rmap int64 [R] block-table row per request (NULL: identity), lut = 2^-f table,
  * l2e = round(log2(e) * 2^28) for head_dim 64. Outputs num int64 [R, HKV, M, 64], den int64 [R, HKV, M].
- * nblk * bs < 43690. cluster_size: CTAs per (request, head) splitting the keys, 0 = automatic, else 1, 2, 4 or 8
- * (no effect on results).
+ * nb = number of cache blocks. nblk * bs < 43690. cluster_size: CTAs per (request, head) splitting the keys,
+ * 0 = automatic, else 1, 2, 4 or 8. variant: 0 = automatic, 1 = direct-load kernel (any page size / strides),
+ * 2 = TMA-staged kernel (page size 8..64 dividing 64, 16-byte aligned strides). Neither changes a result.
  * Replaces tri_exact_attn.attend (src/bitexact/vllm_plugin/tri_exact_attn.py:138-165). */
-int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t sc_nb,
-                       int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
-                       const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num, int64_t* den, int R,
-                       int HKV, int M, int HD, int cluster_size, void* stream);
+int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
+                       int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
+                       int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
+                       int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream);
 
 /* ---- integer sampler ------------------------------------------------------------------------------------
  * Raw PCG64 words of numpy's default_rng([20261022, seed, t]): keys int64 [n, 2] -> out int64 [n, V].

@@ -30,8 +30,8 @@ def test_argument_contracts_fail_before_touching_a_device():
     lib = nv.lib()
     assert lib.bx_exact_linear(None, 0, None, None, None, None, None, None, None, 0, None, None, None,
                                4, 128, 128, 1, 0, None) == nv.BX_EARG
-    assert lib.bx_exact_attention(None, None, None, None, 0, 0, 0, 16, None, 0, 0, 4, None, None, 0, None, None,
-                                  1, 8, 4, 64, 0, None) == nv.BX_EARG
+    assert lib.bx_exact_attention(None, None, None, None, 1, 0, 0, 0, 16, None, 0, 0, 4, None, None, 0, None, None,
+                                  1, 8, 4, 64, 0, 0, None) == nv.BX_EARG
     assert lib.bx_sample(None, 0, None, None, None, None, 1, 10, 24, None) == nv.BX_EARG
     assert lib.bx_exact_linear_scratch_bytes(3, 64) == 3 * 3 * 64
 

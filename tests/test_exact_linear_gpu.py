@@ -32,7 +32,7 @@ def test_golden_linear_with_residual_and_extreme_shifts():
     z = np.load(os.path.join(GOLD, "exact_ops.npz"))
     dec = {k: z["lin_" + k] for k in ("limbs", "g", "d", "rr", "rc", "rv")}
     fl = _lin(dec)
-    for tile in (None, 16, 32, 48, 64, 80):
+    for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48):      # negative: the persistent kernel
         y, flag = _run(fl, z["lin_q"], z["lin_sh"], True, tile)
         assert np.array_equal(y, z["lin_y"]), tile
         assert flag == bool(z["lin_flag"])
@@ -61,7 +61,26 @@ def test_seeded_shapes_against_oracle(M, N, K):
     sh = rng.randint(-45, -8, M).astype(np.int64)
     want, wflag = ox.linear(q, sh, dec, checked=True)
     fl = _lin(dec)
-    for tile in (None, 16, 80) if M > 16 else (None, 64):
+    for tile in (None, 16, 80, -48) if M > 16 else (None, 64, -16):
+        y, flag = _run(fl, q, sh, True, tile)
+        assert np.array_equal(y, want), (tile, int((y != want).sum()))
+        assert flag == wflag
+
+
+def test_persistent_kernel_many_tiles_per_cta():
+    """More tiles than SMs: every CTA of the persistent kernel walks several tiles through both TMEM buffers."""
+    rng = np.random.RandomState(77)
+    M, N, K = 100, 20480, 256
+    W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
+    q = rng.randint(-(1 << 22), (1 << 22) + 1, (M, K)).astype(np.int64)
+    dec = {"limbs": np.stack([l.astype(np.int8) for l in ox.split_limbs(W, 3)[0]]),
+           "g": rng.randint(-34, -24, N).astype(np.int64), "d": rng.randint(0, 31, N).astype(np.int64),
+           "rr": np.arange(0, N, 97, dtype=np.int64), "rc": rng.randint(0, K, len(range(0, N, 97))).astype(np.int64),
+           "rv": rng.randint(-(1 << 20), 1 << 20, len(range(0, N, 97))).astype(np.int64)}
+    sh = rng.randint(-45, -8, M).astype(np.int64)
+    want, wflag = ox.linear(q, sh, dec, checked=True)
+    fl = _lin(dec)
+    for tile in (-16, -32, -48, None):
         y, flag = _run(fl, q, sh, True, tile)
         assert np.array_equal(y, want), (tile, int((y != want).sum()))
         assert flag == wflag
