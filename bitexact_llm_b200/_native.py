@@ -40,6 +40,7 @@ _SIGNATURES = {
     "bx_pcg_raw": (I, [P, P, I, I, P]),
     "bx_sample_scratch_bytes": (Z, [I, I]),
     "bx_sample": (I, [P, L, P, P, P, P, I, I, I, P]),
+    "bx_sample_shard": (I, [P, L, P, P, P, P, P, I, I, L, I, P]),
 }
 
 

@@ -286,10 +286,13 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
   // TMA-staged kernel when the cache layout allows a tensor map over it, else the direct-load kernel.
   const bool tma_ok = (bs % 8 == 0) && (ATT2_STAGE_KEYS % bs == 0) && sc_bs % 16 == 0 && sc_h % 16 == 0 &&
                       sc_nb % 16 == 0 && sc_bs >= 384 && aligned16(cache);
-  if (variant == 2 && !tma_ok) return BX_EARG;
-  const bool use_tma = variant == 2 || (variant == 0 && tma_ok);
-  const int64_t fixed = use_tma ? (int64_t)ATT2_NS * ATT2_STAGE_BYTES + (int64_t)sizeof(Attn2Small)
-                                : (int64_t)sizeof(AttnShared);
+  if ((variant == 2 || variant == 3) && !tma_ok) return BX_EARG;
+  if (variant < 0 || variant > 3) return BX_EARG;
+  const int kind = variant != 0 ? variant : (tma_ok ? 3 : 1);   // 1 direct loads, 2 TMA-staged, 3 TMA + tcgen05 p.V
+  const bool use_tma = kind >= 2;
+  const int64_t fixed = kind == 3 ? 1024 + (int64_t)ATT3_NS * ATT3_STAGE_BYTES + (int64_t)sizeof(Attn3Small)
+                        : kind == 2 ? (int64_t)ATT2_NS * ATT2_STAGE_BYTES + (int64_t)sizeof(Attn2Small)
+                                    : (int64_t)sizeof(AttnShared);
   const int64_t gran = use_tma ? ATT2_STAGE_KEYS : 8;
   const int64_t cap_limit = (smem_limit - fixed) / 32 / gran * gran;
   int cs = cluster_size;
@@ -297,7 +300,7 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
     cs = 1;
     const int64_t pairs = (int64_t)R * HKV;
     while (cs < ATT_MAXCS && pairs * cs < 2 * 148) cs *= 2;               // fill the SMs
-    while (cs < ATT_MAXCS && (max_keys + cs - 1) / cs > 2048) cs *= 2;    // keep the score buffer small
+    while (cs < ATT_MAXCS && (max_keys + cs - 1) / cs > 704) cs *= 2;     // score buffer small: 3 CTAs per SM
   }
   if (cs != 1 && cs != 2 && cs != 4 && cs != 8) return BX_EARG;
   auto cap_of = [&](int c) { return ((max_keys + c - 1) / c + gran - 1) / gran * gran; };
@@ -319,16 +322,35 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  static bool configured[2] = {false, false};
-  if (!configured[use_tma]) {
-    cudaError_t e = use_tma ? cudaFuncSetAttribute(exact_attention_tma_kernel,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
-                            : cudaFuncSetAttribute(exact_attention_kernel,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
+  static bool configured[4] = {false, false, false, false};
+  if (!configured[kind]) {
+    cudaError_t e = kind == 3 ? cudaFuncSetAttribute(exact_attention_tc_kernel,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
+                    : kind == 2 ? cudaFuncSetAttribute(exact_attention_tma_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
+                                : cudaFuncSetAttribute(exact_attention_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
     if (e != cudaSuccess) return BX_ELAUNCH;
-    configured[use_tma] = true;
+    configured[kind] = true;
   }
-  if (use_tma) {
+  if (kind == 3) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return BX_ELAUNCH;
+    CUtensorMap tk, tv;
+    cuuint64_t dims[4] = {512, (cuuint64_t)bs, (cuuint64_t)HKV, (cuuint64_t)nb};
+    cuuint64_t strides[3] = {(cuuint64_t)sc_bs, (cuuint64_t)sc_h, (cuuint64_t)sc_nb};
+    cuuint32_t boxk[4] = {ATT2_HALF, (cuuint32_t)bs, 1, 1};
+    cuuint32_t boxv[4] = {128, (cuuint32_t)bs, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (fn(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(cache), dims, strides, boxk, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+        fn(&tv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(cache), dims, strides, boxv, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return BX_ELAUNCH;
+    if (cudaLaunchKernelEx(&cfg, exact_attention_tc_kernel, tk, tv, p) != cudaSuccess) return BX_ELAUNCH;
+  } else if (use_tma) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return BX_ELAUNCH;
     CUtensorMap tm;
@@ -337,7 +359,7 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
     cuuint32_t box[4] = {ATT2_HALF, (cuuint32_t)bs, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     if (fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(cache), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return BX_ELAUNCH;
     if (cudaLaunchKernelEx(&cfg, exact_attention_tma_kernel, tm, p) != cudaSuccess) return BX_ELAUNCH;
@@ -365,9 +387,9 @@ static int sample_chunks(int M, int V) {
 
 size_t bx_sample_scratch_bytes(int M, int V) { return (size_t)2 * 8 * (size_t)(M > 0 ? M : 0) * sample_chunks(M, V); }
 
-int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
-              int64_t* tok, int M, int V, int bits, void* stream) {
-  if (!logits || !rows || !lnt || !scratch || !tok || M < 0 || V <= 0 || ld < V) return BX_EARG;
+static int run_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
+                      int64_t* tok, int64_t* omax, int M, int V, int64_t voff, int bits, void* stream) {
+  if (!logits || !rows || !lnt || !scratch || !tok || M < 0 || V <= 0 || ld < V || voff < 0 || M > 65535) return BX_EARG;
   if (M == 0) return BX_OK;
   const int nch0 = sample_chunks(M, V);
   const int ch = ((V + nch0 - 1) / nch0 + 1) / 2 * 2;
@@ -376,9 +398,20 @@ int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int6
   i64* pidx = pmax + (size_t)M * nch0;
   cudaStream_t st = (cudaStream_t)stream;
   sample_part_kernel<<<dim3(nch, M), SAMPLE_THREADS, 0, st>>>((const i64*)logits, ld, (const i64*)rows, (const i64*)lnt,
-                                                              pmax, pidx, V, ch, nch, bits);
-  sample_combine_kernel<<<(M + 127) / 128, 128, 0, st>>>(pmax, pidx, (i64*)tok, M, nch);
+                                                              pmax, pidx, V, ch, nch, bits, (i64)voff);
+  sample_combine_kernel<<<(M + 127) / 128, 128, 0, st>>>(pmax, pidx, (i64*)tok, (i64*)omax, M, nch);
   return launched(2);
+}
+
+int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
+              int64_t* tok, int M, int V, int bits, void* stream) {
+  return run_sample(logits, ld, rows, lnt, scratch, tok, nullptr, M, V, 0, bits, stream);
+}
+
+int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
+                    int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream) {
+  if (!best) return BX_EARG;
+  return run_sample(logits, ld, rows, lnt, scratch, idx, best, M, V_local, v_offset, bits, stream);
 }
 
 int bx_int8_mm(const int8_t* a, const int8_t* w, int32_t* c, int M, int N, int K, int tile_rows, void* stream) {

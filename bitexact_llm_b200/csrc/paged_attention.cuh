@@ -582,3 +582,381 @@ exact_attention_tma_kernel(const __grid_constant__ CUtensorMap tmap, const AttnP
 }
 
 }  // namespace bx
+
+// =====================================================================================================================
+// Tensor-memory variant: as the TMA-staged kernel, but p.V runs on tcgen05 with the accumulators in TMEM.
+//
+// The contraction of p.V is over KEYS, while the cache rows hold DIMS contiguously. tcgen05 reads an "MN-major"
+// int8 operand directly from shared memory, so the staged V rows need no transposition: the A operand is the V tile
+// [32 keys x 128 bytes] (bytes = limb 0 | limb 1 of the 64 dims; a second tile holds limb 2), loaded by TMA with the
+// 128-byte swizzle; the B operand is the tile of p limbs [16 rows = (limb i, query g)] x [32 keys], K-major, written
+// by the consumer warps. D [128 lanes = (V limb, dim)] x [16 columns = (p limb, query)] accumulates in TMEM over
+// ALL keys of the CTA (|sum| <= keys * 2^14 < 2^31) and is read once at the end, so the per-key work of sweep 2
+// is only the weight function and three byte stores.
+namespace bx {
+
+constexpr int ATT3_STAGE_BYTES = ATT2_STAGE_KEYS * 256;        // 16384: [V0|V1] tile 8 KB + [V2|pad] tile 8 KB
+constexpr int ATT3_NS = 3;
+constexpr int ATT3_TMEM_COLS = 32;
+
+struct Attn3Small {
+  i64 cnum[4][ATT_HD];
+  i64 pden[ATT_WARPS][4];
+  i64 cden[4];
+  i64 wmax[ATT_WARPS][4];
+  i64 cmax[4];
+  uint64_t full[ATT3_NS];
+  uint64_t empty_k[ATT3_NS];     // sweep 1: the 8 consumer warps release a stage
+  uint64_t empty_v[ATT3_NS];     // sweep 2: tcgen05.commit releases a stage
+  uint64_t acc_done;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+// K-major, unswizzled operand tile: 8-row core matrices of 16 bytes per row; lbo = bytes between the two 16-byte K
+// chunks, sbo = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t umma_desc_kmajor_plain(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(lbo >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
+// int8 x int8 -> int32, A MN-major, B K-major, M = 128.
+__host__ __device__ constexpr uint32_t umma_idesc_i8_amn(int n) {
+  return umma_idesc_i8(n) | (1u << 15);
+}
+
+__global__ void __launch_bounds__(ATT2_THREADS, 3)
+exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                          const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t att_smem[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att_smem) + 1023) & ~uintptr_t(1023));
+  i64* scores = reinterpret_cast<i64*>(ring + ATT3_NS * ATT3_STAGE_BYTES);   // later, in place: the p-limb tiles
+  Attn3Small* sm = reinterpret_cast<Attn3Small*>(reinterpret_cast<uint8_t*>(scores) + (size_t)p.chunk_cap * 32);
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CS = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  const int64_t pz = blockIdx.x / CS;
+  const int64_t r = pz / p.HKV;
+  const int h = (int)(pz % p.HKV);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  i64 kend = 0;
+  for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[r * p.M + g] + 1);
+  kend = imin(kend, (i64)p.nblk * p.bs);
+  const i64 per = (kend + CS - 1) / CS;
+  i64 chunk = (per + ATT2_STAGE_KEYS - 1) / ATT2_STAGE_KEYS * ATT2_STAGE_KEYS;
+  if (chunk > p.chunk_cap) chunk = p.chunk_cap;
+  const i64 lo = imin((i64)rank * chunk, kend);
+  const i64 hi = imin(lo + chunk, kend);
+  const int nst = (int)((hi - lo + ATT2_STAGE_KEYS - 1) / ATT2_STAGE_KEYS);
+  const i64 brow = p.rmap ? p.rmap[r] : r;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ATT3_NS; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty_k[s], ATT_WARPS);
+      mbar_init(&sm->empty_v[s], 1);
+    }
+    mbar_init(&sm->acc_done, 1);
+    sm->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(&sm->tmem_base, ATT3_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+
+  if (warp == ATT_WARPS) {
+    // ---------------- producer warp ----------------
+    // Block-table entries are fetched 32 pages at a time (one per lane) and handed out by shuffles, so that issuing a
+    // stage never waits for a global load.
+    const int pages_per_stage = ATT2_STAGE_KEYS / p.bs;
+    const i64 pg0 = lo / p.bs;
+    const int npg = (int)((hi - lo + p.bs - 1) / p.bs);
+    auto load_bt = [&](int block) -> i64 {
+      const int rel = block * 32 + lane;
+      if (rel >= npg) return 0;
+      return p.bt64 ? reinterpret_cast<const i64*>(p.bt)[brow * p.sbt + pg0 + rel]
+                    : (i64) reinterpret_cast<const int32_t*>(p.bt)[brow * p.sbt + pg0 + rel];
+    };
+    int cur_block = 0;
+    i64 my_bt = load_bt(0);
+    bool ok = true;
+    for (int idx = 0; idx < 2 * nst; ++idx) {
+      if (idx == nst) cluster_arrive();
+      const int sweep = idx >= nst, st = idx - sweep * nst;
+      const int slot = idx % ATT3_NS;
+      const int rel0 = st * pages_per_stage;                        // first page of the stage (a stage never straddles
+      if (rel0 / 32 != cur_block) {                                 // a block of 32 pages: pages_per_stage divides 32)
+        cur_block = rel0 / 32;
+        my_bt = load_bt(cur_block);
+      }
+      const i64 blk = __shfl_sync(0xffffffffu, my_bt, (rel0 + lane) & 31);
+      const int prev = idx - ATT3_NS;                               // previous use of this slot
+      if (ok && prev >= 0) {
+        if (prev < nst) {
+          ok = mbar_wait(&sm->empty_k[slot], (prev / ATT3_NS) & 1);
+        } else {                                                    // ordinal of `prev` among this slot's sweep-2 uses
+          const int ord = (prev + ATT3_NS - 1 - slot) / ATT3_NS - (nst + ATT3_NS - 1 - slot) / ATT3_NS;
+          ok = mbar_wait(&sm->empty_v[slot], ord & 1);
+        }
+      }
+      if (!ok) continue;
+      const i64 key0 = lo + (i64)st * ATT2_STAGE_KEYS;
+      int npages = (int)((hi - key0 + p.bs - 1) / p.bs);
+      if (npages > pages_per_stage) npages = pages_per_stage;
+      if (lane == 0)
+        mbar_arrive_expect_tx(&sm->full[slot], (uint32_t)(npages * p.bs * (sweep ? 256 : ATT2_HALF)));
+      __syncwarp();
+      if (lane < npages) {
+        uint8_t* st_base = ring + slot * ATT3_STAGE_BYTES;
+        if (!sweep) {
+          tma_load_4d(st_base + lane * p.bs * ATT2_HALF, &tmap_k, &sm->full[slot], 0, 0, h, (int)blk);
+        } else {
+          tma_load_4d(st_base + lane * p.bs * 128, &tmap_v, &sm->full[slot], 192, 0, h, (int)blk);
+          tma_load_4d(st_base + 8192 + lane * p.bs * 128, &tmap_v, &sm->full[slot], 320, 0, h, (int)blk);
+        }
+      }
+    }
+    if (nst == 0) cluster_arrive();
+    if (!ok && lane == 0) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
+    cluster_wait();
+    cluster.sync();
+    cluster.sync();
+    __syncthreads();                                               // TMEM release point of the CTA
+    return;
+  }
+
+  // ---------------- consumer warps ----------------
+  uint32_t afrag[2][4];
+  {
+    const int row_lo = lane >> 2;
+    const int g = row_lo & 3;
+    const int limb_lo = row_lo >> 2;
+    const bool hi_used = row_lo < 4;
+    const int32_t* qrow = p.q + (pz * p.M + g) * ATT_HD;
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int d0 = 16 * (lane & 3) + 4 * (2 * t + half);
+        uint32_t wl = 0, wh = 0;
+        if (g < p.M) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            int v = qrow[d0 + b];
+            const int l0 = split8(v), l1 = split8(v), l2 = split8(v);
+            wl |= (uint32_t)((limb_lo ? l1 : l0) & 255) << (8 * b);
+            wh |= (uint32_t)(l2 & 255) << (8 * b);
+          }
+        }
+        afrag[t][2 * half] = wl;
+        afrag[t][2 * half + 1] = hi_used ? wh : 0u;
+      }
+  }
+
+  bool ok = true;
+  // ---- sweep 1: scores (as the TMA-staged kernel) ----
+  i64 mymax[2] = {ATT_NEG, ATT_NEG};
+  const i64 qp_s1 = (lane < 16 && (lane >> 2) < p.M) ? p.qpos[r * p.M + (lane >> 2)] : -1;
+  for (int st = 0; st < nst; ++st) {
+    const int slot = st % ATT3_NS, round = st / ATT3_NS;
+    if (ok) ok = mbar_wait(&sm->full[slot], round & 1);
+    ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sm->abort_flag) == 0);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const i64 kb = lo + (i64)st * ATT2_STAGE_KEYS + 8 * warp;
+      if (kb < hi) {
+        const uint8_t* kp = ring + slot * ATT3_STAGE_BYTES + (8 * warp + (lane >> 2)) * ATT2_HALF + 16 * (lane & 3);
+        int acc[3][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+        const bool kvalid = kb + (lane >> 2) < hi;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          uint4 w = make_uint4(0, 0, 0, 0);
+          if (kvalid) w = *reinterpret_cast<const uint4*>(kp + j * ATT_HD);
+          mma_s8(acc[j], afrag[0], w.x, w.y);
+          mma_s8(acc[j], afrag[1], w.z, w.w);
+        }
+        i64 slo[2], shi[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          slo[c] = (i64)acc[0][c] + shl((i64)acc[1][c], 8) + shl((i64)acc[2][c], 16);
+          shi[c] = (i64)acc[0][2 + c] + shl((i64)acc[1][2 + c], 8) + shl((i64)acc[2][2 + c], 16);
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const i64 mid = __shfl_down_sync(0xffffffffu, slo[c], 16);
+          if (lane < 16) {
+            const i64 raw = slo[c] + shl(mid, 8) + shl(shi[c], 16);
+            const i64 kk = kb + (lane & 3) * 2 + c;
+            if (kk < hi) {
+              scores[(kk - lo) * 4 + (lane >> 2)] = raw;
+              if (kk <= qp_s1) mymax[c] = imax(mymax[c], raw);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->empty_k[slot]);
+  }
+  {
+    i64 m = imax(mymax[0], mymax[1]);
+    m = imax(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = imax(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    if (lane < 16 && (lane & 3) == 0) sm->wmax[warp][lane >> 2] = m;
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  if (threadIdx.x < 4) {
+    i64 m = ATT_NEG;
+    for (int w = 0; w < ATT_WARPS; ++w) m = imax(m, sm->wmax[w][threadIdx.x]);
+    sm->cmax[threadIdx.x] = m;
+  }
+  cluster.sync();
+
+  // ---- sweep 2, phase A: weights of every key of this CTA, written in place of the scores as p-limb tiles ----
+  // A group of 32 keys owns 1024 bytes of the score buffer; one warp reads its 128 scores (4 per lane), then
+  // overwrites the first 512 bytes with the K-major tile [16 rows (limb, query)] x [32 keys].
+  const int g2 = lane & 3;
+  i64 mx = ATT_NEG;
+  for (int c = 0; c < CS; ++c) mx = imax(mx, cluster.map_shared_rank(sm->cmax, c)[g2]);
+  const bool gok = g2 < p.M;
+  const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
+  const i64 rowshift = gok ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
+  i64 den = 0;
+  const int ngroups = (int)((hi - lo + 31) / 32);
+  for (int grp = warp; grp < ngroups; grp += ATT_WARPS) {
+    i64 sc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sc[j] = scores[((i64)grp * 32 + 8 * j + (lane >> 2)) * 4 + g2];
+    __syncwarp();
+    uint8_t* pt = reinterpret_cast<uint8_t*>(scores) + (size_t)grp * 1024;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kl = 8 * j + (lane >> 2);
+      const i64 key = lo + (i64)grp * 32 + kl;
+      i64 pv = 0;
+      if (key < hi && key <= qp2) pv = attn_weight(sc[j], mx, rowshift, p.l2e, p.lut);
+      den += pv;
+      int pr = (int)pv;
+      const int off = (kl >> 4) * 256 + (kl & 15) + g2 * 16;
+      pt[off] = (uint8_t)split8(pr);                                // row g      (limb 0)
+      pt[off + 64] = (uint8_t)split8(pr);                           // row 4 + g  (limb 1)
+      pt[off + 128] = (uint8_t)split8(pr);                          // row 8 + g  (limb 2)
+    }
+  }
+  fence_proxy_async_smem();
+  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+
+  // ---- sweep 2, phase B: one thread streams the staged V tiles through tcgen05 ----
+  constexpr uint32_t IDESC = umma_idesc_i8_amn(16);
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < nst; ++st) {
+      const int idx = nst + st;
+      const int slot = idx % ATT3_NS, round = idx / ATT3_NS;
+      if (ok) ok = mbar_wait(&sm->full[slot], round & 1);
+      ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sm->abort_flag) == 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t vbase = smem_u32(ring + slot * ATT3_STAGE_BYTES);
+#pragma unroll
+      for (int kg = 0; kg < 2; ++kg) {
+        const int grp = 2 * st + kg;
+        if (grp < ngroups) {
+          const uint64_t bdesc = umma_desc_kmajor_plain(smem_u32(scores) + grp * 1024, 256, 128);
+          const uint32_t accum = grp > 0 ? 1u : 0u;
+          umma_i8(tmem, umma_desc_sw128(vbase + kg * 4096), bdesc, IDESC, accum);
+          umma_i8(tmem + 16, umma_desc_sw128(vbase + 8192 + kg * 4096), bdesc, IDESC, accum);
+        }
+      }
+      umma_commit(&sm->empty_v[slot]);
+      if (st == nst - 1) umma_commit(&sm->acc_done);
+    }
+    if (!ok) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
+  }
+  __syncwarp();
+
+  den += __shfl_xor_sync(0xffffffffu, den, 4);
+  den += __shfl_xor_sync(0xffffffffu, den, 8);
+  den += __shfl_xor_sync(0xffffffffu, den, 16);
+  if (lane < 4) sm->pden[warp][lane] = den;
+
+  // ---- read the accumulators: lane L < 64 holds (V limb 0, dim L) and, in the second tile, (V limb 2, dim L);
+  //      lane 64 + L holds (V limb 1, dim L). Column 4 i + g = (p limb i, query g). ----
+  i64 part[4] = {0, 0, 0, 0};
+  if (warp < 4) {
+    bool done = ok && nst > 0;
+    if (done) done = mbar_wait(&sm->acc_done, 0);
+    done = done && (*reinterpret_cast<volatile uint32_t*>(&sm->abort_flag) == 0);
+    done = __all_sync(0xffffffffu, done);
+    if (done) {
+      tc_fence_after();
+      uint32_t d01[16], d2[16];
+      const uint32_t tb = tmem + ((uint32_t)(warp * 32) << 16);
+      tmem_ld16(tb, d01);
+      tmem_ld16(tb + 16, d2);
+      tmem_ld_wait();
+      const int vl = warp >= 2 ? 1 : 0;                            // V limb of the first tile on this lane
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        i64 a = (i64)(int32_t)d01[g] + shl((i64)(int32_t)d01[4 + g], 8) + shl((i64)(int32_t)d01[8 + g], 16);
+        a = shl(a, 8 * vl);
+        if (warp < 2) {
+          const i64 b = (i64)(int32_t)d2[g] + shl((i64)(int32_t)d2[4 + g], 8) + shl((i64)(int32_t)d2[8 + g], 16);
+          a += shl(b, 16);
+        }
+        part[g] = a;
+      }
+    }
+  }
+  tc_fence_before();
+  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  if (warp < 2) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) sm->cnum[g][warp * 32 + lane] = part[g];
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  if (warp >= 2 && warp < 4) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) sm->cnum[g][(warp - 2) * 32 + lane] += part[g];
+  }
+  if (threadIdx.x < 4) {
+    i64 t = 0;
+    for (int w = 0; w < ATT_WARPS; ++w) t += sm->pden[w][threadIdx.x];
+    sm->cden[threadIdx.x] = t;
+  }
+  cluster.sync();
+  if (rank == 0) {
+    const int g = threadIdx.x >> 6, d = threadIdx.x & 63;
+    if (g < p.M) {
+      i64 s = 0;
+      for (int c = 0; c < CS; ++c) s += cluster.map_shared_rank(&sm->cnum[0][0], c)[g * ATT_HD + d];
+      p.num[(pz * p.M + g) * ATT_HD + d] = s;
+    }
+    if (threadIdx.x < p.M) {
+      i64 t = 0;
+      for (int c = 0; c < CS; ++c) t += cluster.map_shared_rank(sm->cden, c)[threadIdx.x];
+      p.den[pz * p.M + threadIdx.x] = t;
+    }
+  }
+  cluster.sync();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, ATT3_TMEM_COLS);
+  }
+}
+
+}  // namespace bx

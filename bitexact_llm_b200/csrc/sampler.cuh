@@ -152,7 +152,7 @@ pcg_raw_kernel(const i64* __restrict__ keys, i64* __restrict__ out, int V, int r
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_part_kernel(const i64* __restrict__ logits, int64_t ld, const i64* __restrict__ rows,
                    const i64* __restrict__ lnt, i64* __restrict__ pmax, i64* __restrict__ pidx, int V, int ch,
-                   int nch, int bits) {
+                   int nch, int bits, i64 voff) {
   __shared__ i64 smax[SAMPLE_THREADS / 32], sidx[SAMPLE_THREADS / 32];
   const int64_t row = blockIdx.y;
   const int chunk = blockIdx.x;
@@ -162,18 +162,18 @@ sample_part_kernel(const i64* __restrict__ logits, int64_t ld, const i64* __rest
   const int run = (ch + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
   const int64_t e0 = c0 + (int64_t)threadIdx.x * run;
   const int64_t e1 = e0 + run < c1 ? e0 + run : c1;
-  i64 best = (i64)0x8000000000000000ull, bidx = V;
-  const i64* lr = logits + row * ld;
+  i64 best = (i64)0x8000000000000000ull, bidx = 0x7fffffffffffffffll;
+  const i64* lr = logits + row * ld;     // local columns; vocabulary index = voff + column
   if (e0 < e1) {
     if (tn == 0) {
       for (int64_t e = e0; e < e1; ++e) {
         const i64 v = lr[e];
-        if (v > best) { best = v; bidx = e; }
+        if (v > best) { best = v; bidx = voff + e; }
       }
     } else {
       u128 st, inc;
       pcg_seed((u64)rows[4 * row], (u64)rows[4 * row + 1], st, inc);
-      st = pcg_advance(st, inc, (u64)e0);
+      st = pcg_advance(st, inc, (u64)(voff + e0));
       const u64 dv = (u64)(2 * tn);
       const u64 inv = ~0ull / dv;
       for (int64_t e = e0; e < e1; ++e) {
@@ -184,7 +184,7 @@ sample_part_kernel(const i64* __restrict__ logits, int64_t ld, const i64* __rest
         const u64 qd = uqr_recip((u64)iabs(a), dv, inv, rem);
         const i64 fq = a < 0 ? -(i64)qd - (rem != 0 ? 1 : 0) : (i64)qd;
         const i64 v = fq + g;
-        if (v > best) { best = v; bidx = e; }
+        if (v > best) { best = v; bidx = voff + e; }
       }
     }
   }
@@ -206,8 +206,9 @@ sample_part_kernel(const i64* __restrict__ logits, int64_t ld, const i64* __rest
   }
 }
 
+// tok[row] = first index of the maximum over the chunks; omax (may be null) receives the maximum itself.
 __global__ void sample_combine_kernel(const i64* __restrict__ pmax, const i64* __restrict__ pidx,
-                                      i64* __restrict__ tok, int M, int nch) {
+                                      i64* __restrict__ tok, i64* __restrict__ omax, int M, int nch) {
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= M) return;
   i64 best = pmax[(int64_t)row * nch], bidx = pidx[(int64_t)row * nch];
@@ -216,6 +217,7 @@ __global__ void sample_combine_kernel(const i64* __restrict__ pmax, const i64* _
     if (v > best || (v == best && i < bidx)) { best = v; bidx = i; }
   }
   tok[row] = bidx;
+  if (omax) omax[row] = best;
 }
 
 }  // namespace bx

@@ -1,0 +1,115 @@
+"""Multi-GPU layout of the hot path: one process per GPU, `torch.distributed` for the plumbing.
+
+Two shardings, both exact (no value is ever reduced in floating point, so every GPU count gives the same bits):
+
+* sequence sharding  - every rule of the engine is row-local, so rank r simply owns a contiguous block of the
+                       batch (its own KV cache, no communication).
+* column sharding    - a large-N projection (LM head, gate/up) is split by OUTPUT columns: y[m, n] depends only on
+                       row m and weight row n. Each rank computes y[:, n0:n1]; one all-gather of the int64 outputs
+                       rebuilds y. The sampler needs no full row at all: each rank reduces its shard to a
+                       (max, first index) pair per row and the pairs are all-gathered.
+
+The reference is single-GPU (README "TP = 1, PP = 1"); these helpers are the new part the multi-GPU configs need.
+The collective wrappers take any process group (NCCL on GPUs; the unit tests run them on CPU tensors over gloo).
+"""
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n, world, rank):
+    """Contiguous near-equal split of n items: [lo, hi) of `rank` (the first n % world ranks get one more)."""
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def column_bounds(N, world, rank, align=1):
+    """[n0, n1) of `rank` when N output columns are split evenly (N % (world * align) must be 0)."""
+    if N % (world * align):
+        raise ValueError(f"{N} columns do not split over {world} ranks in multiples of {align}")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_linear_constants(c, name, n0, n1):
+    """The constants of weight rows [n0, n1) of linear `name` (reference key layout), residual rows re-based."""
+    rr = c[f"{name}.rr"]
+    keep = (rr >= n0) & (rr < n1)
+    return {"limbs": c[f"{name}.limbs"][:, n0:n1].contiguous(), "g": c[f"{name}.g"][n0:n1].contiguous(),
+            "d": c[f"{name}.d"][n0:n1].contiguous(), "rr": rr[keep] - n0, "rc": c[f"{name}.rc"][keep],
+            "rv": c[f"{name}.rv"][keep]}
+
+
+def gather_columns(y_local, group=None):
+    """y_local int [M, n_local] on every rank (equal shapes) -> y [M, world * n_local] (rank-major columns)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return y_local
+    y_local = y_local.contiguous()
+    M, nl = y_local.shape
+    out = torch.empty((world * M, nl), dtype=y_local.dtype, device=y_local.device)      # rank-major blocks of rows
+    dist.all_gather_into_tensor(out, y_local, group=group)
+    return out.view(world, M, nl).permute(1, 0, 2).reshape(M, world * nl)
+
+
+def gather_rows(x_local, group=None):
+    """x_local [m_local, ...] (equal m_local on every rank) -> [world * m_local, ...] in rank order."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return x_local
+    x_local = x_local.contiguous()
+    out = torch.empty((world * x_local.shape[0],) + tuple(x_local.shape[1:]), dtype=x_local.dtype,
+                      device=x_local.device)
+    dist.all_gather_into_tensor(out, x_local, group=group)
+    return out
+
+
+def combine_argmax(best, idx, group=None):
+    """Per-row (shard maximum, first global index) pairs of every rank -> the row's first argmax over all shards:
+    the larger value wins, then the smaller index."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return idx
+    pair = torch.stack([best, idx], 1).contiguous()                       # [M, 2] int64
+    allp = torch.empty((world * pair.shape[0], 2), dtype=pair.dtype, device=pair.device)
+    dist.all_gather_into_tensor(allp, pair, group=group)
+    allp = allp.view(world, pair.shape[0], 2)
+    b, i = allp[..., 0], allp[..., 1]                                     # [world, M]
+    top = b.amax(0, keepdim=True)
+    big = torch.iinfo(torch.int64).max
+    return torch.where(b == top, i, torch.full_like(i, big)).amin(0)
+
+
+class ShardedHead:
+    """Column-sharded LM head + sampler: rank r holds vocabulary rows [v0, v1) of the LM head; logits never leave
+    the shard unless `full_logits` is called (test / hashing mode)."""
+
+    def __init__(self, c, device, group=None):
+        from .exact.model import Lin
+        from .vllm_plugin.exact_gemm import FusedLin
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        V = c["lm.limbs"].shape[1]
+        self.v0, self.v1 = column_bounds(V, self.world, self.rank)
+        self.lin = FusedLin(Lin(shard_linear_constants(c, "lm", self.v0, self.v1), None, device))
+
+    def local_logits(self, q, sh, flag):
+        return self.lin(q, sh, flag, True)
+
+    def full_logits(self, q, sh, flag):
+        return gather_columns(self.local_logits(q, sh, flag), self.group)
+
+    def sample(self, q, sh, flag, rows, lnt, fr=24):
+        """rows int64 [M, 4] = (seed, t, tn, td) on the device -> tokens int64 [M] (identical on every rank)."""
+        from . import _native as nv
+        lg = self.local_logits(q, sh, flag)
+        M, Vl = lg.shape
+        lib = nv.lib()
+        best = torch.empty(M, dtype=torch.long, device=lg.device)
+        idx = torch.empty(M, dtype=torch.long, device=lg.device)
+        scratch = torch.empty(max(1, lib.bx_sample_scratch_bytes(M, Vl)), dtype=torch.uint8, device=lg.device)
+        rc = lib.bx_sample_shard(lg.data_ptr(), lg.stride(0), rows.data_ptr(), lnt.data_ptr(), scratch.data_ptr(),
+                                 best.data_ptr(), idx.data_ptr(), M, Vl, self.v0, fr, nv.stream())
+        nv.check(rc, "bx_sample_shard")
+        return combine_argmax(best, idx, self.group)

@@ -145,7 +145,8 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
  * l2e = round(log2(e) * 2^28) for head_dim 64. Outputs num int64 [R, HKV, M, 64], den int64 [R, HKV, M].
  * nb = number of cache blocks. nblk * bs < 43690. cluster_size: CTAs per (request, head) splitting the keys,
  * 0 = automatic, else 1, 2, 4 or 8. variant: 0 = automatic, 1 = direct-load kernel (any page size / strides),
- * 2 = TMA-staged kernel (page size 8..64 dividing 64, 16-byte aligned strides). Neither changes a result.
+ * 2 = TMA-staged kernel, 3 = TMA-staged kernel with p.V on tcgen05 / TMEM (2 and 3: page size 8..64 dividing
+ * 64, 16-byte aligned strides). None of them changes a result.
  * Replaces tri_exact_attn.attend (src/bitexact/vllm_plugin/tri_exact_attn.py:138-165). */
 int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
                        int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
@@ -162,9 +163,17 @@ int bx_pcg_raw(const int64_t* keys, int64_t* out, int n, int V, void* stream);
  * lnt = ln table int64 [65537] at 40 bits; scratch: bx_sample_scratch_bytes(M, V) bytes; tok int64 [M].
  * Replaces sampler.integer_sample / tri_logits.first_argmax (src/bitexact/vllm_plugin/sampler.py:57-88,
  * vllm_plugin/tri_logits.py:77-100) = sampling.sample(gumbel(raw_rows(.))) (src/bitexact/sampling.py:50-67). */
+/* bx_sample_shard: the same pass over a COLUMN SHARD of the logits (vocabulary entries v_offset .. v_offset +
+ * V_local - 1; the noise of entry i is word i of the row's PCG64 stream whatever the shard). Writes per row the
+ * shard's maximum `best` and its first global index `idx`; the caller all-gathers the pairs and keeps, per row,
+ * the larger `best`, then the smaller `idx` - the rule of the reference's chunk combine
+ * (src/bitexact/vllm_plugin/tri_sample.py:275-290). Has no single-kernel counterpart in the reference, which
+ * never shards the vocabulary. */
 size_t bx_sample_scratch_bytes(int M, int V);
 int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
               int64_t* tok, int M, int V, int bits, void* stream);
+int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
+                    int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream);
 
 #ifdef __cplusplus
 }

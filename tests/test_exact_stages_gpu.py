@@ -136,7 +136,7 @@ def test_attention_golden_all_cluster_sizes():
     R = z["attn_q"].shape[0]
     args = (T(z["attn_q"], torch.int32), T(z["attn_sh"]), T(z["attn_qpos"]), T(z["attn_cache"]), T(z["attn_bt"]),
             torch.arange(R, device="cuda"), lut, ox.L2E28)
-    for variant in (1, 2):                                   # direct-load kernel, TMA-staged kernel
+    for variant in (1, 2, 3):                                # direct-load, TMA-staged, TMA + tcgen05 p.V
         for ns in (None, 1, 2, 5, 64):
             num, den = tri_exact_attn.attend(*args, nsplit=ns, variant=variant)
             assert np.array_equal(N_(num), z["attn_num"]) and np.array_equal(N_(den), z["attn_den"]), (variant, ns)
@@ -169,7 +169,7 @@ def test_attention_seeded_random_masks_and_padding(lim):
         q = rng.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, M, HD)).astype(np.int64)
         sh = rng.randint(-40, -10, (R, HKV, M)).astype(np.int64)
         wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, rmap, lut_np)
-        for variant, ns in ((1, None), (1, 8), (2, None), (2, 1), (2, 4), (2, 8)):
+        for variant, ns in ((1, None), (1, 8), (2, None), (2, 4), (3, None), (3, 1), (3, 4), (3, 8)):
             num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), T(rmap), lut,
                                              ox.L2E28, nsplit=ns, variant=variant)
             assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), (R, M, P, variant, ns)
@@ -188,7 +188,7 @@ def test_attention_bound_stress_equal_scores_at_limb_extremes():
     q = np.full((1, HKV, 4, HD), 1 << 22, dtype=np.int64)
     sh = np.full((1, HKV, 4), -30, dtype=np.int64)
     qpos = np.full((1, 4), S - 1, dtype=np.int64)
-    for variant in (1, 2):
+    for variant in (1, 2, 3):
         num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), None,
                                          T(ox.exp2_table()), ox.L2E28, variant=variant)
         assert int(den.min()) == S << 22 and int(num.min()) == (S << 22) * 8355711 and int(num.max()) == int(num.min())
@@ -225,3 +225,31 @@ def test_pcg_words_and_sampler():
         want.append(int(osamp.sample(logits[r:r + 1], tn, td, g)[0]))
     tok = sampler.integer_sample(T(logits), seeds, ts, temps, lnt)
     assert N_(tok).tolist() == want and want[3] == 777
+
+
+def test_sharded_sampler_pairs_combine_to_the_full_row_token():
+    """Eight vocabulary shards, each reduced to (max, first global index) by bx_sample_shard, combine to exactly the
+    token bx_sample picks on the full row (greedy and T = 0.7; a tie across shards resolves to the first index)."""
+    from bitexact_llm_b200 import _native as nv
+    from bitexact_llm_b200.exact.consts import ln_table
+    from bitexact_llm_b200.vllm_plugin import sampler
+    lib = nv.lib()
+    V, M, W = 128256, 6, 8
+    g = torch.Generator(device="cuda").manual_seed(4)
+    li = torch.randint(-(25 << 24), 25 << 24, (M, V), device="cuda", generator=g)
+    li[2, 100] = li[2, 90000] = li[2].max() + 7
+    rows = torch.tensor([[r, 3 + r, (0 if r % 2 else 7), (1 if r % 2 else 10)] for r in range(M)], device="cuda")
+    lnt = ln_table(device="cuda")
+    want = sampler.sample_rows(li, rows, lnt)
+    per = V // W
+    best = torch.empty(W, M, dtype=torch.long, device="cuda")
+    idx = torch.empty(W, M, dtype=torch.long, device="cuda")
+    scratch = torch.empty(lib.bx_sample_scratch_bytes(M, per), dtype=torch.uint8, device="cuda")
+    for s in range(W):
+        loc = li[:, s * per:(s + 1) * per]                              # a strided view: ld = V
+        rc = lib.bx_sample_shard(loc.data_ptr(), loc.stride(0), rows.data_ptr(), lnt.data_ptr(), scratch.data_ptr(),
+                                 best[s].data_ptr(), idx[s].data_ptr(), M, per, s * per, 24, nv.stream())
+        assert rc == 0
+    top = best.amax(0, keepdim=True)
+    tok = torch.where(best == top, idx, torch.full_like(idx, 1 << 62)).amin(0)
+    assert torch.equal(tok, want) and int(tok[2]) in (100, int(want[2]))
