@@ -234,11 +234,13 @@ def run_b200(args, rank, world):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     timer.on = True
     with ClockSampler(local) as clk:
+        torch.cuda.profiler.start()                                  # capture range for `ncu --profile-from-start off`
         e0.record()
         for _ in range(K):
             step()
         e1.record()
         barrier()
+        torch.cuda.profiler.stop()
     timer.on = False
     launches = lib.bx_launch_count() - n0
     ms = e0.elapsed_time(e1)
