@@ -69,6 +69,67 @@ class Session:
         return x
 
 
+class GraphDecoder:
+    """The decode step (LM head, sampler, one forward over the batch) captured once in a CUDA graph and replayed:
+    no Python or launch overhead per kernel. The step's state lives in static device tensors: the residual rows,
+    the sampler rows (seed, t, tn, td) whose t advances on the device, the session's lengths."""
+
+    def __init__(self, ses, rows, h, warmup=2):
+        self.ses, self.eng = ses, ses.eng
+        self.rows = rows
+        self.h = h.clone()
+        self.tok = torch.zeros(ses.B, dtype=torch.long, device=h.device)
+        for _ in range(warmup):                     # configures every kernel and fills the caching allocator
+            self._body()
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._body()
+
+    def _body(self):
+        lg = self.eng.logits(self.h)
+        tok = sampler.sample_rows(lg, self.rows, self.eng.ln, self.eng.FR)
+        self.h.copy_(self.ses.step(tok))
+        self.rows[:, 1] += 1
+        self.tok.copy_(tok)
+
+    def step(self):
+        """Runs one captured step; returns the sampled tokens (a static tensor, overwritten by the next step)."""
+        self.graph.replay()
+        return self.tok
+
+
+class GraphHostStep:
+    """One decode step driven from the host, captured in a CUDA graph: the caller copies this step's token ids,
+    positions and sampler rows into the static input tensors (`tok_in`, `pos_in`, `rows_in`), replays, and reads
+    the sampled tokens from `tok`. Forward, LM head and sampler run inside the graph."""
+
+    def __init__(self, ses, rows):
+        self.ses, self.eng = ses, ses.eng
+        dev = rows.device
+        self.tok_in = torch.zeros(ses.B, dtype=torch.long, device=dev)
+        self.pos_in = ses.lens.clone()
+        self.rows_in = rows.clone()
+        self.tok = torch.zeros(ses.B, dtype=torch.long, device=dev)
+        keep = ses.lens.clone()
+        for _ in range(2):
+            self._body()
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._body()
+        ses.lens.copy_(keep)                         # warm-up and capture advanced the device-side lengths
+
+    def _body(self):
+        x = self.ses.step(self.tok_in, self.pos_in)
+        lg = self.eng.logits(x)
+        self.tok.copy_(sampler.sample_rows(lg, self.rows_in, self.eng.ln, self.eng.FR))
+
+    def step(self):
+        self.graph.replay()
+        return self.tok
+
+
 @torch.no_grad()
 def generate(eng, prompts, max_new, tn=0, td=1, seeds=None, hashes=True, max_len=None, perm_seed=None, lens=None):
     """prompts int64 [B, P] (right-padded, true lengths `lens`); generated token t of sequence b uses the noise

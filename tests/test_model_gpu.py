@@ -66,3 +66,34 @@ def test_prompt_chunking_does_not_change_bits(tiny):
         outs.append(eng.logits(ses.prefill(ids, lens, chunk_rows=chunk)))
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     eng.check()
+
+
+def test_cuda_graph_decode_equals_eager(tiny):
+    """The captured decode step (LM head + sampler + forward) replays to the same tokens and residual rows as the
+    kernel-by-kernel loop."""
+    from bitexact_llm_b200.decode import GraphDecoder, Session
+    from bitexact_llm_b200.vllm_plugin import sampler
+    eng, z, prompts = tiny
+    ids, lens = _padded(prompts)
+
+    def fresh():
+        ses = Session(eng, 3, 64)
+        h = ses.prefill(ids, lens)
+        rows = torch.tensor([[b, 0, 7, 10] for b in range(3)], device="cuda")
+        return ses, h, rows
+
+    ses, h, rows = fresh()
+    eager = []
+    for t in range(6):
+        tok = sampler.sample_rows(eng.logits(h), rows, eng.ln, eng.FR)
+        rows[:, 1] += 1
+        h = ses.step(tok)
+        eager.append(tok.clone())
+    ses2, h2, rows2 = fresh()
+    dec = GraphDecoder(ses2, rows2, h2, warmup=0)
+    for t in range(6):
+        assert torch.equal(dec.step(), eager[t]), t
+    assert torch.equal(dec.h, h)
+    for b in range(3):
+        assert [int(e[b]) for e in eager] == z[f"p{b}_t07_tok"][:6].tolist()
+    eng.check()
