@@ -37,6 +37,13 @@ _SIGNATURES = {
     "bx_exact_attn_out": (I, [P, P, P, P, P, I, I, I, P]),
     "bx_exact_silu_quant": (I, [P, P, P, P, P, P, I, I, P]),
     "bx_exact_attention": (I, [P, P, P, P, L, L, L, L, I, P, I, L, I, P, P, L, P, P, I, I, I, I, I, I, P]),
+    "bx_int8_attention": (I, [P, P, P, L, L, L, L, I, P, I, L, I, P, P, P, P, I, I, I, I, I, I, P]),
+    "bx_int8_norm": (I, [I, P, P, P, P, P, P, P, P, P, I, I, I, P]),
+    "bx_int8_qkv": (I, [P, P, P, P, P, P, L, L, L, I, P, P, P, I, I, I, I, P]),
+    "bx_int8_attn_out": (I, [P, P, P, P, P, I, I, I, P]),
+    "bx_int8_silu_quant": (I, [P, P, P, P, P, P, I, I, P]),
+    "bx_int8_flag_end": (I, [P, P, I, P]),
+    "bx_int8_post": (I, [P, P, L, P, P, P, P, I, I, I, P]),
     "bx_pcg_raw": (I, [P, P, I, I, P]),
     "bx_sample_scratch_bytes": (Z, [I, I]),
     "bx_sample": (I, [P, L, P, P, P, P, I, I, I, P]),

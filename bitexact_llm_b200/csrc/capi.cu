@@ -8,6 +8,7 @@
 #include "../../include/bitexact_b200.h"
 #include "exact_linear.cuh"
 #include "int8_linear.cuh"
+#include "int8_stages.cuh"
 #include "elementwise.cuh"
 #include "paged_attention.cuh"
 #include "sampler.cuh"
@@ -273,11 +274,13 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
   return launched(1);
 }
 
-int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
-                       int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
-                       int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
-                       int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream) {
-  if (!q || !sh || !qpos || !cache || !bt || !lut || !num || !den) return BX_EARG;
+static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
+                         int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
+                         int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e,
+                         const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M, int HD,
+                         int cluster_size, int variant, void* stream) {
+  if (!q || !qpos || !cache || !bt || !num || !den) return BX_EARG;
+  if (!ptab && (!sh || !lut)) return BX_EARG;
   if (R < 0 || HKV <= 0 || M < 1 || M > 4 || HD != ATT_HD || bs <= 0 || nblk <= 0 || nb <= 0) return BX_EARG;
   const int64_t max_keys = (int64_t)nblk * bs;
   if (max_keys >= 43690) return BX_EARG;
@@ -309,7 +312,7 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
   if (chunk_cap > cap_limit) return BX_EARG;
   const size_t smem = (size_t)fixed + (size_t)chunk_cap * 32;
   AttnParams p{q, (const i64*)sh, (const i64*)qpos, cache, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
-               (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, chunk_cap};
+               (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, chunk_cap, ptab};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)((int64_t)cs * R * HKV), 1, 1);
   cfg.blockDim = dim3(use_tma ? ATT2_THREADS : ATT_THREADS, 1, 1);
@@ -366,6 +369,88 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
   } else {
     if (cudaLaunchKernelEx(&cfg, exact_attention_kernel, p) != cudaSuccess) return BX_ELAUNCH;
   }
+  return launched(1);
+}
+
+int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
+                       int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
+                       int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
+                       int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream) {
+  if (!sh || !lut) return BX_EARG;
+  return run_attention(q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, lut, l2e,
+                       nullptr, num, den, R, HKV, M, HD, cluster_size, variant, stream);
+}
+
+int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache, int64_t nb, int64_t sc_nb,
+                      int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
+                      const int64_t* rmap, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
+                      int HD, int cluster_size, int variant, void* stream) {
+  if (!ptab) return BX_EARG;
+  return run_attention(q, nullptr, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, nullptr,
+                       0, ptab, num, den, R, HKV, M, HD, cluster_size, variant, stream);
+}
+
+int bx_int8_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gamma,
+                 int64_t* xo, int8_t* a8, int64_t* mant, int64_t* e, int32_t* flag, int M, int D, int do_norm,
+                 void* stream) {
+  if (!xin || !flag || M < 0 || D < 1 || D > NORM_THREADS * NORM_EPT || mode < 0 || mode > 2) return BX_EARG;
+  if ((mode == 0 && !ids) || (mode == 1 && !yin) || (do_norm && (!gamma || !a8 || !mant || !e))) return BX_EARG;
+  if (M == 0) return BX_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mode == 0) i8::int8_norm_kernel<0><<<M, NORM_THREADS, 0, st>>>(xin, (const i64*)yin, (const i64*)ids, (const i64*)gamma, (i64*)xo, a8, (i64*)mant, (i64*)e, flag, M, D, do_norm);
+  else if (mode == 1) i8::int8_norm_kernel<1><<<M, NORM_THREADS, 0, st>>>(xin, (const i64*)yin, (const i64*)ids, (const i64*)gamma, (i64*)xo, a8, (i64*)mant, (i64*)e, flag, M, D, do_norm);
+  else i8::int8_norm_kernel<2><<<M, NORM_THREADS, 0, st>>>(xin, (const i64*)yin, (const i64*)ids, (const i64*)gamma, (i64*)xo, a8, (i64*)mant, (i64*)e, flag, M, D, do_norm);
+  return launched(1);
+}
+
+int bx_int8_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos, const int64_t* slot,
+                int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, int64_t* q64, int32_t* q32,
+                int32_t* flag, int N, int H, int HKV, int HD, void* stream) {
+  if (!y || !cos || !sin || !pos || !flag || (!q64 && !q32) || N < 0) return BX_EARG;
+  if ((HD != 64 && HD != 128) || HKV <= 0 || H % HKV || (cache && (!slot || bs <= 0))) return BX_EARG;
+  if (N == 0) return BX_OK;
+  i8::Qkv8Params p{(const i64*)y, (const i64*)cos, (const i64*)sin, (const i64*)pos, (const i64*)slot, cache, sc_nb,
+                   sc_h, sc_bs, bs, (i64*)q64, q32, flag, H, HKV, HD};
+  i8::int8_qkv_kernel<<<dim3(N, HKV), HD / 2, 0, (cudaStream_t)stream>>>(p);
+  return launched(1);
+}
+
+int bx_int8_attn_out(const int64_t* num, const int64_t* den, int8_t* a8, int64_t* mant, int64_t* e, int N, int K2,
+                     int HD, void* stream) {
+  if (!num || !den || !a8 || !mant || !e || N < 0 || K2 <= 0 || K2 > AO_THREADS * AO_EPT || HD <= 0 || K2 % HD ||
+      K2 / HD > AO_MAXH)
+    return BX_EARG;
+  if (N == 0) return BX_OK;
+  i8::int8_attn_out_kernel<<<N, AO_THREADS, 0, (cudaStream_t)stream>>>((const i64*)num, (const i64*)den, a8, (i64*)mant, (i64*)e, N, K2, HD);
+  return launched(1);
+}
+
+int bx_int8_silu_quant(const int64_t* y, const int64_t* lut, int8_t* a8, int64_t* mant, int64_t* e, int64_t* scr,
+                       int N, int FF, void* stream) {
+  if (!y || !lut || !a8 || !mant || !e || N < 0 || FF <= 0 || FF > SILU_THREADS * 28) return BX_EARG;
+  if (N == 0) return BX_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int ept = (FF + SILU_THREADS - 1) / SILU_THREADS;
+  if (ept <= 4) i8::int8_silu_kernel<4><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, a8, (i64*)mant, (i64*)e, (i64*)scr, N, FF);
+  else if (ept <= 16) i8::int8_silu_kernel<16><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, a8, (i64*)mant, (i64*)e, (i64*)scr, N, FF);
+  else i8::int8_silu_kernel<28><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, a8, (i64*)mant, (i64*)e, (i64*)scr, N, FF);
+  return launched(1);
+}
+
+int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e, int64_t* y,
+                 int32_t* flag, int M, int N, int checked, void* stream) {
+  if (!c || !mul || !mant || !e || !y || !flag || M < 0 || N <= 0) return BX_EARG;
+  if (M == 0) return BX_OK;
+  const int64_t total = (int64_t)M * N;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  i8::int8_post_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(c, (const i64*)mul, (i64)fmsh, (const i64*)mant, (const i64*)e, (i64*)y, flag, M, N, checked);
+  return launched(1);
+}
+
+int bx_int8_flag_end(int64_t* scr, int32_t* flag, int L, void* stream) {
+  if (!scr || !flag || L <= 0) return BX_EARG;
+  i8::int8_flag_end_kernel<<<1, 64, 0, (cudaStream_t)stream>>>((i64*)scr, flag, L);
   return launched(1);
 }
 

@@ -52,6 +52,7 @@ struct AttnParams {
   i64* den;             // [R, HKV, M]
   int M, HKV;
   int chunk_cap;        // score slots per query row in shared memory (multiple of 8)
+  const int32_t* ptab;  // int8 mode: weight table rsh(e^z table, 10), 131073 entries; null = exact mode
 };
 
 struct AttnShared {
@@ -84,6 +85,20 @@ __device__ __forceinline__ i64 attn_weight(i64 raw, i64 mx, i64 rowshift, i64 l2
   const i64 v = a + rshs<FT2 - EXP2_BITS>((b - a) * rr);
   const int s = (int)imin((i64)(EXP2_ONE - FP) + n, 62);
   return (v + (1ll << (s - 1))) >> s;
+}
+
+// The weight of one (query, key) pair in either mode. int8 mode (src/bitexact/int8/segs.py:91-99, fused copy
+// src/bitexact/vllm_plugin/tri_paged.py:171-175, head_dim 64): z = rsh(raw - mx, 2*14 + 3 - 12), direct table
+// lookup, 0 below the table.
+__device__ __forceinline__ i64 attn_weight_any(const AttnParams& p, i64 raw, i64 mx, i64 rowshift) {
+  if (p.ptab) {
+    constexpr int ZSH = 2 * 14 + 3 - 12;
+    constexpr i64 ZLO = -(32ll << 12);
+    const i64 z = ((raw - mx) + (1ll << (ZSH - 1))) >> ZSH;
+    const i64 idx = imax(z, ZLO - 1) - ZLO;
+    return idx >= 0 ? (i64)__ldg(p.ptab + idx) : 0;
+  }
+  return attn_weight(raw, mx, rowshift, p.l2e, p.lut);
 }
 
 __global__ void __launch_bounds__(ATT_THREADS)
@@ -215,7 +230,7 @@ exact_attention_kernel(const AttnParams p) {
   for (int c = 0; c < CS; ++c) mx = imax(mx, cluster.map_shared_rank(sm->cmax, c)[g2]);
   const bool gok = g2 < p.M;
   const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
-  const i64 rowshift = gok ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
+  const i64 rowshift = (gok && p.sh) ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
   i64 den = 0;
   i64 nacc[4][4];
 #pragma unroll
@@ -226,7 +241,7 @@ exact_attention_kernel(const AttnParams p) {
   for (i64 kb = lo + 8 * warp; kb < hi; kb += 8 * ATT_WARPS) {
     const i64 mykey = kb + (lane >> 2);
     i64 pv = 0;
-    if (mykey < hi && mykey <= qp2) pv = attn_weight(scores[(int64_t)g2 * p.chunk_cap + (mykey - lo)], mx, rowshift, p.l2e, p.lut);
+    if (mykey < hi && mykey <= qp2) pv = attn_weight_any(p, scores[(int64_t)g2 * p.chunk_cap + (mykey - lo)], mx, rowshift);
     den += pv;
     const i64 kfor = kb + (lane & 7);
     const int64_t off = kfor < hi ? key_offset(kfor) : 0;
@@ -490,7 +505,7 @@ exact_attention_tma_kernel(const __grid_constant__ CUtensorMap tmap, const AttnP
   for (int c = 0; c < CS; ++c) mx = imax(mx, cluster.map_shared_rank(sm->cmax, c)[g2]);
   const bool gok = g2 < p.M;
   const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
-  const i64 rowshift = gok ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
+  const i64 rowshift = (gok && p.sh) ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
   i64 den = 0;
   i64 nacc[4][4];
 #pragma unroll
@@ -509,7 +524,7 @@ exact_attention_tma_kernel(const __grid_constant__ CUtensorMap tmap, const AttnP
       if (kb < hi) {
         const i64 mykey = kb + (lane >> 2);
         i64 pv = 0;
-        if (mykey < hi && mykey <= qp2) pv = attn_weight(scores[(mykey - lo) * 4 + g2], mx, rowshift, p.l2e, p.lut);
+        if (mykey < hi && mykey <= qp2) pv = attn_weight_any(p, scores[(mykey - lo) * 4 + g2], mx, rowshift);
         den += pv;
         sm->pw[warp][lane >> 2][g2] = (int)pv;
         __syncwarp();
@@ -833,7 +848,7 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
   for (int c = 0; c < CS; ++c) mx = imax(mx, cluster.map_shared_rank(sm->cmax, c)[g2]);
   const bool gok = g2 < p.M;
   const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
-  const i64 rowshift = gok ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
+  const i64 rowshift = (gok && p.sh) ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
   i64 den = 0;
   const int ngroups = (int)((hi - lo + 31) / 32);
   for (int grp = warp; grp < ngroups; grp += ATT_WARPS) {
@@ -847,7 +862,7 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       const int kl = 8 * j + (lane >> 2);
       const i64 key = lo + (i64)grp * 32 + kl;
       i64 pv = 0;
-      if (key < hi && key <= qp2) pv = attn_weight(sc[j], mx, rowshift, p.l2e, p.lut);
+      if (key < hi && key <= qp2) pv = attn_weight_any(p, sc[j], mx, rowshift);
       den += pv;
       int pr = (int)pv;
       const int off = (kl >> 4) * 256 + (kl & 15) + g2 * 16;

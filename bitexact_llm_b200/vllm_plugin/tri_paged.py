@@ -32,3 +32,36 @@ def to_limbs(c):
             out[..., (o + i) * HD:(o + i + 1) * HD] = lo.to(torch.int8)
             r = (r - lo) >> 8
     return out
+
+
+def weight_table(lut):
+    """The attention weight table rsh(exp_lut, 30 - 20) as int32 (src/bitexact/vllm_plugin/tri_paged.py:351-356)."""
+    t = (lut + (1 << 9)) >> 10
+    return t.to(torch.int32).contiguous()
+
+
+def attend(q, qpos, cache, bt, ptab, nsplit=None, bm=None, bn=None, warps=4, rmap=None, variant=0):
+    """int8-mode paged attention, M <= 4 query rows per (request, KV head): q int64 (or int32) [R, HKV, M, HD] within
+    3 limbs, qpos int64 [R, M], cache int8 limb planes [nb, HKV, bs, 8 HD], bt [R, *] block-table rows, ptab =
+    weight_table(exp table). Returns num int64 [R, HKV, M, HD], den int64 [R, HKV, M, 1]
+    (src/bitexact/vllm_plugin/tri_paged.py:363-430, decode form). nsplit maps to the cluster size; bm, bn, warps are
+    accepted and ignored."""
+    R, HKV, M, HD = q.shape
+    assert M <= 4 and HD == 64 and cache.shape[1] == HKV and cache.shape[3] == 8 * HD and cache.stride(3) == 1
+    assert bt.shape[1] * cache.shape[2] < 43690 and bt.dtype in (torch.int32, torch.int64) and bt.stride(1) == 1
+    q32 = q.to(torch.int32).contiguous()
+    qpos = qpos.contiguous()
+    num = torch.empty(R, HKV, M, HD, dtype=torch.long, device=q.device)
+    den = torch.empty(R, HKV, M, 1, dtype=torch.long, device=q.device)
+    cs = 0
+    if nsplit is not None:
+        cs = 1
+        while cs < min(int(nsplit), 8):
+            cs *= 2
+    rc = nv.lib().bx_int8_attention(q32.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0], cache.stride(0),
+                                    cache.stride(1), cache.stride(2), cache.shape[2], bt.data_ptr(),
+                                    int(bt.dtype == torch.int64), bt.stride(0), bt.shape[1],
+                                    nv.ptr(rmap.long().contiguous() if rmap is not None else None), ptab.data_ptr(),
+                                    num.data_ptr(), den.data_ptr(), R, HKV, M, HD, cs, variant, nv.stream())
+    nv.check(rc, "bx_int8_attention")
+    return num, den

@@ -153,6 +153,56 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
                        int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
                        int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream);
 
+/* ---- int8-mode attention and element-wise stages -------------------------------------------------------
+ * Fixed points of int8 mode: residual stream / linear outputs / logits 16 bits, gamma 12, cos / sin 16, q / k / v 14,
+ * attention weights 20. A linear's input is always (a8, mant, e): activation limb planes int8 [2, M, K] (limb i of
+ * row m at row i * M + m: the reference's stack_limbs layout without padding rows) plus the row scale
+ * mant * 2^e with mant in [2^23, 2^24]; its output y is the int64 tensor of bx_int8_linear_post.
+ */
+
+/* Paged attention with the int8-mode weight rule (direct e^z table, no interpolation, head_dim 64):
+ * q int32 [R, HKV, M, 64] (|q| within 3 limbs), ptab int32 [131073] = rsh(exp table, 10); the other arguments as
+ * bx_exact_attention. Replaces tri_paged.attend (src/bitexact/vllm_plugin/tri_paged.py:363-430). */
+int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache, int64_t nb, int64_t sc_nb,
+                      int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
+                      const int64_t* rmap, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
+                      int HD, int cluster_size, int variant, void* stream);
+
+/* x = emb[ids] (mode 0) | xin + yin (mode 1) | xin (mode 2); with do_norm: pre_norm(x, gamma) -> (a8, mant, e),
+ * else the |x| >= 2^42 bound flag. gamma int64 [D] at 12 bits. D <= 4096.
+ * Replaces tri_fuse.embed_norm / add_norm (src/bitexact/vllm_plugin/tri_fuse.py:82-160) = segs.pre_norm
+ * (src/bitexact/int8/segs.py:48-53) after post + residual add. */
+int bx_int8_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gamma,
+                 int64_t* xo, int8_t* a8, int64_t* mant, int64_t* e, int32_t* flag, int M, int D, int do_norm,
+                 void* stream);
+
+/* RoPE (16-bit tables) of q and k, v >> 2, LIM3 bound flag, K / V limb planes stored at `slot` of the paged cache.
+ * y int64 [N, (H + 2 HKV) HD]; q64 int64 and / or q32 int32 [N, HKV, G, HD] (either may be NULL).
+ * Replaces tri_fuse.qkv (src/bitexact/vllm_plugin/tri_fuse.py:163-214) = segs.qkv (src/bitexact/int8/segs.py:69-88). */
+int bx_int8_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos, const int64_t* slot,
+                int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, int64_t* q64, int32_t* q32,
+                int32_t* flag, int N, int H, int HKV, int HD, void* stream);
+
+/* o = rdiv(num << 2, den) per head, pre_plain(o) -> (a8, mant, e). num int64 [N, K2], den int64 [N, K2 / HD].
+ * Replaces tri_fuse.attn_out (src/bitexact/vllm_plugin/tri_fuse.py:217-240) = segs.attn_out
+ * (src/bitexact/int8/segs.py:101-109). */
+int bx_int8_attn_out(const int64_t* num, const int64_t* den, int8_t* a8, int64_t* mant, int64_t* e, int N, int K2,
+                     int HD, void* stream);
+
+/* h = rsh(silu_table(gate) * up, 16), pre_plain(h) -> (a8, mant, e). y int64 [N, 2 FF], lut = SiLU table int64
+ * [262145]. scr (may be NULL) int64 [2]: receives atomic maxima of |silu(gate)| and |up| for the product-bound flag.
+ * Replaces tri_mlp.silu_quant (src/bitexact/vllm_plugin/tri_mlp.py:153-183) = segs.silu_mul
+ * (src/bitexact/int8/segs.py:111-118). bx_int8_flag_end: flag |= scr[i][0] * scr[i][1] >= 2^62 for i < L, then
+ * clears scr (tri_fuse.flag_end, src/bitexact/vllm_plugin/tri_fuse.py:248-265). */
+int bx_int8_silu_quant(const int64_t* y, const int64_t* lut, int8_t* a8, int64_t* mant, int64_t* e, int64_t* scr,
+                       int N, int FF, void* stream);
+int bx_int8_flag_end(int64_t* scr, int32_t* flag, int L, void* stream);
+
+/* segs.post on a raw bx_int8_mm output (src/bitexact/int8/segs.py:62-67): c int32 [>= 2 M, N] -> y int64 [M, N].
+ * For callers that keep the reference's two-step int_mm + post form; bx_int8_linear_post does both in one kernel. */
+int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e, int64_t* y,
+                 int32_t* flag, int M, int N, int checked, void* stream);
+
 /* ---- integer sampler ------------------------------------------------------------------------------------
  * Raw PCG64 words of numpy's default_rng([20261022, seed, t]): keys int64 [n, 2] -> out int64 [n, V].
  * Replaces gpu_pcg.raw_rows (src/bitexact/vllm_plugin/gpu_pcg.py:94-108; CPU: src/bitexact/sampling.py:27-37). */

@@ -98,10 +98,68 @@ def generate(model, prompt, max_new, tn=0, td=1, seed=0):
     V = model.c["emb"].shape[0]
     for t in range(max_new):
         lg = model.logits(h)
-        g = osamp.gumbel(osamp.raw_words(seed, t, V), model.c["ln"], ox.FR)[None] if tn else None
+        g = osamp.gumbel(osamp.raw_words(seed, t, V), model.c["ln"], getattr(model, "FR", ox.FR))[None] if tn else None
         y = int(osamp.sample(lg, tn, td, g)[0])
         toks.append(y)
         shas.append(logits_sha(lg[0]))
         if t + 1 < max_new:
             h = model.forward(cache, [y], [P + t], [0])
     return toks, shas
+
+
+class OracleInt8Model:
+    """int8-mode forward on the CPU from the oracle's int8 stages (src/bitexact/int8/model.py:69-124, in the
+    token-row form of the plugin). Constants dict with numpy arrays under the reference's int8 keys."""
+
+    FR = 16
+
+    def __init__(self, c):
+        from . import int8 as o8
+        self.o8 = o8
+        cfg = c["cfg"]
+        self.D, self.H, self.HKV = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+        self.HD = cfg.get("head_dim") or self.D // self.H
+        self.L = c["n_layers"]
+        self.c = {k: (np.asarray(v) if hasattr(v, "shape") else v) for k, v in c.items()}
+        self.flag = False
+
+    def _lin(self, pre, name, x=None):
+        o8, c = self.o8, self.c
+        q, mant, e = pre
+        y, f = o8.post(o8.imm(q, c[name]), c[f"{name}.m"], int(c[f"{name}.fm"]) + 8 - 24, mant, e)
+        self.flag |= f
+        return y if x is None else x + y
+
+    def new_cache(self, B):
+        return [[{"k": [], "v": []} for _ in range(self.L)] for _ in range(B)]
+
+    def forward(self, cache, ids, pos, seq):
+        o8, c, H, HKV, HD = self.o8, self.c, self.H, self.HKV, self.HD
+        G = H // HKV
+        N = len(ids)
+        x = i64(c["emb"][np.asarray(ids)])
+        for i in range(self.L):
+            y = self._lin(o8.pre_norm(x, c[f"{i}.ga"]), f"{i}.wqkv")
+            q, k, v, f = o8.rope_qkv(y, np.asarray(pos), c["cos"], c["sin"], H, HKV, HD)
+            self.flag |= f
+            num = np.zeros((N, H, HD), dtype=I64)
+            den = np.zeros((N, H, 1), dtype=I64)
+            for n in range(N):
+                kv = cache[seq[n]][i]
+                assert len(kv["k"]) == pos[n]
+                kv["k"].append(k[n]), kv["v"].append(v[n])
+                K, V = np.stack(kv["k"], 1), np.stack(kv["v"], 1)
+                raw = np.einsum("hgd,hsd->hgs", q[n].reshape(HKV, G, HD), K)
+                p, dn = o8.softmax(raw, np.ones_like(raw, dtype=bool), c["exp"])
+                num[n] = np.einsum("hgs,hsd->hgd", p, V).reshape(H, HD)
+                den[n] = dn.reshape(H, 1)
+            x = self._lin(o8.attn_out(num, den), f"{i}.wo", x)
+            gu = self._lin(o8.pre_norm(x, c[f"{i}.gm"]), f"{i}.wgu")
+            a, mant, e, f = o8.silu_mul(gu, c["silu"])
+            self.flag |= f
+            x = self._lin((a, mant, e), f"{i}.wd", x)
+        self.flag |= bool(np.abs(x).max(initial=0) >= 1 << 42)
+        return x
+
+    def logits(self, h):
+        return self._lin(self.o8.pre_norm(h, self.c["gf"]), "lm")

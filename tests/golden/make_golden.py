@@ -220,9 +220,39 @@ def tiny_model():
     np.savez_compressed(os.path.join(HERE, "tiny_model.npz"), **out)
 
 
+def tiny_model_int8():
+    """The same tiny model through the reference's int8 constants build and CPU engine (IntLlama)."""
+    import tempfile
+
+    from safetensors.torch import save_file
+    from transformers import LlamaConfig
+
+    from bitexact.generate import generate
+    from bitexact.int8.consts import build
+    from bitexact.int8.model import IntLlama
+    sd = tiny_state_dict()
+    with tempfile.TemporaryDirectory() as d:
+        LlamaConfig(max_position_embeddings=4096, **TINY).save_pretrained(d)
+        save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(d, "model.safetensors"))
+        c = build(d)
+    m = IntLlama(c, "cpu")
+    out = {"sha256": np.array(c["sha256"]), "cos": n(c["cos"][:128]), "sin": n(c["sin"][:128]),
+           "post_check": np.array(bool(m.post_check))}
+    for pi, prompt in enumerate(TINY_PROMPTS):
+        for name, (tn, td) in (("greedy", (0, 1)), ("t07", (7, 10))):
+            toks, hashes = generate(m, prompt, 8, tn, td, seed=pi)
+            out[f"p{pi}_{name}_tok"] = np.array(toks)
+            out[f"p{pi}_{name}_sha"] = np.array(hashes)
+    # a few constants for pinning this repository's int8 weight preparation
+    out["wqkv0"] = n(c["0.wqkv"][:64]); out["wqkv0_m"] = n(c["0.wqkv.m"]); out["wqkv0_fm"] = np.array(c["0.wqkv.fm"])
+    out["emb_head"] = n(c["emb"][:8]); out["ga0"] = n(c["0.ga"])
+    np.savez_compressed(os.path.join(HERE, "tiny_model_int8.npz"), **out)
+
+
 if __name__ == "__main__":
     exact_ops()
     sampler()
     int8_ops()
     tiny_model()
+    tiny_model_int8()
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))

@@ -52,3 +52,19 @@ def test_oracle_model_reproduces_reference_generation():
             assert toks == z[f"p{pi}_{name}_tok"][:4].tolist(), (pi, name)
             assert shas == z[f"p{pi}_{name}_sha"][:4].tolist(), (pi, name)
     assert not m.flag
+
+
+def test_int8_weight_preparation_and_oracle_model_reproduce_the_reference():
+    from make_golden import TINY, TINY_PROMPTS, tiny_state_dict
+    from bitexact_llm_b200.int8 import consts
+    from oracle.model import OracleInt8Model, generate
+    z = np.load(os.path.join(GOLD, "tiny_model_int8.npz"))
+    c = consts.build(TINY, tiny_state_dict())
+    assert consts.digest(c) == str(z["sha256"])
+    m = OracleInt8Model({k: (v.numpy() if torch.is_tensor(v) else v) for k, v in c.items()})
+    for pi in (0, 1):
+        for name, (tn, td) in (("greedy", (0, 1)), ("t07", (7, 10))):
+            toks, shas = generate(m, TINY_PROMPTS[pi], 3, tn, td, seed=pi)
+            assert toks == z[f"p{pi}_{name}_tok"][:3].tolist(), (pi, name)
+            assert shas == z[f"p{pi}_{name}_sha"][:3].tolist(), (pi, name)
+    assert not m.flag
