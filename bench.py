@@ -35,6 +35,8 @@ def parse():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--mode", default="exact", choices=["exact", "int8"],
+                    help="exact: original bf16 weights as 3 limbs (the headline); int8: int8 weights, 2-limb activations")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="launch kernel by kernel instead of replaying a CUDA graph")
@@ -194,15 +196,23 @@ def run_b200(args, rank, world):
     cfg = dict(consts.LLAMA_1B)
     cfg["num_hidden_layers"] = args.layers
     sd = consts.random_state_dict(cfg, seed=0, device=dev)          # same weights on every rank
-    c = consts.build(cfg, sd, n_pos=P + 4 * (K + W) + 64)
-    del sd
-    eng = ExactEngine(c, dev)
-    del c
     timer = LinTimer()
-    for ly in eng.layers:
-        for n in ("wqkv", "wo", "wgu", "wd"):
-            ly[n].timer = timer
-    eng.lm.timer = timer
+    if args.mode == "exact":
+        c = consts.build(cfg, sd, n_pos=P + 4 * (K + W) + 64)
+        del sd
+        eng = ExactEngine(c, dev)
+        del c
+        for ly in eng.layers:
+            for n in ("wqkv", "wo", "wgu", "wd"):
+                ly[n].timer = timer
+        eng.lm.timer = timer
+    else:
+        from bitexact_llm_b200.int8 import consts as consts8
+        from bitexact_llm_b200.int8.engine import IntEngine
+        c = consts8.build(cfg, sd, n_pos=max(2048, P + 4 * (K + W) + 64))
+        del sd
+        eng = IntEngine(c, dev)
+        del c
 
     g = torch.Generator().manual_seed(1000 + rank)                  # every rank its own sequences
     prompts = torch.randint(0, cfg["vocab_size"], (B, P), generator=g)
@@ -319,11 +329,12 @@ def run_b200(args, rank, world):
     bf16 = peaks.get("bf16_tflops_sustained")
     peak_int8 = 2.0 * bf16 if bf16 else 2.0 * 1400.0
     achieved = lin_ops / (lin_ms * 1e-3) / 1e12 if lin_ms > 0 else None
+    metric = METRIC if args.mode == "exact" else METRIC.replace("exact-mode", "int8-mode")
     line = {
-        "metric": METRIC, "value": world * B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
+        "metric": metric, "value": world * B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 limbs -> int32 -> int64", "data": "synthetic",
-        "config": {"workload": "BASELINE config 4: random-init Llama-3.2-1B exact-mode decode, "
+        "config": {"workload": f"BASELINE config {4 if args.mode == 'exact' else 5}: random-init Llama-3.2-1B {args.mode}-mode decode, "
                                f"{P}-token uniform random prompts, batch {B} per GPU, T=0.7 integer Gumbel sampler",
                    "batch_per_gpu": B, "prompt": P, "layers": args.layers, "page": 16,
                    "parallelism": f"sequence-sharded x{world}, no data-path collective",
