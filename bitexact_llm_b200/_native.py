@@ -26,6 +26,7 @@ _SIGNATURES = {
     "bx_clear_device_status": (I, []),
     "bx_exact_linear_scratch_bytes": (Z, [I, I]),
     "bx_exact_linear": (I, [P, L, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, P]),
+    "bx_exact_linear_planes": (I, [P, P, L, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, P]),
     "bx_exact_linear_static_max_bytes": (Z, []),
     "bx_exact_linear_static": (I, [P, L, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, P]),
     "bx_split_limbs": (I, [P, L, P, I, I, P]),

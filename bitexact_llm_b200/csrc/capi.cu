@@ -167,17 +167,12 @@ int bx_split_limbs(const int32_t* q, int64_t ldq, int8_t* a8, int M, int K, void
   return launched(1);
 }
 
-int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
-                    const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
-                    int8_t* scratch, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
-                    void* stream) {
-  if (!q || !sh || !limbs || !d || !g || !scratch || !y || !flag) return BX_EARG;
-  if (M < 0 || N <= 0 || K <= 0 || K % 16 || K >= 43690 || !aligned16(limbs) || !aligned16(scratch)) return BX_EARG;
-  if (cnt && (!ec || !ev || R <= 0)) return BX_EARG;
-  if (M == 0) return BX_OK;
+static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
+                             const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
+                             const int8_t* planes, int64_t* y, int32_t* flag, int M, int N, int K, int checked,
+                             int tile_rows, void* stream) {
+  int8_t* scratch = const_cast<int8_t*>(planes);
   cudaStream_t st = (cudaStream_t)stream;
-  int rc = bx_split_limbs(q, ldq, scratch, M, K, stream);
-  if (rc != BX_OK) return rc;
   int ta = tile_rows;
   bool persistent = false;
   if (ta < 0) {                       // negative: that tile size on the persistent kernel (16, 32, 48)
@@ -224,9 +219,15 @@ int bx_exact_norm(int mode, const void* xin, const int64_t* yin, const int64_t* 
   while ((1 << lg) < D) ++lg;
   cudaStream_t st = (cudaStream_t)stream;
   const i64* y = (const i64*)yin; const i64* id = (const i64*)ids;
-  if (mode == 0) norm_kernel<0><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
-  else if (mode == 1) norm_kernel<1><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
-  else norm_kernel<2><<<M, NORM_THREADS, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, flag, M, D, lg, do_norm);
+#define BX_NORM_LAUNCH(MODE, NT, EPT) \
+  norm_kernel<MODE, NT, EPT><<<M, NT, 0, st>>>(xin, y, id, (const i64*)gm, (const i64*)ge, (i64*)xo, q, (i64*)sh, a8, \
+                                              flag, M, D, lg, do_norm)
+  if (D <= 2048) {                      // 512 threads x 4 elements
+    if (mode == 0) BX_NORM_LAUNCH(0, 512, 4); else if (mode == 1) BX_NORM_LAUNCH(1, 512, 4); else BX_NORM_LAUNCH(2, 512, 4);
+  } else {                              // 512 threads x 8 elements
+    if (mode == 0) BX_NORM_LAUNCH(0, 512, 8); else if (mode == 1) BX_NORM_LAUNCH(1, 512, 8); else BX_NORM_LAUNCH(2, 512, 8);
+  }
+#undef BX_NORM_LAUNCH
   return launched(1);
 }
 
@@ -267,6 +268,23 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
   if (!y || !lut || !q || !sh || !flag || N < 0 || FF <= 0 || FF > SILU_THREADS * 28) return BX_EARG;
   if (N == 0) return BX_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (FF == SILU_CL * SILU_CL_THREADS * 8 && N <= 4096) {          // decode batches of the 1B model: cluster form
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(SILU_CL * N, 1, 1);
+    cfg.blockDim = dim3(SILU_CL_THREADS, 1, 1);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = SILU_CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, silu_cluster_kernel<8>, (const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF) !=
+        cudaSuccess)
+      return BX_ELAUNCH;
+    return launched(1);
+  }
   const int ept = (FF + SILU_THREADS - 1) / SILU_THREADS;
   if (ept <= 4) silu_kernel<4><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
   else if (ept <= 16) silu_kernel<16><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag, N, FF);
@@ -289,21 +307,23 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
   // TMA-staged kernel when the cache layout allows a tensor map over it, else the direct-load kernel.
   const bool tma_ok = (bs % 8 == 0) && (ATT2_STAGE_KEYS % bs == 0) && sc_bs % 16 == 0 && sc_h % 16 == 0 &&
                       sc_nb % 16 == 0 && sc_bs >= 384 && aligned16(cache);
-  if ((variant == 2 || variant == 3) && !tma_ok) return BX_EARG;
-  if (variant < 0 || variant > 3) return BX_EARG;
-  const int kind = variant != 0 ? variant : (tma_ok ? 3 : 1);   // 1 direct loads, 2 TMA-staged, 3 TMA + tcgen05 p.V
+  if (variant >= 2 && !tma_ok) return BX_EARG;
+  if (variant < 0 || variant > 4 || (variant == 4 && bs > 32)) return BX_EARG;
+  // 1 direct loads, 2 TMA-staged, 3 TMA + tcgen05 p.V with 8 consumer warps, 4 the same with 4 consumer warps
+  const int kind = variant != 0 ? variant : (tma_ok ? ((bs <= 32 && (int64_t)R * HKV >= 64) ? 4 : 3) : 1);
+  const int nw = kind == 4 ? 4 : 8;
   const bool use_tma = kind >= 2;
-  const int64_t fixed = kind == 3 ? 1024 + (int64_t)ATT3_NS * ATT3_STAGE_BYTES + (int64_t)sizeof(Attn3Small)
+  const int64_t fixed = kind >= 3 ? 1024 + (int64_t)ATT3_NS * (8 * nw * 256) + (int64_t)sizeof(Attn3Small)
                         : kind == 2 ? (int64_t)ATT2_NS * ATT2_STAGE_BYTES + (int64_t)sizeof(Attn2Small)
                                     : (int64_t)sizeof(AttnShared);
-  const int64_t gran = use_tma ? ATT2_STAGE_KEYS : 8;
+  const int64_t gran = kind >= 3 ? 8 * nw : use_tma ? ATT2_STAGE_KEYS : 8;
   const int64_t cap_limit = (smem_limit - fixed) / 32 / gran * gran;
   int cs = cluster_size;
   if (cs == 0) {
     cs = 1;
     const int64_t pairs = (int64_t)R * HKV;
     while (cs < ATT_MAXCS && pairs * cs < 2 * 148) cs *= 2;               // fill the SMs
-    while (cs < ATT_MAXCS && (max_keys + cs - 1) / cs > 704) cs *= 2;     // score buffer small: 3 CTAs per SM
+    while (cs < ATT_MAXCS && (max_keys + cs - 1) / cs > (kind == 4 ? 512 : 704)) cs *= 2;   // small score buffer
   }
   if (cs != 1 && cs != 2 && cs != 4 && cs != 8) return BX_EARG;
   auto cap_of = [&](int c) { return ((max_keys + c - 1) / c + gran - 1) / gran * gran; };
@@ -315,7 +335,7 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
                (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, chunk_cap, ptab};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)((int64_t)cs * R * HKV), 1, 1);
-  cfg.blockDim = dim3(use_tma ? ATT2_THREADS : ATT_THREADS, 1, 1);
+  cfg.blockDim = dim3(kind == 4 ? 160 : use_tma ? ATT2_THREADS : ATT_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];
@@ -325,9 +345,11 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  static bool configured[4] = {false, false, false, false};
+  static bool configured[5] = {false, false, false, false, false};
   if (!configured[kind]) {
-    cudaError_t e = kind == 3 ? cudaFuncSetAttribute(exact_attention_tc_kernel,
+    cudaError_t e = kind == 4 ? cudaFuncSetAttribute(exact_attention_tc_kernel<4>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
+                    : kind == 3 ? cudaFuncSetAttribute(exact_attention_tc_kernel<8>,
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
                     : kind == 2 ? cudaFuncSetAttribute(exact_attention_tma_kernel,
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
@@ -336,7 +358,7 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
     if (e != cudaSuccess) return BX_ELAUNCH;
     configured[kind] = true;
   }
-  if (kind == 3) {
+  if (kind >= 3) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return BX_ELAUNCH;
     CUtensorMap tk, tv;
@@ -352,7 +374,9 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return BX_ELAUNCH;
-    if (cudaLaunchKernelEx(&cfg, exact_attention_tc_kernel, tk, tv, p) != cudaSuccess) return BX_ELAUNCH;
+    if ((kind == 4 ? cudaLaunchKernelEx(&cfg, exact_attention_tc_kernel<4>, tk, tv, p)
+                   : cudaLaunchKernelEx(&cfg, exact_attention_tc_kernel<8>, tk, tv, p)) != cudaSuccess)
+      return BX_ELAUNCH;
   } else if (use_tma) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return BX_ELAUNCH;
@@ -511,6 +535,30 @@ int bx_int8_linear_post(const int8_t* a, const int8_t* w, const int64_t* mul, in
   if (!mul || !mant || !e || !y || !flag) return BX_EARG;
   Int8EpiParams ep{nullptr, mul, fmsh, mant, e, y, flag, M, N, checked};
   return run_int8<true>(a, w, ep, K, tile_rows, (cudaStream_t)stream);
+}
+
+int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
+                    const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
+                    int8_t* scratch, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
+                    void* stream) {
+  if (!q || !sh || !limbs || !d || !g || !scratch || !y || !flag) return BX_EARG;
+  if (M < 0 || N <= 0 || K <= 0 || K % 16 || K >= 43690 || !aligned16(limbs) || !aligned16(scratch)) return BX_EARG;
+  if (cnt && (!ec || !ev || R <= 0)) return BX_EARG;
+  if (M == 0) return BX_OK;
+  int rc = bx_split_limbs(q, ldq, scratch, M, K, stream);
+  if (rc != BX_OK) return rc;
+  return exact_linear_core(q, ldq, sh, limbs, d, g, cnt, ec, ev, R, scratch, y, flag, M, N, K, checked, tile_rows, stream);
+}
+
+int bx_exact_linear_planes(const int8_t* planes, const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs,
+                           const int64_t* d, const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev,
+                           int R, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
+                           void* stream) {
+  if (!planes || !sh || !limbs || !d || !g || !y || !flag) return BX_EARG;
+  if (M < 0 || N <= 0 || K <= 0 || K % 16 || K >= 43690 || !aligned16(limbs) || !aligned16(planes)) return BX_EARG;
+  if (cnt && (!ec || !ev || R <= 0 || !q)) return BX_EARG;
+  if (M == 0) return BX_OK;
+  return exact_linear_core(q, ldq, sh, limbs, d, g, cnt, ec, ev, R, planes, y, flag, M, N, K, checked, tile_rows, stream);
 }
 
 // ---- allocation-free variant of the exact linear ----

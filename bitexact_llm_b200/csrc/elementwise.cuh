@@ -7,6 +7,8 @@
 // src/bitexact/vllm_plugin/exact_fuse.py:136-334.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "bx_rules.cuh"
 
 namespace bx {
@@ -109,18 +111,20 @@ __device__ __forceinline__ void store_limb_planes(int8_t* a8, int64_t plane, int
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_EPT = 16;     // D <= 4096
 
-template <int MODE>
-__global__ void __launch_bounds__(NORM_THREADS)
+// NT threads per row, EPT = ceil(D / NT) elements per thread (NT = 512, EPT = 4 for D = 2048: the row's serial
+// instruction stream, not bandwidth, bounds this kernel at decode batch sizes).
+template <int MODE, int NT, int EPT>
+__global__ void __launch_bounds__(NT)
 norm_kernel(const void* __restrict__ xin, const i64* __restrict__ yin, const i64* __restrict__ ids,
             const i64* __restrict__ gm, const i64* __restrict__ ge, i64* __restrict__ xo, int32_t* __restrict__ q,
             i64* __restrict__ sh_out, int8_t* __restrict__ a8, int32_t* flag, int M, int D, int lg, int do_norm) {
   __shared__ i64 red[33];
   const int64_t row = blockIdx.x;
-  i64 x[NORM_EPT];
+  i64 x[EPT];
   i64 ax = 0;
 #pragma unroll
-  for (int k = 0; k < NORM_EPT; ++k) {
-    const int c = threadIdx.x + k * NORM_THREADS;
+  for (int k = 0; k < EPT; ++k) {
+    const int c = threadIdx.x + k * NT;
     x[k] = 0;
     if (c < D) {
       if (MODE == 0) x[k] = (i64) reinterpret_cast<const int32_t*>(xin)[ids[row] * D + c];
@@ -138,7 +142,7 @@ norm_kernel(const void* __restrict__ xin, const i64* __restrict__ yin, const i64
   const i64 shx = imax((i64)bitlen(amax) - 25, -6);
   i64 S = 0;
 #pragma unroll
-  for (int k = 0; k < NORM_EPT; ++k) {
+  for (int k = 0; k < EPT; ++k) {
     const i64 xs = rshc(x[k], shx);
     S += xs * xs;
   }
@@ -153,8 +157,8 @@ norm_kernel(const void* __restrict__ xin, const i64* __restrict__ yin, const i64
   // ndiv + quant(., -FN)
   i64 pmax = 0;
 #pragma unroll
-  for (int k = 0; k < NORM_EPT; ++k) {
-    const int c = threadIdx.x + k * NORM_THREADS;
+  for (int k = 0; k < EPT; ++k) {
+    const int c = threadIdx.x + k * NT;
     if (c < D) {
       x[k] = div_round_recip<3>(x[k] * gm[c], ge[c] - FR - er + FN, (u64)r, inv);
       pmax = imax(pmax, iabs(x[k]));
@@ -165,8 +169,8 @@ norm_kernel(const void* __restrict__ xin, const i64* __restrict__ yin, const i64
   if (threadIdx.x == 0) sh_out[row] = sh;
   const int64_t plane = (int64_t)M * D;
 #pragma unroll
-  for (int k = 0; k < NORM_EPT; ++k) {
-    const int c = threadIdx.x + k * NORM_THREADS;
+  for (int k = 0; k < EPT; ++k) {
+    const int c = threadIdx.x + k * NT;
     if (c < D) {
       const int qv = (int)rshc(x[k], sh + FN);
       q[row * D + c] = qv;
@@ -364,6 +368,55 @@ silu_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, int32_t* __r
       if (a8) store_limb_planes(a8, plane, row * FF + c, qv);
     }
   }
+}
+
+// Cluster form of silu_kernel for decode batches: the FF columns of a row are split over the CTAs of a thread-block
+// cluster (4 x 256 threads), the row maximum is exchanged through distributed shared memory. Four times as many
+// CTAs as rows keep every SM busy when the batch has only a few hundred rows.
+constexpr int SILU_CL = 4;
+constexpr int SILU_CL_THREADS = 256;
+
+template <int EPT>
+__global__ void __launch_bounds__(SILU_CL_THREADS)
+silu_cluster_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, int32_t* __restrict__ q,
+                    i64* __restrict__ sh_out, int8_t* __restrict__ a8, int32_t* flag, int M, int FF) {
+  namespace cg = cooperative_groups;
+  __shared__ i64 red[33];
+  __shared__ i64 cta_max;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int part = (int)cluster.block_rank();
+  const int64_t row = blockIdx.x / SILU_CL;
+  const int c0 = part * (FF / SILU_CL);
+  const i64* yr = y + row * (2 * (int64_t)FF);
+  i64 P[EPT];
+  i64 pmax = 0;
+  bool anybad = false;
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) {
+    const int c = c0 + threadIdx.x + k * SILU_CL_THREADS;
+    bool bad;
+    P[k] = silu_p(yr[c], yr[FF + c], lut, bad);
+    anybad |= bad;
+    pmax = imax(pmax, iabs(P[k]));
+  }
+  if (anybad) *flag = 1;
+  pmax = block_reduce<true>(pmax, red);
+  if (threadIdx.x == 0) cta_max = pmax;
+  cluster.sync();
+  i64 rmax = 0;
+#pragma unroll
+  for (int r = 0; r < SILU_CL; ++r) rmax = imax(rmax, *cluster.map_shared_rank(&cta_max, r));
+  const i64 sh = quant_sh(rmax, -2 * FR);
+  if (part == 0 && threadIdx.x == 0) sh_out[row] = sh;
+  const int64_t plane = (int64_t)M * FF;
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) {
+    const int c = c0 + threadIdx.x + k * SILU_CL_THREADS;
+    const int qv = (int)rshc(P[k], sh + 2 * FR);
+    q[row * FF + c] = qv;
+    if (a8) store_limb_planes(a8, plane, row * FF + c, qv);
+  }
+  cluster.sync();                                   // peers may still be reading cta_max
 }
 
 }  // namespace bx

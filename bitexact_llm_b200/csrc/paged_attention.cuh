@@ -611,7 +611,10 @@ exact_attention_tma_kernel(const __grid_constant__ CUtensorMap tmap, const AttnP
 namespace bx {
 
 constexpr int ATT3_STAGE_BYTES = ATT2_STAGE_KEYS * 256;        // 16384: [V0|V1] tile 8 KB + [V2|pad] tile 8 KB
-constexpr int ATT3_NS = 3;
+#ifndef BX_ATT3_NS
+#define BX_ATT3_NS 3
+#endif
+constexpr int ATT3_NS = BX_ATT3_NS;
 constexpr int ATT3_TMEM_COLS = 32;
 
 struct Attn3Small {
@@ -644,12 +647,18 @@ __host__ __device__ constexpr uint32_t umma_idesc_i8_amn(int n) {
   return umma_idesc_i8(n) | (1u << 15);
 }
 
-__global__ void __launch_bounds__(ATT2_THREADS, 3)
+// NW consumer warps (4 or 8) take 8 keys of every stage each: a stage is 8 NW keys. Smaller CTAs (NW = 4) put more
+// independent load streams on an SM.
+template <int NW>
+__global__ void __launch_bounds__(32 * NW + 32, NW == 4 ? 5 : 3)
 exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                           const AttnParams p) {
+  constexpr int KEYS = 8 * NW;                  // keys per stage
+  constexpr int STAGE_BYTES = KEYS * 256;       // [V0|V1] tile + [V2|pad] tile (the K half uses 192 B per key)
+  constexpr int CTHREADS = 32 * NW;             // consumer threads
   extern __shared__ __align__(128) uint8_t att_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att_smem) + 1023) & ~uintptr_t(1023));
-  i64* scores = reinterpret_cast<i64*>(ring + ATT3_NS * ATT3_STAGE_BYTES);   // later, in place: the p-limb tiles
+  i64* scores = reinterpret_cast<i64*>(ring + ATT3_NS * STAGE_BYTES);   // later, in place: the p-limb tiles
   Attn3Small* sm = reinterpret_cast<Attn3Small*>(reinterpret_cast<uint8_t*>(scores) + (size_t)p.chunk_cap * 32);
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -664,17 +673,17 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
   for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[r * p.M + g] + 1);
   kend = imin(kend, (i64)p.nblk * p.bs);
   const i64 per = (kend + CS - 1) / CS;
-  i64 chunk = (per + ATT2_STAGE_KEYS - 1) / ATT2_STAGE_KEYS * ATT2_STAGE_KEYS;
+  i64 chunk = (per + KEYS - 1) / KEYS * KEYS;
   if (chunk > p.chunk_cap) chunk = p.chunk_cap;
   const i64 lo = imin((i64)rank * chunk, kend);
   const i64 hi = imin(lo + chunk, kend);
-  const int nst = (int)((hi - lo + ATT2_STAGE_KEYS - 1) / ATT2_STAGE_KEYS);
+  const int nst = (int)((hi - lo + KEYS - 1) / KEYS);
   const i64 brow = p.rmap ? p.rmap[r] : r;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < ATT3_NS; ++s) {
       mbar_init(&sm->full[s], 1);
-      mbar_init(&sm->empty_k[s], ATT_WARPS);
+      mbar_init(&sm->empty_k[s], NW);
       mbar_init(&sm->empty_v[s], 1);
     }
     mbar_init(&sm->acc_done, 1);
@@ -692,11 +701,11 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
 
-  if (warp == ATT_WARPS) {
+  if (warp == NW) {
     // ---------------- producer warp ----------------
     // Block-table entries are fetched 32 pages at a time (one per lane) and handed out by shuffles, so that issuing a
     // stage never waits for a global load.
-    const int pages_per_stage = ATT2_STAGE_KEYS / p.bs;
+    const int pages_per_stage = KEYS / p.bs;
     const i64 pg0 = lo / p.bs;
     const int npg = (int)((hi - lo + p.bs - 1) / p.bs);
     auto load_bt = [&](int block) -> i64 {
@@ -728,19 +737,19 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
         }
       }
       if (!ok) continue;
-      const i64 key0 = lo + (i64)st * ATT2_STAGE_KEYS;
+      const i64 key0 = lo + (i64)st * KEYS;
       int npages = (int)((hi - key0 + p.bs - 1) / p.bs);
       if (npages > pages_per_stage) npages = pages_per_stage;
       if (lane == 0)
         mbar_arrive_expect_tx(&sm->full[slot], (uint32_t)(npages * p.bs * (sweep ? 256 : ATT2_HALF)));
       __syncwarp();
       if (lane < npages) {
-        uint8_t* st_base = ring + slot * ATT3_STAGE_BYTES;
+        uint8_t* st_base = ring + slot * STAGE_BYTES;
         if (!sweep) {
           tma_load_4d(st_base + lane * p.bs * ATT2_HALF, &tmap_k, &sm->full[slot], 0, 0, h, (int)blk);
         } else {
           tma_load_4d(st_base + lane * p.bs * 128, &tmap_v, &sm->full[slot], 192, 0, h, (int)blk);
-          tma_load_4d(st_base + 8192 + lane * p.bs * 128, &tmap_v, &sm->full[slot], 320, 0, h, (int)blk);
+          tma_load_4d(st_base + KEYS * 128 + lane * p.bs * 128, &tmap_v, &sm->full[slot], 320, 0, h, (int)blk);
         }
       }
     }
@@ -791,9 +800,9 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sm->abort_flag) == 0);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
-      const i64 kb = lo + (i64)st * ATT2_STAGE_KEYS + 8 * warp;
+      const i64 kb = lo + (i64)st * KEYS + 8 * warp;
       if (kb < hi) {
-        const uint8_t* kp = ring + slot * ATT3_STAGE_BYTES + (8 * warp + (lane >> 2)) * ATT2_HALF + 16 * (lane & 3);
+        const uint8_t* kp = ring + slot * STAGE_BYTES + (8 * warp + (lane >> 2)) * ATT2_HALF + 16 * (lane & 3);
         int acc[3][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
         const bool kvalid = kb + (lane >> 2) < hi;
 #pragma unroll
@@ -832,10 +841,10 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     m = imax(m, __shfl_xor_sync(0xffffffffu, m, 2));
     if (lane < 16 && (lane & 3) == 0) sm->wmax[warp][lane >> 2] = m;
   }
-  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
   if (threadIdx.x < 4) {
     i64 m = ATT_NEG;
-    for (int w = 0; w < ATT_WARPS; ++w) m = imax(m, sm->wmax[w][threadIdx.x]);
+    for (int w = 0; w < NW; ++w) m = imax(m, sm->wmax[w][threadIdx.x]);
     sm->cmax[threadIdx.x] = m;
   }
   cluster.sync();
@@ -851,7 +860,7 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
   const i64 rowshift = (gok && p.sh) ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
   i64 den = 0;
   const int ngroups = (int)((hi - lo + 31) / 32);
-  for (int grp = warp; grp < ngroups; grp += ATT_WARPS) {
+  for (int grp = warp; grp < ngroups; grp += NW) {
     i64 sc[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) sc[j] = scores[((i64)grp * 32 + 8 * j + (lane >> 2)) * 4 + g2];
@@ -872,7 +881,7 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     }
   }
   fence_proxy_async_smem();
-  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
 
   // ---- sweep 2, phase B: one thread streams the staged V tiles through tcgen05 ----
   constexpr uint32_t IDESC = umma_idesc_i8_amn(16);
@@ -884,15 +893,15 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sm->abort_flag) == 0);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t vbase = smem_u32(ring + slot * ATT3_STAGE_BYTES);
+      const uint32_t vbase = smem_u32(ring + slot * STAGE_BYTES);
 #pragma unroll
-      for (int kg = 0; kg < 2; ++kg) {
-        const int grp = 2 * st + kg;
+      for (int kg = 0; kg < KEYS / 32; ++kg) {
+        const int grp = (KEYS / 32) * st + kg;
         if (grp < ngroups) {
           const uint64_t bdesc = umma_desc_kmajor_plain(smem_u32(scores) + grp * 1024, 256, 128);
           const uint32_t accum = grp > 0 ? 1u : 0u;
           umma_i8(tmem, umma_desc_sw128(vbase + kg * 4096), bdesc, IDESC, accum);
-          umma_i8(tmem + 16, umma_desc_sw128(vbase + 8192 + kg * 4096), bdesc, IDESC, accum);
+          umma_i8(tmem + 16, umma_desc_sw128(vbase + KEYS * 128 + kg * 4096), bdesc, IDESC, accum);
         }
       }
       umma_commit(&sm->empty_v[slot]);
@@ -936,28 +945,30 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     }
   }
   tc_fence_before();
-  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
   if (warp < 2) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) sm->cnum[g][warp * 32 + lane] = part[g];
   }
-  asm volatile("bar.sync 1, %0;" ::"r"(ATT_THREADS) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
   if (warp >= 2 && warp < 4) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) sm->cnum[g][(warp - 2) * 32 + lane] += part[g];
   }
   if (threadIdx.x < 4) {
     i64 t = 0;
-    for (int w = 0; w < ATT_WARPS; ++w) t += sm->pden[w][threadIdx.x];
+    for (int w = 0; w < NW; ++w) t += sm->pden[w][threadIdx.x];
     sm->cden[threadIdx.x] = t;
   }
   cluster.sync();
   if (rank == 0) {
-    const int g = threadIdx.x >> 6, d = threadIdx.x & 63;
-    if (g < p.M) {
-      i64 s = 0;
-      for (int c = 0; c < CS; ++c) s += cluster.map_shared_rank(&sm->cnum[0][0], c)[g * ATT_HD + d];
-      p.num[(pz * p.M + g) * ATT_HD + d] = s;
+    for (int t = threadIdx.x; t < 4 * ATT_HD; t += CTHREADS) {
+      const int g = t >> 6, d = t & 63;
+      if (g < p.M) {
+        i64 s = 0;
+        for (int c = 0; c < CS; ++c) s += cluster.map_shared_rank(&sm->cnum[0][0], c)[g * ATT_HD + d];
+        p.num[(pz * p.M + g) * ATT_HD + d] = s;
+      }
     }
     if (threadIdx.x < p.M) {
       i64 t = 0;

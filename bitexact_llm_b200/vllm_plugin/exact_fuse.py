@@ -18,10 +18,14 @@ def _norm(m, x, y, ids, gamma, fl, mode, norm, store):
     q = torch.empty(M, D, dtype=torch.int32, device=dev) if norm else None
     sh = torch.empty(M, dtype=torch.long, device=dev) if norm else None
     gm, ge = gamma if gamma is not None else (None, None)
+    planes = torch.empty(3, M, D, dtype=torch.int8, device=dev) if norm else None
     rc = nv.lib().bx_exact_norm(mode, xin.data_ptr(), nv.ptr(y.contiguous() if y is not None else None),
                                 nv.ptr(ids.contiguous() if ids is not None else None), nv.ptr(gm), nv.ptr(ge),
-                                nv.ptr(xo), nv.ptr(q), nv.ptr(sh), None, fl.data_ptr(), M, D, int(norm), nv.stream())
+                                nv.ptr(xo), nv.ptr(q), nv.ptr(sh), nv.ptr(planes), fl.data_ptr(), M, D, int(norm),
+                                nv.stream())
     nv.check(rc, "bx_exact_norm")
+    if norm:
+        q._bx_planes = planes                            # the next fused linear skips its limb-splitting pass
     return (xo if store else x), q, sh
 
 
@@ -67,9 +71,11 @@ def attn_out(m, num, den):
     K2 = m.H * m.HD
     q = torch.empty(N, K2, dtype=torch.int32, device=m.dev)
     sh = torch.empty(N, dtype=torch.long, device=m.dev)
+    planes = torch.empty(3, N, K2, dtype=torch.int8, device=m.dev)
     rc = nv.lib().bx_exact_attn_out(num.contiguous().data_ptr(), den.contiguous().data_ptr(), q.data_ptr(),
-                                    sh.data_ptr(), None, N, K2, m.HD, nv.stream())
+                                    sh.data_ptr(), planes.data_ptr(), N, K2, m.HD, nv.stream())
     nv.check(rc, "bx_exact_attn_out")
+    q._bx_planes = planes
     return q, sh
 
 
@@ -78,7 +84,9 @@ def silu_quant(m, y, lut, fl):
     N, FF = y.shape[0], y.shape[1] // 2
     q = torch.empty(N, FF, dtype=torch.int32, device=m.dev)
     sh = torch.empty(N, dtype=torch.long, device=m.dev)
-    rc = nv.lib().bx_exact_silu_quant(y.contiguous().data_ptr(), lut.data_ptr(), q.data_ptr(), sh.data_ptr(), None,
-                                      fl.data_ptr(), N, FF, nv.stream())
+    planes = torch.empty(3, N, FF, dtype=torch.int8, device=m.dev)
+    rc = nv.lib().bx_exact_silu_quant(y.contiguous().data_ptr(), lut.data_ptr(), q.data_ptr(), sh.data_ptr(),
+                                      planes.data_ptr(), fl.data_ptr(), N, FF, nv.stream())
     nv.check(rc, "bx_exact_silu_quant")
+    q._bx_planes = planes
     return q, sh

@@ -51,6 +51,15 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
                     int8_t* scratch, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
                     void* stream);
 
+/* bx_exact_linear when the activation limb planes already exist (the stage kernels bx_exact_norm,
+ * bx_exact_attn_out and bx_exact_silu_quant write them next to q through their `a8` argument): no splitting pass,
+ * no scratch. planes int8 [3, M, K], 16-byte aligned; q (only read for the sparse residual) may be NULL when cnt is
+ * NULL. Same results as bx_exact_linear. */
+int bx_exact_linear_planes(const int8_t* planes, const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs,
+                           const int64_t* d, const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev,
+                           int R, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
+                           void* stream);
+
 /* bx_exact_linear for callers that must not allocate device memory. It has no counterpart in the reference.
  *
  * Some hosts of this library cannot provide the scratch buffer bx_exact_linear asks for: a plugin that is
@@ -145,8 +154,8 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
  * l2e = round(log2(e) * 2^28) for head_dim 64. Outputs num int64 [R, HKV, M, 64], den int64 [R, HKV, M].
  * nb = number of cache blocks. nblk * bs < 43690. cluster_size: CTAs per (request, head) splitting the keys,
  * 0 = automatic, else 1, 2, 4 or 8. variant: 0 = automatic, 1 = direct-load kernel (any page size / strides),
- * 2 = TMA-staged kernel, 3 = TMA-staged kernel with p.V on tcgen05 / TMEM (2 and 3: page size 8..64 dividing
- * 64, 16-byte aligned strides). None of them changes a result.
+ * 2 = TMA-staged kernel, 3 / 4 = TMA-staged kernel with p.V on tcgen05 / TMEM and 8 / 4 consumer warps per CTA
+ * (2..4: page size 8..64 dividing 64, 16-byte aligned strides; 4: page size <= 32). None of them changes a result.
  * Replaces tri_exact_attn.attend (src/bitexact/vllm_plugin/tri_exact_attn.py:138-165). */
 int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
                        int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,

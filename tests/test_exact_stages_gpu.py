@@ -136,7 +136,7 @@ def test_attention_golden_all_cluster_sizes():
     R = z["attn_q"].shape[0]
     args = (T(z["attn_q"], torch.int32), T(z["attn_sh"]), T(z["attn_qpos"]), T(z["attn_cache"]), T(z["attn_bt"]),
             torch.arange(R, device="cuda"), lut, ox.L2E28)
-    for variant in (1, 2, 3):                                # direct-load, TMA-staged, TMA + tcgen05 p.V
+    for variant in (1, 2, 3, 4):                             # direct-load, TMA-staged, TMA + tcgen05 p.V (8 / 4 warps)
         for ns in (None, 1, 2, 5, 64):
             num, den = tri_exact_attn.attend(*args, nsplit=ns, variant=variant)
             assert np.array_equal(N_(num), z["attn_num"]) and np.array_equal(N_(den), z["attn_den"]), (variant, ns)
@@ -169,7 +169,7 @@ def test_attention_seeded_random_masks_and_padding(lim):
         q = rng.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, M, HD)).astype(np.int64)
         sh = rng.randint(-40, -10, (R, HKV, M)).astype(np.int64)
         wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, rmap, lut_np)
-        for variant, ns in ((1, None), (1, 8), (2, None), (2, 4), (3, None), (3, 1), (3, 4), (3, 8)):
+        for variant, ns in ((1, None), (1, 8), (2, None), (2, 4), (3, None), (3, 4), (4, None), (4, 1), (4, 2), (4, 8)):
             num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), T(rmap), lut,
                                              ox.L2E28, nsplit=ns, variant=variant)
             assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), (R, M, P, variant, ns)
@@ -188,7 +188,7 @@ def test_attention_bound_stress_equal_scores_at_limb_extremes():
     q = np.full((1, HKV, 4, HD), 1 << 22, dtype=np.int64)
     sh = np.full((1, HKV, 4), -30, dtype=np.int64)
     qpos = np.full((1, 4), S - 1, dtype=np.int64)
-    for variant in (1, 2, 3):
+    for variant in (1, 2, 3, 4):
         num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), None,
                                          T(ox.exp2_table()), ox.L2E28, variant=variant)
         assert int(den.min()) == S << 22 and int(num.min()) == (S << 22) * 8355711 and int(num.max()) == int(num.min())
