@@ -292,6 +292,68 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
   return launched(1);
 }
 
+// Persistent streaming kernel (variants 5: 8 consumer warps, 6: 4 consumer warps). BX_ENOFIT: too few pairs or a
+// context whose scores do not fit beside the ring (the caller falls back to the cluster kernels unless the variant
+// was asked for explicitly).
+constexpr int BX_ENOFIT = -100;
+
+static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache,
+                                int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt,
+                                int bt_is_int64, int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut,
+                                int64_t l2e, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
+                                bool forced, void* stream) {
+  const int KEYS = 8 * NW, STAGE = KEYS * 256;
+  const int64_t max_keys = (int64_t)nblk * bs;
+  const int64_t npairs = (int64_t)R * HKV;
+  if (bs > KEYS || KEYS % bs != 0 || 32 % bs != 0) return forced ? BX_EARG : BX_ENOFIT;
+  if (!forced && npairs < 2 * 148) return BX_ENOFIT;
+  const int64_t cap = (max_keys + KEYS - 1) / KEYS * KEYS;
+  const int64_t fixed = 1024 + cap * 32 + (int64_t)sizeof(Attn6Small);
+  int per_sm = NW == 4 ? 4 : 2, ns = 0;
+  for (; per_sm >= 1; --per_sm) {                               // most CTAs per SM that still leave a ring of 4 stages
+    const int64_t budget = 227 * 1024 / per_sm - 1024;
+    ns = (int)((budget - fixed) / STAGE);
+    if (ns >= 4 || (per_sm == 1 && ns >= 3)) break;
+  }
+  if (per_sm < 1) return forced ? BX_EARG : BX_ENOFIT;
+  if (!forced && per_sm < 2) return BX_ENOFIT;                  // one CTA per SM: the cluster kernels stream better
+  if (ns > ATT6_MAXNS) ns = ATT6_MAXNS;
+  const size_t smem = (size_t)fixed + (size_t)ns * STAGE;
+  AttnParams p{q, (const i64*)sh, (const i64*)qpos, cache, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
+               (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, (int)cap, ptab};
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(exact_attention_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             227 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(exact_attention_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             227 * 1024) != cudaSuccess)
+      return BX_ELAUNCH;
+    configured = true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return BX_ELAUNCH;
+  CUtensorMap tk, tv;
+  cuuint64_t dims[4] = {512, (cuuint64_t)bs, (cuuint64_t)HKV, (cuuint64_t)nb};
+  cuuint64_t strides[3] = {(cuuint64_t)sc_bs, (cuuint64_t)sc_h, (cuuint64_t)sc_nb};
+  cuuint32_t boxk[4] = {ATT2_HALF, (cuuint32_t)bs, 1, 1};
+  cuuint32_t boxv[4] = {128, (cuuint32_t)bs, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (fn(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(cache), dims, strides, boxk, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+      fn(&tv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(cache), dims, strides, boxv, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return BX_ELAUNCH;
+  const int64_t grid = npairs < (int64_t)per_sm * 148 ? npairs : (int64_t)per_sm * 148;
+  if (NW == 8)
+    exact_attention_stream_kernel<8><<<(unsigned)grid, 288, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+  else
+    exact_attention_stream_kernel<4><<<(unsigned)grid, 160, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+  if (cudaGetLastError() != cudaSuccess) return BX_ELAUNCH;
+  return launched(1);
+}
+
 static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
                          int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
                          int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e,
@@ -308,7 +370,16 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
   const bool tma_ok = (bs % 8 == 0) && (ATT2_STAGE_KEYS % bs == 0) && sc_bs % 16 == 0 && sc_h % 16 == 0 &&
                       sc_nb % 16 == 0 && sc_bs >= 384 && aligned16(cache);
   if (variant >= 2 && !tma_ok) return BX_EARG;
-  if (variant < 0 || variant > 4 || (variant == 4 && bs > 32)) return BX_EARG;
+  if (variant < 0 || variant > 6 || (variant == 4 && bs > 32)) return BX_EARG;
+  // 5 / 6: persistent streaming kernel (8 / 4 consumer warps); the automatic choice when there are enough pairs
+  if (variant == 5 || (variant == 0 && tma_ok)) {
+    const int rc = run_attention_stream(8, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
+                                           rmap, lut, l2e, ptab, num, den, R, HKV, M, variant == 5, stream);
+    if (rc != BX_ENOFIT) return rc;
+  }
+  if (variant == 6)
+    return run_attention_stream(4, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap,
+                                   lut, l2e, ptab, num, den, R, HKV, M, true, stream);
   // 1 direct loads, 2 TMA-staged, 3 TMA + tcgen05 p.V with 8 consumer warps, 4 the same with 4 consumer warps
   const int kind = variant != 0 ? variant : (tma_ok ? ((bs <= 32 && (int64_t)R * HKV >= 64) ? 4 : 3) : 1);
   const int nw = kind == 4 ? 4 : 8;

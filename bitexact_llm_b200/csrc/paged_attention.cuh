@@ -986,3 +986,341 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 }
 
 }  // namespace bx
+
+// =====================================================================================================================
+// Persistent streaming variant for decode batches with many (request, KV head) pairs and contexts whose scores fit in
+// shared memory: no clusters; every CTA walks a list of pairs and its producer warp keeps the ring of TMA stages
+// full ACROSS pair boundaries (K stages of a pair, its V stages, K stages of the next pair, ...), so the HBM stream
+// of an SM does not stop while the consumer warps run the phases that read no new bytes (row maxima, weight pass,
+// accumulator read-out). One ring and one pair of barriers per slot serve both sweeps: a K stage is released by the
+// NW consumer warps, a V stage by the tcgen05.commit of its MMAs plus NW - 1 arrivals of the issuing thread.
+//
+// V tiles: [V limb 0 | V limb 1] (cache bytes 192..319) and [V limb 1 | V limb 2] (bytes 256..383), both 128-byte
+// swizzled rows, so no byte outside the limbs is fetched; TMEM lanes 0..63 of the second accumulator repeat limb 1
+// and are ignored. The arithmetic is that of the kernel above.
+namespace bx {
+
+constexpr int ATT6_MAXNS = 8;
+
+struct Attn6Small {
+  i64 cnum[4][ATT_HD];
+  i64 pden[ATT_WARPS][4];
+  i64 wmax[ATT_WARPS][4];
+  uint64_t full[ATT6_MAXNS];
+  uint64_t empty[ATT6_MAXNS];
+  uint64_t acc_done;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template <int NW>
+__global__ void __launch_bounds__(32 * NW + 32, NW == 4 ? 4 : 2)
+exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                              const AttnParams p, int NS, int64_t npairs) {
+  constexpr int KEYS = 8 * NW;                  // keys per stage
+  constexpr int STAGE_BYTES = KEYS * 256;       // two V tiles of 128-byte rows (the K sweep uses 192 B per key)
+  constexpr int CTHREADS = 32 * NW;             // consumer threads
+  extern __shared__ __align__(128) uint8_t att_smem[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att_smem) + 1023) & ~uintptr_t(1023));
+  i64* scores = reinterpret_cast<i64*>(ring + (size_t)NS * STAGE_BYTES);   // later, in place: the p-limb tiles
+  Attn6Small* sm = reinterpret_cast<Attn6Small*>(reinterpret_cast<uint8_t*>(scores) + (size_t)p.chunk_cap * 32);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], NW);
+    }
+    mbar_init(&sm->acc_done, 1);
+    sm->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(&sm->tmem_base, ATT3_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(&sm->abort_flag);
+
+  auto keys_of = [&](int64_t pz) -> i64 {
+    const int64_t r = pz / p.HKV;
+    i64 kend = 0;
+    for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[r * p.M + g] + 1);
+    kend = imin(kend, (i64)p.nblk * p.bs);
+    return imin(kend, (i64)p.chunk_cap);
+  };
+
+  if (warp == NW) {
+    // ---------------- producer warp ----------------
+    const int pages_per_stage = KEYS / p.bs;
+    bool ok = true;
+    uint32_t gidx = 0;                                               // stages issued so far, over all pairs
+    for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x) {
+      const int64_t r = pz / p.HKV;
+      const int h = (int)(pz % p.HKV);
+      const i64 hi = keys_of(pz);
+      const int nst = (int)((hi + KEYS - 1) / KEYS);
+      const i64 brow = p.rmap ? p.rmap[r] : r;
+      const int npg = (int)((hi + p.bs - 1) / p.bs);
+      // Block-table entries, 32 pages per fetch (one per lane), handed out by shuffles.
+      auto load_bt = [&](int block) -> i64 {
+        const int rel = block * 32 + lane;
+        if (rel >= npg) return 0;
+        return p.bt64 ? reinterpret_cast<const i64*>(p.bt)[brow * p.sbt + rel]
+                      : (i64) reinterpret_cast<const int32_t*>(p.bt)[brow * p.sbt + rel];
+      };
+      int cur_block = 0;
+      i64 my_bt = load_bt(0);
+      for (int idx = 0; idx < 2 * nst; ++idx, ++gidx) {
+        const int sweep = idx >= nst, st = idx - sweep * nst;
+        const uint32_t slot = gidx % (uint32_t)NS, use = gidx / (uint32_t)NS;
+        const int rel0 = st * pages_per_stage;                       // a stage never straddles a block of 32 pages
+        if (rel0 / 32 != cur_block) {
+          cur_block = rel0 / 32;
+          my_bt = load_bt(cur_block);
+        }
+        const i64 blk = __shfl_sync(0xffffffffu, my_bt, (rel0 + lane) & 31);
+        if (ok && use > 0) ok = mbar_wait(&sm->empty[slot], (use - 1) & 1);
+        ok = ok && (*abort_flag == 0);
+        if (!ok) continue;
+        int npages = npg - rel0;
+        if (npages > pages_per_stage) npages = pages_per_stage;
+        if (lane == 0)
+          mbar_arrive_expect_tx(&sm->full[slot], (uint32_t)(npages * p.bs * (sweep ? 256 : ATT2_HALF)));
+        __syncwarp();
+        if (lane < npages) {
+          uint8_t* st_base = ring + (size_t)slot * STAGE_BYTES;
+          if (!sweep) {
+            tma_load_4d(st_base + lane * p.bs * ATT2_HALF, &tmap_k, &sm->full[slot], 0, 0, h, (int)blk);
+          } else {
+            tma_load_4d(st_base + lane * p.bs * 128, &tmap_v, &sm->full[slot], 192, 0, h, (int)blk);
+            tma_load_4d(st_base + KEYS * 128 + lane * p.bs * 128, &tmap_v, &sm->full[slot], 256, 0, h, (int)blk);
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
+    __syncthreads();                                                 // TMEM release point of the CTA
+    return;
+  }
+
+  // ---------------- consumer warps ----------------
+  bool ok = true;
+  uint32_t gidx = 0;
+  uint32_t item = 0;
+  constexpr uint32_t IDESC = umma_idesc_i8_amn(16);
+  for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x, ++item) {
+    const int64_t r = pz / p.HKV;
+    const i64 hi = keys_of(pz);
+    const int nst = (int)((hi + KEYS - 1) / KEYS);
+
+    uint32_t afrag[2][4];
+    {
+      const int row_lo = lane >> 2;
+      const int g = row_lo & 3;
+      const int limb_lo = row_lo >> 2;
+      const bool hi_used = row_lo < 4;
+      const int32_t* qrow = p.q + (pz * p.M + g) * ATT_HD;
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int d0 = 16 * (lane & 3) + 4 * (2 * t + half);
+          uint32_t wl = 0, wh = 0;
+          if (g < p.M) {
+            const int4 qv = *reinterpret_cast<const int4*>(qrow + d0);
+            const int qe[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              int v = qe[b];
+              const int l0 = split8(v), l1 = split8(v), l2 = split8(v);
+              wl |= (uint32_t)((limb_lo ? l1 : l0) & 255) << (8 * b);
+              wh |= (uint32_t)(l2 & 255) << (8 * b);
+            }
+          }
+          afrag[t][2 * half] = wl;
+          afrag[t][2 * half + 1] = hi_used ? wh : 0u;
+        }
+    }
+
+    // ---- sweep 1: scores ----
+    i64 mymax[2] = {ATT_NEG, ATT_NEG};
+    const i64 qp_s1 = (lane < 16 && (lane >> 2) < p.M) ? p.qpos[r * p.M + (lane >> 2)] : -1;
+    for (int st = 0; st < nst; ++st, ++gidx) {
+      const uint32_t slot = gidx % (uint32_t)NS, use = gidx / (uint32_t)NS;
+      if (ok) ok = mbar_wait(&sm->full[slot], use & 1);
+      ok = ok && (*abort_flag == 0);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        const i64 kb = (i64)st * KEYS + 8 * warp;
+        if (kb < hi) {
+          const uint8_t* kp = ring + (size_t)slot * STAGE_BYTES + (8 * warp + (lane >> 2)) * ATT2_HALF + 16 * (lane & 3);
+          int acc[3][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+          const bool kvalid = kb + (lane >> 2) < hi;
+#pragma unroll
+          for (int j = 0; j < 3; ++j) {
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (kvalid) w = *reinterpret_cast<const uint4*>(kp + j * ATT_HD);
+            mma_s8(acc[j], afrag[0], w.x, w.y);
+            mma_s8(acc[j], afrag[1], w.z, w.w);
+          }
+          i64 slo[2], shi[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            slo[c] = (i64)acc[0][c] + shl((i64)acc[1][c], 8) + shl((i64)acc[2][c], 16);
+            shi[c] = (i64)acc[0][2 + c] + shl((i64)acc[1][2 + c], 8) + shl((i64)acc[2][2 + c], 16);
+          }
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const i64 mid = __shfl_down_sync(0xffffffffu, slo[c], 16);
+            if (lane < 16) {
+              const i64 raw = slo[c] + shl(mid, 8) + shl(shi[c], 16);
+              const i64 kk = kb + (lane & 3) * 2 + c;
+              if (kk < hi) {
+                scores[kk * 4 + (lane >> 2)] = raw;
+                if (kk <= qp_s1) mymax[c] = imax(mymax[c], raw);
+              }
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm->empty[slot]);
+    }
+    {
+      i64 m = imax(mymax[0], mymax[1]);
+      m = imax(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = imax(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      if (lane < 16 && (lane & 3) == 0) sm->wmax[warp][lane >> 2] = m;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
+
+    // ---- sweep 2, phase A: weights, written in place of the scores as p-limb tiles (one warp per 32 keys) ----
+    const int g2 = lane & 3;
+    i64 mx = ATT_NEG;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) mx = imax(mx, sm->wmax[w][g2]);
+    const bool gok = g2 < p.M;
+    const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
+    const i64 rowshift = (gok && p.sh) ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
+    i64 den = 0;
+    const int ngroups = (int)((hi + 31) / 32);
+    for (int grp = warp; grp < ngroups; grp += NW) {
+      i64 sc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sc[j] = scores[((i64)grp * 32 + 8 * j + (lane >> 2)) * 4 + g2];
+      __syncwarp();
+      uint8_t* pt = reinterpret_cast<uint8_t*>(scores) + (size_t)grp * 1024;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kl = 8 * j + (lane >> 2);
+        const i64 key = (i64)grp * 32 + kl;
+        i64 pv = 0;
+        if (key < hi && key <= qp2) pv = attn_weight_any(p, sc[j], mx, rowshift);
+        den += pv;
+        int pr = (int)pv;
+        const int off = (kl >> 4) * 256 + (kl & 15) + g2 * 16;
+        pt[off] = (uint8_t)split8(pr);                                // row g      (limb 0)
+        pt[off + 64] = (uint8_t)split8(pr);                           // row 4 + g  (limb 1)
+        pt[off + 128] = (uint8_t)split8(pr);                          // row 8 + g  (limb 2)
+      }
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
+
+    // ---- sweep 2, phase B: one thread streams the staged V tiles through tcgen05 ----
+    if (threadIdx.x == 0) {
+      bool okb = ok;
+      for (int st = 0; st < nst; ++st) {
+        const uint32_t gi = gidx + (uint32_t)st;
+        const uint32_t slot = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
+        if (okb) okb = mbar_wait(&sm->full[slot], use & 1);
+        okb = okb && (*abort_flag == 0);
+        if (!okb) break;
+        tc_fence_after();
+        const uint32_t vbase = smem_u32(ring + (size_t)slot * STAGE_BYTES);
+#pragma unroll
+        for (int kg = 0; kg < KEYS / 32; ++kg) {
+          const int grp = (KEYS / 32) * st + kg;
+          if (grp < ngroups) {
+            const uint64_t bdesc = umma_desc_kmajor_plain(smem_u32(scores) + grp * 1024, 256, 128);
+            const uint32_t accum = grp > 0 ? 1u : 0u;
+            umma_i8(tmem, umma_desc_sw128(vbase + kg * 4096), bdesc, IDESC, accum);
+            umma_i8(tmem + 16, umma_desc_sw128(vbase + KEYS * 128 + kg * 4096), bdesc, IDESC, accum);
+          }
+        }
+        umma_commit(&sm->empty[slot]);                               // one of the NW arrivals of the slot's phase
+        for (int a = 1; a < NW; ++a) mbar_arrive(&sm->empty[slot]);
+        if (st == nst - 1) umma_commit(&sm->acc_done);
+      }
+      if (!okb) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
+    }
+    __syncwarp();
+    gidx += (uint32_t)nst;
+
+    den += __shfl_xor_sync(0xffffffffu, den, 4);
+    den += __shfl_xor_sync(0xffffffffu, den, 8);
+    den += __shfl_xor_sync(0xffffffffu, den, 16);
+    if (lane < 4) sm->pden[warp][lane] = den;
+
+    // ---- accumulators: first tile lanes 0..63 = (V limb 0, dim), 64..127 = (V limb 1, dim); second tile lanes
+    //      64..127 = (V limb 2, dim). Column 4 i + g = (p limb i, query g). ----
+    i64 part[4] = {0, 0, 0, 0};
+    if (warp < 4) {
+      bool done = ok && nst > 0;
+      if (done) done = mbar_wait(&sm->acc_done, item & 1);
+      done = done && (*abort_flag == 0);
+      done = __all_sync(0xffffffffu, done);
+      if (done) {
+        tc_fence_after();
+        uint32_t d01[16], d12[16];
+        const uint32_t tb = tmem + ((uint32_t)(warp * 32) << 16);
+        tmem_ld16(tb, d01);
+        tmem_ld16(tb + 16, d12);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          i64 a = (i64)(int32_t)d01[g] + shl((i64)(int32_t)d01[4 + g], 8) + shl((i64)(int32_t)d01[8 + g], 16);
+          if (warp >= 2) {
+            const i64 b = (i64)(int32_t)d12[g] + shl((i64)(int32_t)d12[4 + g], 8) + shl((i64)(int32_t)d12[8 + g], 16);
+            a = shl(a, 8) + shl(b, 16);
+          }
+          part[g] = a;
+        }
+      } else if (nst > 0) {
+        ok = false;
+      }
+      tc_fence_before();
+    }
+    if (warp < 2) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) sm->cnum[g][warp * 32 + lane] = part[g];
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");     // cnum, pden written; accumulators and p tiles read
+    if (warp >= 2 && warp < 4) {
+      const int d = (warp - 2) * 32 + lane;
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        if (g < p.M) p.num[(pz * p.M + g) * ATT_HD + d] = sm->cnum[g][d] + part[g];
+    }
+    if (threadIdx.x < p.M) {
+      i64 t = 0;
+      for (int w = 0; w < NW; ++w) t += sm->pden[w][threadIdx.x];
+      p.den[pz * p.M + threadIdx.x] = t;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");     // cnum / pden / wmax are free for the next pair
+  }
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, ATT3_TMEM_COLS);
+  }
+}
+
+}  // namespace bx

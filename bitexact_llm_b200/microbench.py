@@ -2,11 +2,15 @@
 
     python -m bitexact_llm_b200.microbench gemm [--m 1,16,256,4096] [--tile 0] [--iters 20] [--shapes decode|all]
     python -m bitexact_llm_b200.microbench attn [--batch 256] [--ctx 4128] [--iters 10]
+    python -m bitexact_llm_b200.microbench stages [--batch 256] [--iters 10]
 
 gemm: the exact-mode fused linear on the projection shapes of one Llama-3.2-1B layer and the LM head
       (int8-equivalent ops = 2 * 9 * M * N * K; algorithmic bytes = 3 N K + 4 M K + 8 M N).
 attn: exact-mode paged decode attention, 8 KV heads x 4 query heads, head_dim 64, 16-token pages, context lengths
       uniform in [64, 2 ctx - 64] (algorithmic bytes = 384 per key and KV head).
+stages: add + RMSNorm + quant (D 2048: 16 D read + 15 D written per row), SiLU * up + quant (FF 8192: 16 FF read,
+      7 FF written), attention output division (2048 columns: 8 read, 7 written per element) and the seeded
+      Gumbel-max sampler (V 128256: 8 V read per row), on random in-range rows.
 """
 
 import argparse
@@ -75,6 +79,8 @@ def attn(args):
     gen = torch.Generator(device=dev).manual_seed(0)
     lo, hi = 64, max(65, 2 * args.ctx - 64)
     ctx = torch.randint(lo, hi + 1, (B,), generator=gen, device=dev)
+    if args.fixed:
+        ctx = torch.full((B,), args.ctx, device=dev)
     nblk = (int(ctx.max()) + bs) // bs
     nb = 1 + B * nblk
     cache = torch.randint(-128, 128, (nb, HKV, bs, 8 * HD), dtype=torch.int8, device=dev, generator=gen)
@@ -106,15 +112,82 @@ def attn(args):
         torch.cuda.synchronize()
         ms += e0.elapsed_time(e1) / args.iters
     byts = 384.0 * HKV * float(ctx.sum())
-    rec = {"kernel": "exact_attention", "batch": B, "mean_ctx": float(ctx.float().mean()), "us": ms * 1e3,
+    rec = {"kernel": "exact_attention", "variant": args.variant, "cluster": args.cluster, "batch": B, "mean_ctx": float(ctx.float().mean()), "us": ms * 1e3,
            "GBps": byts / ms / 1e6, "bytes": byts}
     print(json.dumps(rec), flush=True)
     return rec
 
 
+def _graph_time(run, nsets, iters, reps=4):
+    """Mean device time of one call: `reps` rounds over `nsets` input sets captured in one CUDA graph (no host gaps;
+    the sets together exceed L2, so every call reads its inputs from HBM)."""
+    for i in range(nsets):
+        run(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            for i in range(nsets):
+                run(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (iters * reps * nsets)
+
+
+def stages(args):
+    from types import SimpleNamespace
+    from .exact.consts import exp2_table, ln_table
+    from .vllm_plugin import exact_fuse
+    from .vllm_plugin.sampler import sample_rows
+    dev, M, D, FF, V = "cuda", args.batch, 2048, 8192, 128256
+    gen = torch.Generator(device=dev).manual_seed(0)
+    fl = torch.zeros(1, dtype=torch.int32, device=dev)
+    m = SimpleNamespace(D=D, H=32, HKV=8, HD=64, dev=dev, exp2=exp2_table(dev))
+    R = lambda lo, hi, *shape: torch.randint(lo, hi, shape, dtype=torch.long, device=dev, generator=gen)
+    gamma = (R(1 << 22, 1 << 24, D), R(-24, -20, D))
+    lnt = ln_table(device=dev)
+
+    def sets(n, make):
+        return [make() for _ in range(n)]
+    out = []
+
+    def report(name, ms, byts):
+        rec = {"kernel": name, "rows": M, "us": ms * 1e3, "GBps": byts / ms / 1e6}
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+
+    n = max(2, (160 << 20) // (16 * M * D) + 1)
+    xs = sets(n, lambda: (R(-(1 << 30), 1 << 30, M, D), R(-(1 << 28), 1 << 28, M, D)))
+    report("add_norm", _graph_time(lambda i: exact_fuse.add_norm(m, xs[i][1], xs[i][0], gamma, fl), n, args.iters),
+           31.0 * M * D)
+    del xs
+    n = max(2, (160 << 20) // (16 * M * FF) + 1)
+    ys = sets(n, lambda: R(-(1 << 27), 1 << 27, M, 2 * FF))
+    report("silu_quant", _graph_time(lambda i: exact_fuse.silu_quant(m, ys[i], m.exp2, fl), n, args.iters),
+           23.0 * M * FF)
+    del ys
+    n = max(2, (160 << 20) // (8 * M * D) + 1)
+    nd = sets(n, lambda: (R(-(1 << 40), 1 << 40, M, 8, 4, 64), R(1 << 20, 1 << 30, M, 8, 4, 1)))
+    report("attn_out", _graph_time(lambda i: exact_fuse.attn_out(m, nd[i][0], nd[i][1]), n, args.iters),
+           (15.0 + 8.0 / 64) * M * D)
+    del nd
+    n = max(2, (160 << 20) // (8 * M * V) + 1)
+    ls = sets(n, lambda: R(-(1 << 28), 1 << 28, M, V))
+    rows = torch.stack([R(0, 1 << 40, M), R(0, 1000, M), R(1, 9, M), R(1, 9, M)], 1)
+    report("sample", _graph_time(lambda i: sample_rows(ls[i], rows, lnt, 24), n, args.iters), 8.0 * M * V)
+    print(json.dumps({"bound_flag": int(fl)}))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn"])
+    ap.add_argument("what", choices=["gemm", "attn", "stages"])
     ap.add_argument("--m", default="1,16,256,4096")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -123,8 +196,9 @@ def main():
     ap.add_argument("--ctx", type=int, default=4128)
     ap.add_argument("--cluster", type=int, default=0)
     ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--fixed", action="store_true", help="attn: every request has exactly --ctx keys")
     args = ap.parse_args()
-    {"gemm": gemm, "attn": attn}[args.what](args)
+    {"gemm": gemm, "attn": attn, "stages": stages}[args.what](args)
     if nv.device_status() != 0:
         raise SystemExit("device-side wait timed out")
 

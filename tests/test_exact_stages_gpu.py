@@ -136,7 +136,8 @@ def test_attention_golden_all_cluster_sizes():
     R = z["attn_q"].shape[0]
     args = (T(z["attn_q"], torch.int32), T(z["attn_sh"]), T(z["attn_qpos"]), T(z["attn_cache"]), T(z["attn_bt"]),
             torch.arange(R, device="cuda"), lut, ox.L2E28)
-    for variant in (1, 2, 3, 4):                             # direct-load, TMA-staged, TMA + tcgen05 p.V (8 / 4 warps)
+    # direct-load, TMA-staged, TMA + tcgen05 p.V (8 / 4 warps), persistent streaming (8 / 4 warps)
+    for variant in (1, 2, 3, 4, 5, 6):
         for ns in (None, 1, 2, 5, 64):
             num, den = tri_exact_attn.attend(*args, nsplit=ns, variant=variant)
             assert np.array_equal(N_(num), z["attn_num"]) and np.array_equal(N_(den), z["attn_den"]), (variant, ns)
@@ -169,10 +170,43 @@ def test_attention_seeded_random_masks_and_padding(lim):
         q = rng.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, M, HD)).astype(np.int64)
         sh = rng.randint(-40, -10, (R, HKV, M)).astype(np.int64)
         wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, rmap, lut_np)
-        for variant, ns in ((1, None), (1, 8), (2, None), (2, 4), (3, None), (3, 4), (4, None), (4, 1), (4, 2), (4, 8)):
+        for variant, ns in ((1, None), (1, 8), (2, None), (2, 4), (3, None), (3, 4), (4, None), (4, 1), (4, 2), (4, 8), (5, None), (6, None)):
             num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), T(rmap), lut,
                                              ox.L2E28, nsplit=ns, variant=variant)
             assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), (R, M, P, variant, ns)
+
+
+@pytest.mark.parametrize("lim", [8355711, 1 << 10])
+def test_attention_persistent_streaming(lim):
+    """The persistent kernels (a CTA walks many (request, KV head) pairs with one TMA ring): more pairs than CTAs,
+    page sizes 8 / 16 / 32, block tables just wide enough and much wider than the contexts, ragged positions."""
+    from bitexact_llm_b200.vllm_plugin import tri_exact_attn
+    rng = np.random.RandomState(7 + lim % 1000)
+    HKV, HD = 8, 64
+    lut_np = ox.exp2_table()
+    lut = T(lut_np)
+    for bs in (16, 8, 32):
+        nb = 1536 // bs
+        c32 = rng.randint(-lim, lim + 1, (nb, HKV, bs, 2 * HD)).astype(np.int64)
+        planes = np.zeros((nb, HKV, bs, 8 * HD), dtype=np.int8)
+        for part, o in ((c32[..., :HD], 0), (c32[..., HD:], 3)):
+            for i, lo in enumerate(ox.split_limbs(part, 3)[0]):
+                planes[..., (o + i) * HD:(o + i + 1) * HD] = lo.astype(np.int8)
+        planes[..., 6 * HD:] = rng.randint(-128, 128, planes[..., 6 * HD:].shape)
+        for R, M, P, width in [(3, 4, 600, 640), (5, 4, 2040, 2048), (90, 1, 300, 1024), (2, 3, 50, 64), (7, 4, 5, 32),
+                               (80, 4, 544, 544), (3, 2, 100, 4000)]:
+            bt = rng.randint(1, nb, (R + 2, -(-width // bs))).astype(np.int32)
+            rmap = rng.randint(0, R + 2, R).astype(np.int64)
+            qpos = rng.randint(0, P, (R, M)).astype(np.int64)
+            q = rng.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, M, HD)).astype(np.int64)
+            sh = rng.randint(-40, -10, (R, HKV, M)).astype(np.int64)
+            wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, rmap, lut_np)
+            for variant in (5, 6):
+                num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), T(rmap), lut,
+                                                 ox.L2E28, variant=variant)
+                assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), (bs, R, M, P, width, variant)
+    from bitexact_llm_b200 import _native as nv
+    assert nv.device_status() == 0
 
 
 def test_attention_bound_stress_equal_scores_at_limb_extremes():

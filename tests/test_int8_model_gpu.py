@@ -111,7 +111,7 @@ def test_int8_paged_attention_against_oracle():
             qpos = rng.randint(0, P, (R, M)).astype(np.int64)
             q = rng.randint(-lim, lim + 1, (R, HKV, M, HD)).astype(np.int64)
             wnum, wden = o8.paged_attention(q, qpos, planes, bt, np.arange(R), expt)
-            for variant, ns in ((1, None), (2, 2), (3, None), (3, 8)):
+            for variant, ns in ((1, None), (2, 2), (3, None), (3, 8), (5, None), (6, None)):
                 num, den = tri_paged.attend(T(q), T(qpos), T(planes), T(bt), ptab, nsplit=ns, variant=variant)
                 assert np.array_equal(num.cpu().numpy(), wnum) and np.array_equal(den.cpu().numpy(), wden), \
                     (lim, R, M, P, variant, ns)
