@@ -301,13 +301,15 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
                                 int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt,
                                 int bt_is_int64, int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut,
                                 int64_t l2e, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
-                                bool forced, void* stream) {
+                                int min_per_sm, void* stream) {
+  const bool forced = min_per_sm == 0;                          // an explicit variant: any fit will do
   const int KEYS = 8 * NW, STAGE = KEYS * 256;
   const int64_t max_keys = (int64_t)nblk * bs;
   const int64_t npairs = (int64_t)R * HKV;
   if (bs > KEYS || KEYS % bs != 0 || 32 % bs != 0) return forced ? BX_EARG : BX_ENOFIT;
   if (!forced && npairs < 2 * 148) return BX_ENOFIT;
   const int64_t cap = (max_keys + KEYS - 1) / KEYS * KEYS;
+  if (cap / 32 > ATT6_MAXGROUPS) return forced ? BX_EARG : BX_ENOFIT;
   const int64_t fixed = 1024 + cap * 32 + (int64_t)sizeof(Attn6Small);
   int per_sm = NW == 4 ? 4 : 2, ns = 0;
   for (; per_sm >= 1; --per_sm) {                               // most CTAs per SM that still leave a ring of 4 stages
@@ -316,7 +318,7 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
     if (ns >= 4 || (per_sm == 1 && ns >= 3)) break;
   }
   if (per_sm < 1) return forced ? BX_EARG : BX_ENOFIT;
-  if (!forced && per_sm < 2) return BX_ENOFIT;                  // one CTA per SM: the cluster kernels stream better
+  if (!forced && per_sm < min_per_sm) return BX_ENOFIT;
   if (ns > ATT6_MAXNS) ns = ATT6_MAXNS;
   const size_t smem = (size_t)fixed + (size_t)ns * STAGE;
   AttnParams p{q, (const i64*)sh, (const i64*)qpos, cache, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
@@ -347,9 +349,9 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
     return BX_ELAUNCH;
   const int64_t grid = npairs < (int64_t)per_sm * 148 ? npairs : (int64_t)per_sm * 148;
   if (NW == 8)
-    exact_attention_stream_kernel<8><<<(unsigned)grid, 288, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+    exact_attention_stream_kernel<8><<<(unsigned)grid, 320, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
   else
-    exact_attention_stream_kernel<4><<<(unsigned)grid, 160, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+    exact_attention_stream_kernel<4><<<(unsigned)grid, 192, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
   if (cudaGetLastError() != cudaSuccess) return BX_ELAUNCH;
   return launched(1);
 }
@@ -371,15 +373,20 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
                       sc_nb % 16 == 0 && sc_bs >= 384 && aligned16(cache);
   if (variant >= 2 && !tma_ok) return BX_EARG;
   if (variant < 0 || variant > 6 || (variant == 4 && bs > 32)) return BX_EARG;
-  // 5 / 6: persistent streaming kernel (8 / 4 consumer warps); the automatic choice when there are enough pairs
-  if (variant == 5 || (variant == 0 && tma_ok)) {
-    const int rc = run_attention_stream(8, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
-                                           rmap, lut, l2e, ptab, num, den, R, HKV, M, variant == 5, stream);
-    if (rc != BX_ENOFIT) return rc;
+  // 5 / 6: persistent streaming kernel (8 / 4 consumer warps). Automatic choice, by CTAs that fit on an SM beside the
+  // score buffer: four 4-warp CTAs, else two 8-warp CTAs, else two or three 4-warp CTAs; with a single CTA per SM
+  // the cluster kernels below stream better.
+  if (variant == 0 && tma_ok) {
+    const int tries[3][2] = {{4, 4}, {8, 2}, {4, 2}};
+    for (int t = 0; t < 3; ++t) {
+      const int rc = run_attention_stream(tries[t][0], q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64,
+                                          sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, tries[t][1], stream);
+      if (rc != BX_ENOFIT) return rc;
+    }
   }
-  if (variant == 6)
-    return run_attention_stream(4, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap,
-                                   lut, l2e, ptab, num, den, R, HKV, M, true, stream);
+  if (variant == 5 || variant == 6)
+    return run_attention_stream(variant == 5 ? 8 : 4, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64,
+                                sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, 0, stream);
   // 1 direct loads, 2 TMA-staged, 3 TMA + tcgen05 p.V with 8 consumer warps, 4 the same with 4 consumer warps
   const int kind = variant != 0 ? variant : (tma_ok ? ((bs <= 32 && (int64_t)R * HKV >= 64) ? 4 : 3) : 1);
   const int nw = kind == 4 ? 4 : 8;

@@ -994,6 +994,10 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 // of an SM does not stop while the consumer warps run the phases that read no new bytes (row maxima, weight pass,
 // accumulator read-out). One ring and one pair of barriers per slot serve both sweeps: a K stage is released by the
 // NW consumer warps, a V stage by the tcgen05.commit of its MMAs plus NW - 1 arrivals of the issuing thread.
+// A separate warp issues the MMAs: it takes a 32-key group as soon as the group's weights are written (a tagged flag
+// per group, release / acquire), so V stages drain while the rest of the weight pass is still running.
+// Pairs are dealt round robin (pair = block index + k * grid size): handing them out through a global ticket counter
+// was measured and lost more to the extra hand-over per pair than it gained on ragged batches.
 //
 // V tiles: [V limb 0 | V limb 1] (cache bytes 192..319) and [V limb 1 | V limb 2] (bytes 256..383), both 128-byte
 // swizzled rows, so no byte outside the limbs is fetched; TMEM lanes 0..63 of the second accumulator repeat limb 1
@@ -1001,6 +1005,7 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 namespace bx {
 
 constexpr int ATT6_MAXNS = 8;
+constexpr int ATT6_MAXGROUPS = 160;        // 32-key groups per pair (5120 keys)
 
 struct Attn6Small {
   i64 cnum[4][ATT_HD];
@@ -1011,10 +1016,31 @@ struct Attn6Small {
   uint64_t acc_done;
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t ptag[ATT6_MAXGROUPS];           // ordinal + 1 of the pair whose weights the group's p tile holds
 };
 
+__device__ __forceinline__ void flag_release(uint32_t* f, uint32_t v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(f)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t flag_acquire(const uint32_t* f) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(f)) : "memory");
+  return v;
+}
+// Bounded wait for *f == want.
+__device__ __forceinline__ bool flag_wait(const uint32_t* f, uint32_t want) {
+  if (flag_acquire(f) == want) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (flag_acquire(f) == want) return true;
+    if (globaltimer_ns() - t0 > BX_WAIT_NS) return false;
+  }
+}
+
 template <int NW>
-__global__ void __launch_bounds__(32 * NW + 32, NW == 4 ? 4 : 2)
+__global__ void __launch_bounds__(32 * NW + 64, NW == 4 ? 4 : 2)
 exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                               const AttnParams p, int NS, int64_t npairs) {
   constexpr int KEYS = 8 * NW;                  // keys per stage
@@ -1037,6 +1063,7 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
+  for (int i = threadIdx.x; i < ATT6_MAXGROUPS; i += blockDim.x) sm->ptag[i] = 0;
   if (warp == 0) {
     tmem_alloc(&sm->tmem_base, ATT3_TMEM_COLS);
     tmem_relinquish();
@@ -1046,6 +1073,7 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(&sm->abort_flag);
+  constexpr uint32_t IDESC = umma_idesc_i8_amn(16);
 
   auto keys_of = [&](int64_t pz) -> i64 {
     const int64_t r = pz / p.HKV;
@@ -1109,11 +1137,58 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     return;
   }
 
+  if (warp == NW + 1) {
+    // ---------------- MMA warp: one thread streams the staged V tiles through tcgen05 ----------------
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t gidx = 0, item = 0;
+      constexpr int GPS = KEYS / 32;                                 // groups per stage
+      for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x, ++item) {
+        const i64 hi = keys_of(pz);
+        const int nst = (int)((hi + KEYS - 1) / KEYS);
+        const int ngroups = (int)((hi + 31) / 32);
+        gidx += (uint32_t)nst;                                       // the K stages of the pair
+        for (int st = 0; st < nst; ++st, ++gidx) {
+          const uint32_t slot = gidx % (uint32_t)NS, use = gidx / (uint32_t)NS;
+          // The group's weights come first: they exist only after sweep 1 of this pair has consumed every K stage,
+          // so the slot is at most one use behind and the parity wait below cannot mistake an older phase of the
+          // barrier for this one.
+          if (ok) ok = flag_wait(&sm->ptag[GPS * st], item + 1);
+          if (ok) ok = mbar_wait(&sm->full[slot], use & 1);
+          ok = ok && (*abort_flag == 0);
+          if (!ok) continue;
+          const uint32_t vbase = smem_u32(ring + (size_t)slot * STAGE_BYTES);
+#pragma unroll
+          for (int kg = 0; kg < GPS; ++kg) {
+            const int grp = GPS * st + kg;
+            if (grp < ngroups && ok) {
+              if (kg > 0) ok = flag_wait(&sm->ptag[grp], item + 1);
+              if (ok) {
+                tc_fence_after();
+                const uint64_t bdesc = umma_desc_kmajor_plain(smem_u32(scores) + grp * 1024, 256, 128);
+                const uint32_t accum = grp > 0 ? 1u : 0u;
+                umma_i8(tmem, umma_desc_sw128(vbase + kg * 4096), bdesc, IDESC, accum);
+                umma_i8(tmem + 16, umma_desc_sw128(vbase + KEYS * 128 + kg * 4096), bdesc, IDESC, accum);
+              }
+            }
+          }
+          if (!ok) continue;
+          umma_commit(&sm->empty[slot]);                             // one of the NW arrivals of the slot's phase
+          for (int a = 1; a < NW; ++a) mbar_arrive(&sm->empty[slot]);
+          if (st == nst - 1) umma_commit(&sm->acc_done);
+        }
+      }
+      if (!ok) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
+    }
+    __syncwarp();
+    __syncthreads();                                                 // TMEM release point of the CTA
+    return;
+  }
+
   // ---------------- consumer warps ----------------
   bool ok = true;
   uint32_t gidx = 0;
   uint32_t item = 0;
-  constexpr uint32_t IDESC = umma_idesc_i8_amn(16);
   for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x, ++item) {
     const int64_t r = pz / p.HKV;
     const i64 hi = keys_of(pz);
@@ -1200,7 +1275,7 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     }
     asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
 
-    // ---- sweep 2, phase A: weights, written in place of the scores as p-limb tiles (one warp per 32 keys) ----
+    // ---- sweep 2: weights, written in place of the scores as p-limb tiles (one warp per 32 keys) ----
     const int g2 = lane & 3;
     i64 mx = ATT_NEG;
 #pragma unroll
@@ -1229,39 +1304,11 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
         pt[off + 64] = (uint8_t)split8(pr);                           // row 4 + g  (limb 1)
         pt[off + 128] = (uint8_t)split8(pr);                          // row 8 + g  (limb 2)
       }
+      fence_proxy_async_smem();                                       // the tile is read by tcgen05 (async proxy)
+      __syncwarp();
+      if (lane == 0) flag_release(&sm->ptag[grp], item + 1);
     }
-    fence_proxy_async_smem();
-    asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");
-
-    // ---- sweep 2, phase B: one thread streams the staged V tiles through tcgen05 ----
-    if (threadIdx.x == 0) {
-      bool okb = ok;
-      for (int st = 0; st < nst; ++st) {
-        const uint32_t gi = gidx + (uint32_t)st;
-        const uint32_t slot = gi % (uint32_t)NS, use = gi / (uint32_t)NS;
-        if (okb) okb = mbar_wait(&sm->full[slot], use & 1);
-        okb = okb && (*abort_flag == 0);
-        if (!okb) break;
-        tc_fence_after();
-        const uint32_t vbase = smem_u32(ring + (size_t)slot * STAGE_BYTES);
-#pragma unroll
-        for (int kg = 0; kg < KEYS / 32; ++kg) {
-          const int grp = (KEYS / 32) * st + kg;
-          if (grp < ngroups) {
-            const uint64_t bdesc = umma_desc_kmajor_plain(smem_u32(scores) + grp * 1024, 256, 128);
-            const uint32_t accum = grp > 0 ? 1u : 0u;
-            umma_i8(tmem, umma_desc_sw128(vbase + kg * 4096), bdesc, IDESC, accum);
-            umma_i8(tmem + 16, umma_desc_sw128(vbase + KEYS * 128 + kg * 4096), bdesc, IDESC, accum);
-          }
-        }
-        umma_commit(&sm->empty[slot]);                               // one of the NW arrivals of the slot's phase
-        for (int a = 1; a < NW; ++a) mbar_arrive(&sm->empty[slot]);
-        if (st == nst - 1) umma_commit(&sm->acc_done);
-      }
-      if (!okb) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
-    }
-    __syncwarp();
-    gidx += (uint32_t)nst;
+    gidx += (uint32_t)nst;                                            // the V stages belong to the MMA warp
 
     den += __shfl_xor_sync(0xffffffffu, den, 4);
     den += __shfl_xor_sync(0xffffffffu, den, 8);

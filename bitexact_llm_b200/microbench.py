@@ -93,11 +93,13 @@ def attn(args):
     den = torch.empty(B, HKV, G, dtype=torch.long, device=dev)
     st = torch.cuda.current_stream().cuda_stream
 
-    def run():
+    def run(variant=None, outs=None):
+        n_, d_ = outs if outs is not None else (num, den)
         rc = lib.bx_exact_attention(q.data_ptr(), sh.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0], cache.stride(0),
                                     cache.stride(1), cache.stride(2), bs, bt.data_ptr(), 0, bt.stride(0), nblk, None,
-                                    lut.data_ptr(), 387270501, num.data_ptr(), den.data_ptr(), B, HKV, G, HD,
-                                    args.cluster, args.variant, st)
+                                    lut.data_ptr(), 387270501, n_.data_ptr(), d_.data_ptr(), B, HKV, G, HD,
+                                    args.cluster if variant is None else 0, args.variant if variant is None else variant,
+                                    st)
         nv.check(rc, "bx_exact_attention")
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(2):
@@ -111,6 +113,12 @@ def attn(args):
         e1.record()
         torch.cuda.synchronize()
         ms += e0.elapsed_time(e1) / args.iters
+    # every timed variant must give the integers of the direct-load kernel
+    want = (torch.empty_like(num), torch.empty_like(den))
+    run(1, want)
+    torch.cuda.synchronize()
+    if not (torch.equal(num, want[0]) and torch.equal(den, want[1])):
+        raise SystemExit("variant %d differs from the direct-load kernel" % args.variant)
     byts = 384.0 * HKV * float(ctx.sum())
     rec = {"kernel": "exact_attention", "variant": args.variant, "cluster": args.cluster, "batch": B, "mean_ctx": float(ctx.float().mean()), "us": ms * 1e3,
            "GBps": byts / ms / 1e6, "bytes": byts}
