@@ -566,7 +566,7 @@ int bx_pcg_raw(const int64_t* keys, int64_t* out, int n, int V, void* stream) {
 }
 
 static int sample_chunks(int M, int V) {
-  int nch = (2 * 148 + (M > 0 ? M : 1) - 1) / (M > 0 ? M : 1);
+  int nch = (8 * 148 + (M > 0 ? M : 1) - 1) / (M > 0 ? M : 1);       // eight 256-thread CTAs per SM
   const int maxch = (V + 2047) / 2048;
   if (nch > maxch) nch = maxch;
   return nch < 1 ? 1 : nch;

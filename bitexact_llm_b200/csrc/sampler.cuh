@@ -100,6 +100,29 @@ __device__ inline u128 pcg_advance(u128 state, u128 inc, u64 delta) {
   return add128(mul128(acc_mult, state), acc_plus);
 }
 
+// (mult, plus) of `delta` LCG steps at once: state -> mult * state + plus.
+__device__ inline void pcg_jump(u128 inc, u64 delta, u128& mult, u128& plus) {
+  u128 cur_mult = {PCG_MULT_HI, PCG_MULT_LO}, cur_plus = inc;
+  mult = u128{0, 1};
+  plus = u128{0, 0};
+  while (delta) {
+    if (delta & 1) {
+      mult = mul128(mult, cur_mult);
+      plus = add128(mul128(plus, cur_mult), cur_plus);
+    }
+    cur_plus = mul128(add128(cur_mult, u128{0, 1}), cur_plus);
+    cur_mult = mul128(cur_mult, cur_mult);
+    delta >>= 1;
+  }
+}
+
+// XSL-RR output of a state.
+__device__ __forceinline__ u64 pcg_output(u128 state) {
+  const u64 x = state.hi ^ state.lo;
+  const int rot = (int)(state.hi >> 58);
+  return (x >> rot) | (x << ((64 - rot) & 63));
+}
+
 __device__ __forceinline__ u64 pcg_next(u128& state, u128 inc) {
   state = add128(mul128(state, u128{PCG_MULT_HI, PCG_MULT_LO}), inc);
   const u64 x = state.hi ^ state.lo;
@@ -159,25 +182,27 @@ sample_part_kernel(const i64* __restrict__ logits, int64_t ld, const i64* __rest
   const i64 tn = rows[4 * row + 2], td = rows[4 * row + 3];
   const int64_t c0 = (int64_t)chunk * ch;
   const int64_t c1 = c0 + ch < V ? c0 + ch : V;
-  const int run = (ch + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-  const int64_t e0 = c0 + (int64_t)threadIdx.x * run;
-  const int64_t e1 = e0 + run < c1 ? e0 + run : c1;
+  // Thread t takes entries c0 + t, c0 + t + 256, ...: a warp reads 32 consecutive logits, and the generator of the
+  // thread jumps 256 states per entry (one 128-bit multiply-add, the cost of a single step).
+  const int64_t e0 = c0 + threadIdx.x;
   i64 best = (i64)0x8000000000000000ull, bidx = 0x7fffffffffffffffll;
   const i64* lr = logits + row * ld;     // local columns; vocabulary index = voff + column
-  if (e0 < e1) {
+  if (e0 < c1) {
     if (tn == 0) {
-      for (int64_t e = e0; e < e1; ++e) {
+      for (int64_t e = e0; e < c1; e += SAMPLE_THREADS) {
         const i64 v = lr[e];
         if (v > best) { best = v; bidx = voff + e; }
       }
     } else {
-      u128 st, inc;
+      u128 st, inc, jm, jp;
       pcg_seed((u64)rows[4 * row], (u64)rows[4 * row + 1], st, inc);
-      st = pcg_advance(st, inc, (u64)(voff + e0));
+      st = pcg_advance(st, inc, (u64)(voff + e0) + 1);         // the state whose output is the word of entry e0
+      pcg_jump(inc, SAMPLE_THREADS, jm, jp);
       const u64 dv = (u64)(2 * tn);
       const u64 inv = ~0ull / dv;
-      for (int64_t e = e0; e < e1; ++e) {
-        const i64 g = gumbel_q((i64)pcg_next(st, inc), lnt, bits);
+      for (int64_t e = e0; e < c1; e += SAMPLE_THREADS) {
+        const i64 g = gumbel_q((i64)pcg_output(st), lnt, bits);
+        st = add128(mul128(jm, st), jp);
         // rdiv(l * td, tn) = floor((2 l td + tn) / (2 tn))
         const i64 a = 2 * lr[e] * td + tn;
         u64 rem;
