@@ -1,6 +1,9 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use: mbarrier, TMA (cp.async.bulk.tensor),
 // tcgen05 (TMEM allocation, MMA, commit, load) and the fences between the generic and async proxies.
-// Every spin-wait is bounded: it gives up after BX_WAIT_NS nanoseconds and reports failure to the caller.
+// Every spin-wait is bounded: it gives up after BX_WAIT_CYCLES SM clock cycles (about two seconds) and reports
+// failure to the caller. The bound is taken from the SM's own cycle counter: reading it costs a few cycles, while a
+// read of the global nanosecond timer takes a sizeable fraction of a microsecond and, done once per hand-over,
+// halves the rate at which a warp can turn pipeline stages around.
 #pragma once
 
 #include <cuda.h>
@@ -9,7 +12,7 @@
 
 namespace bx {
 
-constexpr unsigned long long BX_WAIT_NS = 2000000000ull;   // upper bound of any single device-side wait
+constexpr long long BX_WAIT_CYCLES = 4000000000ll;         // upper bound of any single device-side wait
 
 __device__ int g_wait_timeouts;   // number of bounded waits that gave up (0 in a healthy run)
 
@@ -65,12 +68,12 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 // Bounded wait for the phase with the given parity to complete. Returns false when the time limit passed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > BX_WAIT_NS) return false;
+    if (clock64() - t0 > BX_WAIT_CYCLES) return false;
   }
 }
 

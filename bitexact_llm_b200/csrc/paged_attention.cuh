@@ -1030,12 +1030,12 @@ __device__ __forceinline__ uint32_t flag_acquire(const uint32_t* f) {
 // Bounded wait for *f == want.
 __device__ __forceinline__ bool flag_wait(const uint32_t* f, uint32_t want) {
   if (flag_acquire(f) == want) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (flag_acquire(f) == want) return true;
-    if (globaltimer_ns() - t0 > BX_WAIT_NS) return false;
+    if (clock64() - t0 > BX_WAIT_CYCLES) return false;
   }
 }
 
