@@ -12,6 +12,7 @@
 #include "elementwise.cuh"
 #include "paged_attention.cuh"
 #include "sampler.cuh"
+#include "unfused.cuh"
 
 namespace {
 
@@ -599,6 +600,39 @@ int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, cons
                     int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream) {
   if (!best) return BX_EARG;
   return run_sample(logits, ld, rows, lnt, scratch, idx, best, M, V_local, v_offset, bits, stream);
+}
+
+int bx_bmm(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t* c, int Z, int M, int N, int K,
+           int64_t saz, int64_t sam, int64_t sak, int64_t sbz, int64_t sbk, int64_t sbn, void* stream) {
+  if (!a || !b || !c || Z < 0 || M < 0 || N < 0 || K < 0 || K >= 43690 || Z > 65535) return BX_EARG;
+  if (Z == 0 || M == 0 || N == 0) return BX_OK;
+  const dim3 grid((N + BMM_T - 1) / BMM_T, (M + BMM_T - 1) / BMM_T, Z);
+  if (grid.y > 65535) return BX_EARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (a_is_int64 && b_is_int64)
+    bmm_kernel<i64, i64><<<grid, 256, 0, st>>>((const i64*)a, (const i64*)b, (i64*)c, M, N, K, saz, sam, sak, sbz, sbk, sbn);
+  else if (a_is_int64)
+    bmm_kernel<i64, int32_t><<<grid, 256, 0, st>>>((const i64*)a, (const int32_t*)b, (i64*)c, M, N, K, saz, sam, sak, sbz, sbk, sbn);
+  else if (b_is_int64)
+    bmm_kernel<int32_t, i64><<<grid, 256, 0, st>>>((const int32_t*)a, (const i64*)b, (i64*)c, M, N, K, saz, sam, sak, sbz, sbk, sbn);
+  else
+    bmm_kernel<int32_t, int32_t><<<grid, 256, 0, st>>>((const int32_t*)a, (const int32_t*)b, (i64*)c, M, N, K, saz, sam, sak, sbz, sbk, sbn);
+  return launched(1);
+}
+
+int bx_exact_epilogue(const int64_t* T, const int64_t* B, const int32_t* q, int64_t ldq, const int32_t* cnt,
+                      const int32_t* ec, const int64_t* ev, int R, const int64_t* d, const int64_t* g,
+                      const int64_t* sh, int64_t* y, int32_t* flag, int M, int N, int checked, void* stream) {
+  if (!T || !d || !g || !sh || !y || !flag || M < 0 || N <= 0) return BX_EARG;
+  if (cnt && (!q || !ec || !ev || R <= 0)) return BX_EARG;
+  if (M == 0) return BX_OK;
+  const int64_t total = (int64_t)M * N;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  epilogue_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const i64*)T, (const i64*)B, q, ldq, cnt, ec,
+                                                                      (const i64*)ev, R, (const i64*)d, (const i64*)g,
+                                                                      (const i64*)sh, (i64*)y, flag, M, N, checked);
+  return launched(1);
 }
 
 int bx_int8_mm(const int8_t* a, const int8_t* w, int32_t* c, int M, int N, int K, int tile_rows, void* stream) {

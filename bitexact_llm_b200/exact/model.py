@@ -15,3 +15,9 @@ class Lin:
         self.N, self.K = self.limbs.shape[1], self.limbs.shape[2]
         self.g, self.d = t("g").to(device).contiguous(), t("d").to(device).contiguous()
         self.rr, self.rc, self.rv = t("rr").to(device), t("rc").to(device), t("rv").to(device)
+
+    def __call__(self, q):
+        """(C, rs, d, g): the exact dense product and the residual, the arguments of `segs.lin_y`
+        (src/bitexact/exact/model.py:61-70)."""
+        from .wmm import residual, wmm
+        return wmm(q, self.limbs), (residual(q, self.rr, self.rc, self.rv, self.N),), self.d, self.g

@@ -212,6 +212,21 @@ int bx_int8_flag_end(int64_t* scr, int32_t* flag, int L, void* stream);
 int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e, int64_t* y,
                  int32_t* flag, int M, int N, int checked, void* stream);
 
+/* ---- unfused entry points of the reference's standalone engine -------------------------------------------
+ * bx_bmm replaces bmm(a, b, na, nb) (src/bitexact/bmm.py:78-102): c[z] = a[z] @ b[z] exactly, a [Z, M, K] and
+ * b [Z, K, N] int32 or int64 with element strides (any layout), c int64 [Z, M, N] contiguous; operands of at most
+ * three limbs (|x| < 2^23) and K < 43690, so that no sum leaves int64.
+ * bx_exact_epilogue replaces segs.lin_y on a dense product (src/bitexact/exact/segs.py:25-32,
+ * exact/wmm.py:132-150): y = round((T 2^d + B) 2^(sh + g - d + 24)) with the lost-bit / range flag; B is a dense
+ * int64 [M, N] residual (NULL: zero) and / or the ELL residual (cnt, ec, ev as in bx_exact_linear) gathered from q.
+ * The dense product T itself (wmm_triton, exact/wmm.py:31-96) is bx_exact_linear with d = 0, g = -24, sh = 0 and no
+ * residual: then y = T. */
+int bx_bmm(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t* c, int Z, int M, int N, int K,
+           int64_t saz, int64_t sam, int64_t sak, int64_t sbz, int64_t sbk, int64_t sbn, void* stream);
+int bx_exact_epilogue(const int64_t* T, const int64_t* B, const int32_t* q, int64_t ldq, const int32_t* cnt,
+                      const int32_t* ec, const int64_t* ev, int R, const int64_t* d, const int64_t* g,
+                      const int64_t* sh, int64_t* y, int32_t* flag, int M, int N, int checked, void* stream);
+
 /* ---- integer sampler ------------------------------------------------------------------------------------
  * Raw PCG64 words of numpy's default_rng([20261022, seed, t]): keys int64 [n, 2] -> out int64 [n, V].
  * Replaces gpu_pcg.raw_rows (src/bitexact/vllm_plugin/gpu_pcg.py:94-108; CPU: src/bitexact/sampling.py:27-37). */

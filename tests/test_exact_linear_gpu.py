@@ -115,3 +115,33 @@ def test_strided_rows_and_empty_batch():
     want = ox.linear(q.cpu().numpy(), sh.cpu().numpy(), dec, checked=False)
     assert np.array_equal(y.cpu().numpy(), want)
     assert fl(q[:0], sh[:0], flag).shape == (0, N)
+
+
+def test_unfused_linear_api_and_bmm():
+    """Lin.__call__ + segs.lin_y (dense product, residual and epilogue as separate calls), wmm, and the exact batched
+    product bmm give the integers of the fused kernel / of int64 numpy."""
+    from bitexact_llm_b200.bmm import bmm
+    from bitexact_llm_b200.exact import segs, wmm
+    z = np.load(os.path.join(GOLD, "exact_ops.npz"))
+    dec = {k: z["lin_" + k] for k in ("limbs", "g", "d", "rr", "rc", "rv")}
+    fl = _lin(dec)
+    from bitexact_llm_b200.exact.model import Lin
+    lin = Lin({k: torch.from_numpy(v) for k, v in dec.items()}, None, "cuda")
+    q = torch.from_numpy(z["lin_q"].astype(np.int64)).cuda()
+    sh = torch.from_numpy(z["lin_sh"].astype(np.int64)).cuda()
+    C, rs, d, g = lin(q)
+    assert np.array_equal(C.cpu().numpy(), ox.dense_product(z["lin_q"].astype(np.int64), dec["limbs"]))
+    y, flag = segs.lin_y(C, rs, d, g, sh, True)
+    assert np.array_equal(y.cpu().numpy(), z["lin_y"]) and bool(flag) == bool(z["lin_flag"])
+    y2 = segs.lin_y(C, (q, fl.ec.long(), fl.ev), d, g, sh) if fl.has_res else y
+    assert np.array_equal(y2.cpu().numpy(), z["lin_y"])
+    assert wmm.wmm_triton is wmm.wmm
+    rng = np.random.RandomState(5)
+    for Z, M, K, N, da, db in [(3, 5, 64, 70, np.int64, np.int64), (16, 16, 64, 300, np.int32, np.int64),
+                               (2, 130, 515, 64, np.int64, np.int32), (1, 1, 1, 1, np.int32, np.int32)]:
+        a = rng.randint(-(1 << 22), (1 << 22) + 1, (Z, M, K)).astype(da)
+        b = rng.randint(-8355711, 8355712, (Z, N, K)).astype(db)               # stored transposed: strided view
+        bt = torch.from_numpy(b).cuda().transpose(1, 2)
+        c = bmm(torch.from_numpy(a).cuda(), bt)
+        want = np.einsum("zmk,znk->zmn", a.astype(np.int64), b.astype(np.int64))
+        assert np.array_equal(c.cpu().numpy(), want), (Z, M, K, N)
