@@ -140,3 +140,68 @@ def test_int8_decode_matches_reference_hashes():
     toks, shas = generate(eng, ids, 8, 7, 10, seeds=order, lens=lens, perm_seed=3, max_len=64)
     for b, i in enumerate(order):
         assert toks[b].tolist() == z[f"p{i}_t07_tok"].tolist() and shas[b] == z[f"p{i}_t07_sha"].tolist(), b
+
+
+def test_int8_prefill_tiles_and_head_shims():
+    """tri_prefill.attend writes, for the tokens of its tiles, the rows tri_paged.attend gives them one by one;
+    tri_sample.head / noisy and tri_logits.argmax_float give the oracle's logits, first argmax and tokens."""
+    from bitexact_llm_b200.exact.consts import ln_table
+    from bitexact_llm_b200.vllm_plugin import tri_logits, tri_paged, tri_prefill, tri_sample
+    rng = np.random.RandomState(11)
+    nb, bs, HKV, G, HD = 64, 16, 8, 4, 64
+    expt = o8.exp_table()
+    ptab = T(o8.weight_table(expt), torch.int32)
+    lim = 1 << 13
+    c32 = rng.randint(-lim, lim + 1, (nb, HKV, bs, 2 * HD)).astype(np.int64)
+    planes = np.zeros((nb, HKV, bs, 8 * HD), dtype=np.int8)
+    for part, o in ((c32[..., :HD], 0), (c32[..., HD:], 3)):
+        for i, lo in enumerate(ox.split_limbs(part, 3)[0]):
+            planes[..., (o + i) * HD:(o + i + 1) * HD] = lo.astype(np.int8)
+    # three prefill requests of 37, 5 and 64 new tokens after 10, 0 and 100 cached ones, and 6 decode tokens in between
+    pre = [(0, 0, 37, 47), (2, 43, 5, 5), (1, 48, 64, 164)]
+    N = 112
+    pos = np.zeros(N, dtype=np.int64)
+    for r, t0, ql, sl in pre:
+        pos[t0:t0 + ql] = np.arange(sl - ql, sl)
+    bt = rng.randint(1, nb, (3, 12)).astype(np.int32)
+    q = rng.randint(-lim, lim + 1, (N, HKV, G, HD)).astype(np.int64)
+    num = torch.full((N, HKV, G, HD), -7, dtype=torch.long, device="cuda")
+    den = torch.full((N, HKV, G, 1), -7, dtype=torch.long, device="cuda")
+    tiles = tri_prefill.tile_table(pre, G).cuda()
+    tri_prefill.attend(T(q), T(pos), T(planes), T(bt), ptab, tiles, num, den)
+    for r, t0, ql, sl in pre:
+        rows = np.arange(t0, t0 + ql)
+        wnum, wden = o8.paged_attention(q[rows], np.repeat(pos[rows][:, None], G, 1), planes, bt, np.full(ql, r), expt)
+        assert np.array_equal(num[t0:t0 + ql].cpu().numpy(), wnum) and np.array_equal(den[t0:t0 + ql].cpu().numpy(), wden)
+    assert int(num[37:43].max()) == -7 and int(den[37:43].min()) == -7          # rows outside the tiles are untouched
+
+    M, V, K = 5, 1000, 64
+    a = rng.randint(-127, 128, (2 * M, K)).astype(np.int8)
+    w = rng.randint(-127, 128, (V, K)).astype(np.int8)
+    c = a.astype(np.int64) @ w.astype(np.int64).T
+    mul = rng.randint(1 << 20, 1 << 24, V).astype(np.int64)
+    mant = rng.randint(1 << 23, 1 << 24, M).astype(np.int64)
+    e = rng.randint(-6, 2, M).astype(np.int64)
+    fmsh = 14
+    want, _ = o8.post(c[:M] + (c[M:] << 8), mul, fmsh, mant, e, False)
+    h = tri_sample.Head(T(c.astype(np.int32), torch.int32), T(mul), fmsh, T(mant), T(e), rows=4)
+    assert np.array_equal(h.logits().cpu().numpy(), want[:4])
+    out, y = tri_sample.head(h, "float")
+    assert np.array_equal(y.cpu().numpy(), np.argmax(want[:4], 1))
+    assert np.array_equal(out.cpu().numpy(), want[:4].astype(np.float32) * np.float32(2.0 ** -16))
+    out, y = tri_sample.head(h, "onehot")
+    assert np.array_equal(np.isinf(out.cpu().numpy()).sum(1), np.full(4, V - 1)) and float(out[0, y[0]]) == 0.0
+    assert tri_sample.head(h, "none")[0] is None
+    assert np.array_equal(tri_logits.argmax_float(T(want), mode="none")[1].cpu().numpy(), np.argmax(want, 1))
+    assert np.array_equal(tri_logits.first_argmax(T(want)).cpu().numpy(), np.argmax(want, 1))
+    from oracle import sampler as osamp
+    keys, temps = [(3, 0), (3, 1), (9, 7), (1, 2)], [(7, 10), (0, 1), (13, 10), (1, 1)]
+    st = tri_sample.row_state(keys, temps)
+    lnt = ln_table(device="cuda")
+    vout = torch.zeros(4, V, dtype=torch.float32, device="cuda")
+    tok = tri_sample.noisy(h, st, lnt, out=vout).cpu().numpy()
+    lnt_np = ox.ln_table()
+    for r, ((seed, t), (tn, td)) in enumerate(zip(keys, temps)):
+        g = osamp.gumbel(osamp.raw_words(seed, t, V), lnt_np, 16) if tn else None
+        assert tok[r] == int(osamp.sample(want[r:r + 1], tn, td, g)[0]), r
+        assert float(vout[r, tok[r]]) == 0.0 and int(torch.isinf(vout[r]).sum()) == V - 1
