@@ -603,14 +603,15 @@ exact_attention_tma_kernel(const __grid_constant__ CUtensorMap tmap, const AttnP
 //
 // The contraction of p.V is over KEYS, while the cache rows hold DIMS contiguously. tcgen05 reads an "MN-major"
 // int8 operand directly from shared memory, so the staged V rows need no transposition: the A operand is the V tile
-// [32 keys x 128 bytes] (bytes = limb 0 | limb 1 of the 64 dims; a second tile holds limb 2), loaded by TMA with the
+// [32 keys x 128 bytes] (bytes = limb 0 | limb 1 of the 64 dims; a second tile holds limb 1 | limb 2, so that no byte outside the limbs is
+// fetched: its limb 1 half is computed twice and ignored), loaded by TMA with the
 // 128-byte swizzle; the B operand is the tile of p limbs [16 rows = (limb i, query g)] x [32 keys], K-major, written
 // by the consumer warps. D [128 lanes = (V limb, dim)] x [16 columns = (p limb, query)] accumulates in TMEM over
 // ALL keys of the CTA (|sum| <= keys * 2^14 < 2^31) and is read once at the end, so the per-key work of sweep 2
 // is only the weight function and three byte stores.
 namespace bx {
 
-constexpr int ATT3_STAGE_BYTES = ATT2_STAGE_KEYS * 256;        // 16384: [V0|V1] tile 8 KB + [V2|pad] tile 8 KB
+constexpr int ATT3_STAGE_BYTES = ATT2_STAGE_KEYS * 256;        // 16384: [V0|V1] tile 8 KB + [V1|V2] tile 8 KB
 #ifndef BX_ATT3_NS
 #define BX_ATT3_NS 3
 #endif
@@ -654,7 +655,7 @@ __global__ void __launch_bounds__(32 * NW + 32, NW == 4 ? 5 : 3)
 exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                           const AttnParams p) {
   constexpr int KEYS = 8 * NW;                  // keys per stage
-  constexpr int STAGE_BYTES = KEYS * 256;       // [V0|V1] tile + [V2|pad] tile (the K half uses 192 B per key)
+  constexpr int STAGE_BYTES = KEYS * 256;       // [V0|V1] tile + [V1|V2] tile (the K half uses 192 B per key)
   constexpr int CTHREADS = 32 * NW;             // consumer threads
   extern __shared__ __align__(128) uint8_t att_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att_smem) + 1023) & ~uintptr_t(1023));
@@ -749,7 +750,7 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
           tma_load_4d(st_base + lane * p.bs * ATT2_HALF, &tmap_k, &sm->full[slot], 0, 0, h, (int)blk);
         } else {
           tma_load_4d(st_base + lane * p.bs * 128, &tmap_v, &sm->full[slot], 192, 0, h, (int)blk);
-          tma_load_4d(st_base + KEYS * 128 + lane * p.bs * 128, &tmap_v, &sm->full[slot], 320, 0, h, (int)blk);
+          tma_load_4d(st_base + KEYS * 128 + lane * p.bs * 128, &tmap_v, &sm->full[slot], 256, 0, h, (int)blk);
         }
       }
     }
@@ -916,8 +917,9 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
   den += __shfl_xor_sync(0xffffffffu, den, 16);
   if (lane < 4) sm->pden[warp][lane] = den;
 
-  // ---- read the accumulators: lane L < 64 holds (V limb 0, dim L) and, in the second tile, (V limb 2, dim L);
-  //      lane 64 + L holds (V limb 1, dim L). Column 4 i + g = (p limb i, query g). ----
+  // ---- read the accumulators: first tile lanes 0..63 = (V limb 0, dim), 64..127 = (V limb 1, dim); second tile
+  //      lanes 64..127 = (V limb 2, dim) (its lanes 0..63 repeat limb 1 and are ignored).
+  //      Column 4 i + g = (p limb i, query g). ----
   i64 part[4] = {0, 0, 0, 0};
   if (warp < 4) {
     bool done = ok && nst > 0;
@@ -926,19 +928,17 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     done = __all_sync(0xffffffffu, done);
     if (done) {
       tc_fence_after();
-      uint32_t d01[16], d2[16];
+      uint32_t d01[16], d12[16];
       const uint32_t tb = tmem + ((uint32_t)(warp * 32) << 16);
       tmem_ld16(tb, d01);
-      tmem_ld16(tb + 16, d2);
+      tmem_ld16(tb + 16, d12);
       tmem_ld_wait();
-      const int vl = warp >= 2 ? 1 : 0;                            // V limb of the first tile on this lane
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         i64 a = (i64)(int32_t)d01[g] + shl((i64)(int32_t)d01[4 + g], 8) + shl((i64)(int32_t)d01[8 + g], 16);
-        a = shl(a, 8 * vl);
-        if (warp < 2) {
-          const i64 b = (i64)(int32_t)d2[g] + shl((i64)(int32_t)d2[4 + g], 8) + shl((i64)(int32_t)d2[8 + g], 16);
-          a += shl(b, 16);
+        if (warp >= 2) {
+          const i64 b = (i64)(int32_t)d12[g] + shl((i64)(int32_t)d12[4 + g], 8) + shl((i64)(int32_t)d12[8 + g], 16);
+          a = shl(a, 8) + shl(b, 16);
         }
         part[g] = a;
       }
