@@ -172,45 +172,85 @@ pcg_raw_kernel(const i64* __restrict__ keys, i64* __restrict__ out, int V, int r
 
 // Chunked sampling pass. rows: int64 [M, 4] = seed, t, tn, td (tn == 0: greedy). Each CTA handles vocabulary
 // entries [chunk * ch, chunk * ch + ch) of one row and writes its (max value, first index) pair.
+// Thread t takes entries c0 + t, c0 + t + 256, ...: a warp reads 32 consecutive logits, and the generator of the
+// thread jumps 256 states per entry (one 128-bit multiply-add, the cost of a single step).
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_part_kernel(const i64* __restrict__ logits, int64_t ld, const i64* __restrict__ rows,
                    const i64* __restrict__ lnt, i64* __restrict__ pmax, i64* __restrict__ pidx, int V, int ch,
                    int nch, int bits, i64 voff) {
   __shared__ i64 smax[SAMPLE_THREADS / 32], sidx[SAMPLE_THREADS / 32];
+  __shared__ i64 gtab[41];
   const int64_t row = blockIdx.y;
   const int chunk = blockIdx.x;
   const i64 tn = rows[4 * row + 2], td = rows[4 * row + 3];
   const int64_t c0 = (int64_t)chunk * ch;
   const int64_t c1 = c0 + ch < V ? c0 + ch : V;
-  // Thread t takes entries c0 + t, c0 + t + 256, ...: a warp reads 32 consecutive logits, and the generator of the
-  // thread jumps 256 states per entry (one 128-bit multiply-add, the cost of a single step).
   const int64_t e0 = c0 + threadIdx.x;
   i64 best = (i64)0x8000000000000000ull, bidx = 0x7fffffffffffffffll;
   const i64* lr = logits + row * ld;     // local columns; vocabulary index = voff + column
-  if (e0 < c1) {
-    if (tn == 0) {
-      for (int64_t e = e0; e < c1; e += SAMPLE_THREADS) {
-        const i64 v = lr[e];
-        if (v > best) { best = v; bidx = voff + e; }
+  if (tn == 0) {
+    for (int64_t e = e0; e < c1; e += SAMPLE_THREADS) {
+      const i64 v = lr[e];
+      if (v > best) { best = v; bidx = voff + e; }
+    }
+  } else {
+    // Exact pruning. The noise g is a non-decreasing function of the uniform U within each branch of gumbel_q, so
+    // for 1 - u in (2^-j, 2^-(j-1)] it is at most gtab[j] = g at 1 - u = 2^-j (taken with the same function). An
+    // entry whose scaled logit plus that bound stays below a value some entry of the row already reached cannot be
+    // the first maximum; only the others (a few per cent) pay for the two table logarithms and the division.
+    // The bound every lane prunes with is the warp's best value, refreshed every fourth entry; the comparison is
+    // strict, so equal values (which the first-index rule must see) are always evaluated.
+    if (threadIdx.x >= 1 && threadIdx.x <= 40) {
+      const u64 t = (1ull << 53) - (1ull << (53 - threadIdx.x));
+      gtab[threadIdx.x] = gumbel_q((i64)(t << 11), lnt, bits);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    u128 st, inc, jm, jp;
+    pcg_seed((u64)rows[4 * row], (u64)rows[4 * row + 1], st, inc);
+    st = pcg_advance(st, inc, (u64)(voff + e0) + 1);           // the state whose output is the word of entry e0
+    pcg_jump(inc, SAMPLE_THREADS, jm, jp);
+    const u64 dv = (u64)(2 * tn);
+    const u64 inv = ~0ull / dv;
+    const bool prunable = dv < (1ull << 31);
+    i64 wb = (i64)0x8000000000000000ull;
+    // Four entries per round: their logits are loaded first (independent loads in flight), then each is processed.
+    for (int64_t eb = c0 + (threadIdx.x & ~31); eb < c1; eb += 4 * SAMPLE_THREADS) {
+      i64 lg[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t e = eb + lane + (int64_t)k * SAMPLE_THREADS;
+        lg[k] = e < c1 ? lr[e] : 0;
       }
-    } else {
-      u128 st, inc, jm, jp;
-      pcg_seed((u64)rows[4 * row], (u64)rows[4 * row + 1], st, inc);
-      st = pcg_advance(st, inc, (u64)(voff + e0) + 1);         // the state whose output is the word of entry e0
-      pcg_jump(inc, SAMPLE_THREADS, jm, jp);
-      const u64 dv = (u64)(2 * tn);
-      const u64 inv = ~0ull / dv;
-      for (int64_t e = e0; e < c1; e += SAMPLE_THREADS) {
-        const i64 g = gumbel_q((i64)pcg_output(st), lnt, bits);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t e = eb + lane + (int64_t)k * SAMPLE_THREADS;
+        if (eb + (int64_t)k * SAMPLE_THREADS >= c1) break;       // warp-uniform
+        const bool act = e < c1;
+        const u64 w = pcg_output(st);
         st = add128(mul128(jm, st), jp);
+        const i64 U = iclamp((i64)((w >> 11) & ((1ull << 53) - 1)), UMIN, (1ll << 53) - UMIN);
+        const int j = __clzll((1ll << 53) - U) - 10;           // 1 - u in (2^-j, 2^-(j-1)], 1 <= j <= 40
         // rdiv(l * td, tn) = floor((2 l td + tn) / (2 tn))
-        const i64 a = 2 * lr[e] * td + tn;
-        u64 rem;
-        const u64 qd = uqr_recip((u64)iabs(a), dv, inv, rem);
-        const i64 fq = a < 0 ? -(i64)qd - (rem != 0 ? 1 : 0) : (i64)qd;
-        const i64 v = fq + g;
-        if (v > best) { best = v; bidx = voff + e; }
+        const i64 a = 2 * lg[k] * td + tn;
+        bool pass = act;
+        const i64 lb = imax(best, wb);
+        if (act && prunable && lb > -(1ll << 61)) {
+          const i64 m = lb - gtab[j];                          // floor(a / dv) + gtab[j] < lb  <=>  a < m dv
+          if (m > -(1ll << 31) && m < (1ll << 31)) pass = !(a < m * (i64)dv);
+        }
+        if (__any_sync(0xffffffffu, pass)) {
+          if (pass) {
+            const i64 g = gumbel_q((i64)w, lnt, bits);
+            u64 rem;
+            const u64 qd = uqr_recip((u64)iabs(a), dv, inv, rem);
+            const i64 fq = a < 0 ? -(i64)qd - (rem != 0 ? 1 : 0) : (i64)qd;
+            const i64 v = fq + g;
+            if (v > best) { best = v; bidx = voff + e; }
+          }
+        }
       }
+      wb = warp_max(best);
     }
   }
   // first index of the maximum: larger value wins, then the smaller index

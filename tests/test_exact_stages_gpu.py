@@ -287,3 +287,43 @@ def test_sharded_sampler_pairs_combine_to_the_full_row_token():
     top = best.amax(0, keepdim=True)
     tok = torch.where(best == top, idx, torch.full_like(idx, 1 << 62)).amin(0)
     assert torch.equal(tok, want) and int(tok[2]) in (100, int(want[2]))
+
+
+def test_sampler_pruning_keeps_the_first_maximum():
+    """Rows built to stress the exact pruning of the sampler: flat logits (the noise alone decides), a narrow band,
+    a dominant logit, huge spread, duplicated maxima of logit + noise, 16 and 24 fractional bits, many temperatures,
+    vocabulary sizes that leave ragged warps."""
+    from bitexact_llm_b200.exact.consts import ln_table
+    from bitexact_llm_b200.vllm_plugin import sampler
+    lnt = ln_table(device="cuda")
+    lnt_np = ox.ln_table()
+    rng = np.random.RandomState(21)
+    for V, bits in ((128256, 24), (50001, 16), (777, 24)):
+        rows = []
+        for kind in range(6):
+            if kind == 0:
+                li = np.zeros(V, dtype=np.int64)
+            elif kind == 1:
+                li = rng.randint(-(1 << (bits - 4)), 1 << (bits - 4), V).astype(np.int64)
+            elif kind == 2:
+                li = rng.randint(-(3 << bits), 3 << bits, V).astype(np.int64)
+                li[V // 3] = 40 << bits
+            elif kind == 3:
+                li = rng.randint(-(1 << 40), 1 << 40, V).astype(np.int64)
+            elif kind == 4:
+                li = np.full(V, 5 << bits, dtype=np.int64)
+                li[::7] -= 1
+            else:
+                li = (rng.standard_normal(V) * (1 << bits)).astype(np.int64)
+            rows.append(li)
+        logits = np.stack(rows)
+        seeds = [3, 1 << 33, 5, 6, 7, 123456789]
+        ts = [0, 1, 2, 70000, 4, 5]
+        temps = [(7, 10), (1, 1), (13, 10), (1, 3), (5, 2), (7, 10)]
+        want = []
+        for r in range(len(rows)):
+            raw = np.random.default_rng([osamp.SEED_BASE, seeds[r], ts[r]]).bit_generator.random_raw(V).view(np.int64)
+            g = osamp.gumbel(raw, lnt_np, bits)
+            want.append(int(osamp.sample(logits[r:r + 1], temps[r][0], temps[r][1], g)[0]))
+        tok = sampler.integer_sample(T(logits), seeds, ts, temps, lnt, fr=bits)
+        assert N_(tok).tolist() == want, (V, bits)

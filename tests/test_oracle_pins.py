@@ -184,3 +184,31 @@ def test_golden_int8_linear():
     acc = o8.imm(q, wq)
     y, flag = o8.post(acc, m, fm + 8 - 24, mant, e)
     assert np.array_equal(acc, z["acc"]) and np.array_equal(y, z["y"]) and flag == bool(z["flag"])
+
+
+def test_gumbel_noise_is_monotone_in_the_uniform():
+    """The integer Gumbel noise never decreases when the uniform grows, inside each of its two branches and across
+    every power-of-two boundary of 1 - u: the property the GPU sampler's exact pruning rests on."""
+    from oracle import exact as ox
+    from oracle import sampler as osamp
+    lnt = ox.ln_table()
+    rng = np.random.RandomState(0)
+    for bits in (16, 24):
+        us = [rng.randint(osamp.UMIN, 1 << 53, 400000, dtype=np.int64)]
+        for j in range(1, 41):                                   # both sides of every bucket boundary
+            t = (1 << 53) - (1 << (53 - j))
+            us.append(np.arange(max(t - 300, 1), min(t + 300, (1 << 53) - 1), dtype=np.int64))
+        us.append(np.arange(1, 20000, dtype=np.int64))
+        us.append((1 << 53) - np.arange(1, 20000, dtype=np.int64))
+        us.append((1 << 53) - (1 << 45) + np.arange(-5000, 5000, dtype=np.int64))
+        u = np.unique(np.concatenate(us))
+        g = osamp.gumbel(u << 11, lnt, bits)
+        series = ((1 << 53) - np.clip(u, osamp.UMIN, (1 << 53) - osamp.UMIN)) < (1 << 45)
+        for part in (g[~series], g[series]):                     # monotone inside each branch
+            assert (np.diff(part) >= 0).all()
+        for j in range(1, 41):                                   # and bounded by the value at the bucket's top
+            t = (1 << 53) - (1 << (53 - j))
+            lo = (1 << 53) - (1 << (54 - j)) if j > 1 else 0
+            sel = (u > lo) & (u <= t)
+            gt = osamp.gumbel(np.array([t], dtype=np.int64) << 11, lnt, bits)[0]
+            assert (g[sel] <= gt).all(), j
