@@ -46,6 +46,8 @@ _SIGNATURES = {
     "bx_int8_flag_end": (I, [P, P, I, P]),
     "bx_int8_post": (I, [P, P, L, P, P, P, P, I, I, I, P]),
     "bx_pcg_raw": (I, [P, P, I, I, P]),
+    "bx_exact_silu_prod": (I, [P, P, P, P, P, I, I, P]),
+    "bx_exact_quant_rows": (I, [P, P, I, P, L, P, P, L, I, I, P]),
     "bx_bmm": (I, [P, I, P, I, P, I, I, I, I, L, L, L, L, L, L, P]),
     "bx_exact_epilogue": (I, [P, P, P, L, P, P, P, I, P, P, P, P, P, I, I, I, P]),
     "bx_sample_scratch_bytes": (Z, [I, I]),

@@ -602,6 +602,25 @@ int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, cons
   return run_sample(logits, ld, rows, lnt, scratch, idx, best, M, V_local, v_offset, bits, stream);
 }
 
+int bx_exact_silu_prod(const int64_t* y, const int64_t* lut, int64_t* P, int64_t* rowmax, int32_t* flag, int N, int FFl,
+                       void* stream) {
+  if (!y || !lut || !P || !rowmax || !flag || N < 0 || FFl <= 0) return BX_EARG;
+  if (N == 0) return BX_OK;
+  silu_prod_kernel<512><<<N, 512, 0, (cudaStream_t)stream>>>((const i64*)y, (const i64*)lut, (i64*)P, (i64*)rowmax, flag,
+                                                             FFl);
+  return launched(1);
+}
+
+int bx_exact_quant_rows(const int64_t* P, const int64_t* rowmax, int fbits, int32_t* q, int64_t ldq, int64_t* sh,
+                        int8_t* a8, int64_t plane, int N, int K, void* stream) {
+  if (!P || !rowmax || !q || N < 0 || K <= 0 || ldq < K || fbits < 0 || fbits > 62 || (a8 && plane < (int64_t)N * ldq))
+    return BX_EARG;
+  if (N == 0) return BX_OK;
+  quant_rows_kernel<<<N, 256, 0, (cudaStream_t)stream>>>((const i64*)P, (const i64*)rowmax, fbits, q, ldq, (i64*)sh, a8,
+                                                         plane, K);
+  return launched(1);
+}
+
 int bx_bmm(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t* c, int Z, int M, int N, int K,
            int64_t saz, int64_t sam, int64_t sak, int64_t sbz, int64_t sbk, int64_t sbn, void* stream) {
   if (!a || !b || !c || Z < 0 || M < 0 || N < 0 || K < 0 || K >= 43690 || Z > 65535) return BX_EARG;

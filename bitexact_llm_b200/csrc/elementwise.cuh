@@ -419,4 +419,44 @@ silu_cluster_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, int3
   cluster.sync();                                   // peers may still be reading cta_max
 }
 
+// ---- SiLU * up + quant in two kernels, for a gate / up projection sharded by output column over several GPUs ----
+// silu_prod_kernel: y [N, 2 FFl] (the rank's gate columns, then its up columns) -> P int64 [N, FFl] and the row maximum
+// of |P| over the rank's columns. The ranks then take the integer maximum of the row maxima (an exact all-reduce) and
+// quant_rows_kernel quantises every shard with the same row exponent: the integers of silu_kernel on the full row.
+template <int NT>
+__global__ void __launch_bounds__(NT)
+silu_prod_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, i64* __restrict__ P, i64* __restrict__ rowmax,
+                 int32_t* flag, int FFl) {
+  __shared__ i64 red[33];
+  const int64_t row = blockIdx.x;
+  const i64* yr = y + row * (2 * (int64_t)FFl);
+  i64 pmax = 0;
+  bool anybad = false;
+  for (int c = threadIdx.x; c < FFl; c += NT) {
+    bool bad;
+    const i64 v = silu_p(yr[c], yr[FFl + c], lut, bad);
+    anybad |= bad;
+    pmax = imax(pmax, iabs(v));
+    P[row * FFl + c] = v;
+  }
+  if (anybad) *flag = 1;
+  pmax = block_reduce<true>(pmax, red);
+  if (threadIdx.x == 0) rowmax[row] = pmax;
+}
+
+// q = rshc(P, sh + fbits) with sh = quant_sh(rowmax, -fbits) (exact/ops.py:82-89); also the limb planes of q (optional)
+// with row pitch `ldq` and plane size `plane` elements, so that a rank can write its columns into the full-width planes.
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const i64* __restrict__ P, const i64* __restrict__ rowmax, int fbits, int32_t* __restrict__ q,
+                  int64_t ldq, i64* __restrict__ sh_out, int8_t* __restrict__ a8, int64_t plane, int K) {
+  const int64_t row = blockIdx.x;
+  const i64 sh = quant_sh(rowmax[row], -(i64)fbits);
+  if (threadIdx.x == 0 && sh_out) sh_out[row] = sh;
+  for (int c = threadIdx.x; c < K; c += 256) {
+    const int qv = (int)rshc(P[row * K + c], sh + fbits);
+    q[row * ldq + c] = qv;
+    if (a8) store_limb_planes(a8, plane, row * ldq + c, qv);
+  }
+}
+
 }  // namespace bx

@@ -81,6 +81,63 @@ def combine_argmax(best, idx, group=None):
     return torch.where(b == top, i, torch.full_like(i, big)).amin(0)
 
 
+def allreduce_max(x, group=None):
+    """Integer maximum over the ranks, in place (exact: no arithmetic, only comparisons)."""
+    if dist.get_world_size(group) > 1:
+        dist.all_reduce(x, op=dist.ReduceOp.MAX, group=group)
+    return x
+
+
+def shard_gate_up_constants(c, name, FF, f0, f1):
+    """Constants of the fused gate / up linear `name` (weight rows [0, FF) = gate, [FF, 2 FF) = up) restricted to the
+    intermediate columns [f0, f1): the rank's gate rows followed by its up rows."""
+    a = shard_linear_constants(c, name, f0, f1)
+    b = shard_linear_constants(c, name, FF + f0, FF + f1)
+    n = f1 - f0
+    return {"limbs": torch.cat([a["limbs"], b["limbs"]], 1).contiguous(), "g": torch.cat([a["g"], b["g"]]),
+            "d": torch.cat([a["d"], b["d"]]), "rr": torch.cat([a["rr"], b["rr"] + n]),
+            "rc": torch.cat([a["rc"], b["rc"]]), "rv": torch.cat([a["rv"], b["rv"]])}
+
+
+class ShardedMLP:
+    """Column-sharded MLP of one layer: rank r holds intermediate columns [f0, f1) of gate and up and output columns
+    [d0, d1) of down. Two exchanges per call: the integer maximum of the SiLU row maxima (so that every shard
+    quantises with the row exponent of the full row) with an all-gather of the quantised shard, and the all-gather
+    of the down outputs. Nothing is summed across ranks, so every world size gives the bits of the single GPU."""
+
+    def __init__(self, c, layer, FF, device, group=None):
+        from .exact.model import Lin
+        from .vllm_plugin.exact_gemm import FusedLin
+        self.group, self.FF = group, FF
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.f0, self.f1 = column_bounds(FF, self.world, self.rank, 16)
+        D = c[f"{layer}.wd.limbs"].shape[1]
+        self.d0, self.d1 = column_bounds(D, self.world, self.rank)
+        self.wgu = FusedLin(Lin(shard_gate_up_constants(c, f"{layer}.wgu", FF, self.f0, self.f1), None, device))
+        self.wd = FusedLin(Lin(shard_linear_constants(c, f"{layer}.wd", self.d0, self.d1), None, device))
+
+    def __call__(self, q, sh, lut, flag):
+        """q int32 [M, D], sh int64 [M] (the normalised input, identical on every rank) -> the down projection's
+        output y int64 [M, D] at 24 bits, identical on every rank."""
+        from . import _native as nv
+        lib = nv.lib()
+        M = q.shape[0]
+        FFl = self.f1 - self.f0
+        dev = q.device
+        y = self.wgu(q, sh, flag, False)                                   # [M, 2 FFl]
+        P = torch.empty(M, FFl, dtype=torch.long, device=dev)
+        rmax = torch.empty(M, dtype=torch.long, device=dev)
+        nv.check(lib.bx_exact_silu_prod(y.data_ptr(), lut.data_ptr(), P.data_ptr(), rmax.data_ptr(), flag.data_ptr(), M,
+                                        FFl, nv.stream()), "bx_exact_silu_prod")
+        allreduce_max(rmax, self.group)
+        ql = torch.empty(M, FFl, dtype=torch.int32, device=dev)
+        shq = torch.empty(M, dtype=torch.long, device=dev)
+        nv.check(lib.bx_exact_quant_rows(P.data_ptr(), rmax.data_ptr(), 48, ql.data_ptr(), FFl, shq.data_ptr(), None, 0,
+                                         M, FFl, nv.stream()), "bx_exact_quant_rows")
+        qf = gather_columns(ql, self.group)                               # [M, FF]: every rank needs all of K
+        return gather_columns(self.wd(qf.contiguous(), shq, flag, True), self.group)
+
+
 class ShardedHead:
     """Column-sharded LM head + sampler: rank r holds vocabulary rows [v0, v1) of the LM head; logits never leave
     the shard unless `full_logits` is called (test / hashing mode)."""

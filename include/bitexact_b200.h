@@ -147,6 +147,18 @@ int bx_exact_attn_out(const int64_t* num, const int64_t* den, int32_t* q, int64_
 int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag,
                         int N, int FF, void* stream);
 
+/* SiLU * up + quantisation in two steps, for a gate / up projection sharded by output column over several GPUs (the
+ * reference is single-GPU; same integers as exact_fuse.silu_quant, src/bitexact/vllm_plugin/exact_fuse.py:266-309,
+ * 407-414, on the full row). bx_exact_silu_prod: y int64 [N, 2 FFl] (the rank's gate columns, then its up columns)
+ * -> P int64 [N, FFl] and rowmax int64 [N] = max |P| over the rank's columns. The caller takes the integer maximum
+ * of rowmax over the ranks (an exact all-reduce MAX). bx_exact_quant_rows: q = rshc(P, sh + fbits) with
+ * sh = quant_sh(rowmax, -fbits) (src/bitexact/exact/ops.py:82-89; fbits = 48 after SiLU): q int32 with row pitch
+ * ldq, sh int64 [N] (may be NULL), optional limb planes a8 (plane = elements per plane, row pitch ldq). */
+int bx_exact_silu_prod(const int64_t* y, const int64_t* lut, int64_t* P, int64_t* rowmax, int32_t* flag, int N, int FFl,
+                       void* stream);
+int bx_exact_quant_rows(const int64_t* P, const int64_t* rowmax, int fbits, int32_t* q, int64_t ldq, int64_t* sh,
+                        int8_t* a8, int64_t plane, int N, int K, void* stream);
+
 /* ---- exact-mode paged attention -------------------------------------------------------------------------
  * q int32 [R, HKV, M, 64] (M <= 4), sh int64 [R, HKV, M], qpos int64 [R, M] (key s visible to row i iff
  * s <= qpos[r, i]), cache int8 limb planes [nb, HKV, bs, 512], bt [*, nblk] block table (int32, or int64 when

@@ -327,3 +327,41 @@ def test_sampler_pruning_keeps_the_first_maximum():
             want.append(int(osamp.sample(logits[r:r + 1], temps[r][0], temps[r][1], g)[0]))
         tok = sampler.integer_sample(T(logits), seeds, ts, temps, lnt, fr=bits)
         assert N_(tok).tolist() == want, (V, bits)
+
+
+def test_two_step_silu_equals_the_fused_kernel_for_any_column_split():
+    """bx_exact_silu_prod per column shard + the maximum of the shard row maxima + bx_exact_quant_rows give the q and
+    sh of exact_fuse.silu_quant on the full row (what the column-sharded MLP does across GPUs)."""
+    from bitexact_llm_b200 import _native as nv
+    from bitexact_llm_b200.vllm_plugin import exact_fuse as fz
+    lib = nv.lib()
+    rng = np.random.RandomState(31)
+    lut = T(ox.exp2_table())
+    for N, FF, parts in ((5, 8192, 4), (3, 256, 2), (9, 48, 3)):
+        y = rng.randint(-(1 << 27), 1 << 27, (N, 2 * FF)).astype(np.int64)
+        y[0, :FF] = 0                                                     # a row whose product is all zero
+        y[1, 3] = 70 << 24                                                # beyond the clamp of |g|
+        fl = flag0()
+        q_full, sh_full = fz.silu_quant(model(), T(y), lut, fl)
+        wq, wsh, wflag = ox.silu_quant(y, ox.exp2_table())
+        assert np.array_equal(N_(q_full), wq) and np.array_equal(N_(sh_full), wsh)
+        bounds = np.linspace(0, FF, parts + 1).astype(int)
+        Ps, rmaxes = [], []
+        fl2 = flag0()
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            yl = T(np.concatenate([y[:, a:b], y[:, FF + a:FF + b]], 1))
+            P = torch.empty(N, b - a, dtype=torch.long, device="cuda")
+            rmax = torch.empty(N, dtype=torch.long, device="cuda")
+            nv.check(lib.bx_exact_silu_prod(yl.data_ptr(), lut.data_ptr(), P.data_ptr(), rmax.data_ptr(), fl2.data_ptr(),
+                                            N, b - a, nv.stream()), "prod")
+            Ps.append(P)
+            rmaxes.append(rmax)
+        rmax = torch.stack(rmaxes).amax(0).contiguous()
+        q = torch.empty(N, FF, dtype=torch.int32, device="cuda")
+        planes = torch.zeros(3, N, FF, dtype=torch.int8, device="cuda")
+        sh = torch.empty(N, dtype=torch.long, device="cuda")
+        for (a, b), P in zip(zip(bounds[:-1], bounds[1:]), Ps):
+            nv.check(lib.bx_exact_quant_rows(P.data_ptr(), rmax.data_ptr(), 48, q[:, a:].data_ptr(), FF, sh.data_ptr(),
+                                             planes[:, :, a:].data_ptr(), N * FF, N, int(b - a), nv.stream()), "quant")
+        assert np.array_equal(N_(q), wq) and np.array_equal(N_(sh), wsh) and int(fl2) == int(fl)
+        assert np.array_equal(N_(planes), N_(q_full._bx_planes))

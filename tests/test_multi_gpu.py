@@ -1,5 +1,6 @@
 """Two ranks over NCCL (needs >= 2 GPUs; skipped otherwise): the column-sharded LM head gathers to the single-GPU
-logits bit for bit and the sharded sampler picks the single-GPU tokens; sequence-sharded decode of a batch split
+logits bit for bit and the sharded sampler picks the single-GPU tokens; the column-sharded MLP (gate / up and down
+split by output column, integer all-reduce MAX of the SiLU row maxima) gives the single-GPU output; sequence-sharded decode of a batch split
 over the ranks reproduces the reference's tokens and logits hashes of every sequence."""
 
 import os
@@ -43,6 +44,14 @@ def _worker(rank, world, port, ret):
         ok &= torch.equal(head.full_logits(q, sh, eng.fl), full)
         rows = torch.tensor([[r, 2 * r, (7 if r % 2 else 0), (10 if r % 2 else 1)] for r in range(7)], device=dev)
         ok &= torch.equal(head.sample(q, sh, eng.fl, rows, eng.ln), sampler.sample_rows(full, rows, eng.ln))
+        # (1b) column-sharded MLP of layer 0: the single-GPU wgu -> silu_quant -> wd output on every rank
+        hq = torch.randint(-(1 << 22), (1 << 22) + 1, (6, eng.D), generator=g).to(torch.int32).to(dev)
+        hs = torch.randint(-40, -30, (6,), generator=g).to(dev)
+        ly = eng.layers[0]
+        q1, sh1 = exact_fuse.silu_quant(eng, ly["wgu"](hq, hs, eng.fl, False), eng.exp2, eng.fl)
+        want = ly["wd"](q1, sh1, eng.fl, True)
+        mlp = par.ShardedMLP(c, 0, eng.FF, dev)
+        ok &= torch.equal(mlp(hq, hs, eng.exp2, eng.fl), want)
         # (2) sequence sharding: 4 sequences over 2 ranks, each rank decodes its block
         order = [0, 1, 2, 1]
         lo, hi = par.shard_bounds(len(order), world, rank)

@@ -49,6 +49,25 @@ def _worker(rank, world, port, ret):
             idx = torch.from_numpy(ox.first_argmax(vl) + n0)
             tok = par.combine_argmax(best, idx)
             ok = ok and bool(np.array_equal(tok.numpy(), want)) and int(tok[1]) == 10
+        # column-sharded gate / up: shard constants, local SiLU products, integer all-reduce MAX of the row maxima,
+        # quantisation with the common exponent, all-gather of the shards = the full-row silu_quant
+        FF = 64
+        wgu = (rng.standard_normal((2 * FF, K)) * 0.05).astype(np.float32)
+        dgu = ox.decompose(torch.from_numpy(wgu).to(torch.bfloat16).view(torch.int16).numpy().astype(np.uint16))
+        lut = ox.exp2_table()
+        y_full, _ = ox.linear(q, sh, dgu)
+        wq, wsh, _ = ox.silu_quant(y_full, lut)
+        cgu = {f"0.wgu.{k}": torch.from_numpy(np.ascontiguousarray(v)) for k, v in dgu.items()}
+        f0, f1 = par.column_bounds(FF, world, rank, 16)
+        sgu = {k: v.numpy() for k, v in par.shard_gate_up_constants(cgu, "0.wgu", FF, f0, f1).items()}
+        y_loc, _ = ox.linear(q, sh, sgu)
+        ok = ok and bool(np.array_equal(y_loc, np.concatenate([y_full[:, f0:f1], y_full[:, FF + f0:FF + f1]], 1)))
+        P_loc, _ = ox.silu_mul(y_loc[:, :f1 - f0], y_loc[:, f1 - f0:], lut)
+        rmax = par.allreduce_max(torch.from_numpy(np.abs(P_loc).max(1)))
+        _, sh_c = ox.quant(rmax.numpy()[:, None], -48)
+        q_loc = ox.rshc(P_loc, sh_c[:, None] + 48)
+        qg = par.gather_columns(torch.from_numpy(q_loc))
+        ok = ok and bool(np.array_equal(qg.numpy(), wq)) and bool(np.array_equal(sh_c, wsh))
         # sequence shards partition the batch
         lo, hi = par.shard_bounds(11, world, rank)
         rows = par.gather_rows(torch.arange(lo, lo + 5))                   # equal-size blocks gather in rank order
