@@ -302,17 +302,16 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
                                 int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt,
                                 int bt_is_int64, int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut,
                                 int64_t l2e, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
-                                int min_per_sm, int cs, void* stream) {
+                                int min_per_sm, void* stream) {
   const bool forced = min_per_sm == 0;                          // an explicit variant: any fit will do
   const int KEYS = 8 * NW, STAGE = KEYS * 256;
   const int64_t max_keys = (int64_t)nblk * bs;
   const int64_t npairs = (int64_t)R * HKV;
   if (bs > KEYS || KEYS % bs != 0 || 32 % bs != 0) return forced ? BX_EARG : BX_ENOFIT;
-  if (cs != 1 && cs != 2 && cs != 4 && cs != 8) return BX_EARG;
-  if (!forced && npairs * cs < 2 * 148) return BX_ENOFIT;
-  const int64_t cap = ((max_keys + cs - 1) / cs + KEYS - 1) / KEYS * KEYS;          // keys of one CTA's slice
+  if (!forced && npairs < 2 * 148) return BX_ENOFIT;
+  const int64_t cap = (max_keys + KEYS - 1) / KEYS * KEYS;
   if (cap / 32 > ATT6_MAXGROUPS) return forced ? BX_EARG : BX_ENOFIT;
-  const int64_t fixed = 1024 + cap * 32 + (int64_t)sizeof(Attn6Small) + (cs > 1 ? (int64_t)2 * cs * 4 * ATT_HD * 8 : 0);
+  const int64_t fixed = 1024 + cap * 32 + (int64_t)sizeof(Attn6Small);
   int per_sm = NW == 4 ? 4 : 2, ns = 0;
   for (; per_sm >= 1; --per_sm) {                               // most CTAs per SM that still leave a ring of 4 stages
     const int64_t budget = 227 * 1024 / per_sm - 1024;
@@ -349,25 +348,12 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return BX_ELAUNCH;
-  // whole clusters only: as many as fit on the GPU at once, at most one per pair
-  int64_t clusters = (int64_t)per_sm * 148 / cs;
-  if (clusters > npairs) clusters = npairs;
-  if (clusters < 1) clusters = 1;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(clusters * cs), 1, 1);
-  cfg.blockDim = dim3(32 * NW + 64, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = (cudaStream_t)stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = cs;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const cudaError_t e = NW == 8 ? cudaLaunchKernelEx(&cfg, exact_attention_stream_kernel<8>, tk, tv, p, ns, npairs)
-                                : cudaLaunchKernelEx(&cfg, exact_attention_stream_kernel<4>, tk, tv, p, ns, npairs);
-  if (e != cudaSuccess) return BX_ELAUNCH;
+  const int64_t grid = npairs < (int64_t)per_sm * 148 ? npairs : (int64_t)per_sm * 148;
+  if (NW == 8)
+    exact_attention_stream_kernel<8><<<(unsigned)grid, 320, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+  else
+    exact_attention_stream_kernel<4><<<(unsigned)grid, 192, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+  if (cudaGetLastError() != cudaSuccess) return BX_ELAUNCH;
   return launched(1);
 }
 
@@ -388,26 +374,20 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
                       sc_nb % 16 == 0 && sc_bs >= 384 && aligned16(cache);
   if (variant >= 2 && !tma_ok) return BX_EARG;
   if (variant < 0 || variant > 6 || (variant == 4 && bs > 32)) return BX_EARG;
-  // 5 / 6: persistent streaming kernel (8 / 4 consumer warps), alone or as clusters of `cluster_size` CTAs that split
-  // the keys of a pair. Automatic choice, by CTAs that fit on an SM beside the score buffer: four 4-warp CTAs, else
-  // two 8-warp CTAs, else two or three 4-warp CTAs, each first without clusters, then with clusters of 2, 4, 8 (long
-  // contexts); with a single CTA per SM the cluster kernels below stream better.
+  // 5 / 6: persistent streaming kernel (8 / 4 consumer warps). Automatic choice, by CTAs that fit on an SM beside the
+  // score buffer: four 4-warp CTAs, else two 8-warp CTAs, else two or three 4-warp CTAs; with a single CTA per SM
+  // the cluster kernels below stream better.
   if (variant == 0 && tma_ok) {
     const int tries[3][2] = {{4, 4}, {8, 2}, {4, 2}};
-    for (int c = 1; c <= ATT_MAXCS; c *= 2) {
-      if (cluster_size != 0 && c != cluster_size) continue;
-      for (int t = 0; t < 3; ++t) {
-        const int rc = run_attention_stream(tries[t][0], q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt,
-                                            bt_is_int64, sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M,
-                                            tries[t][1], c, stream);
-        if (rc != BX_ENOFIT) return rc;
-      }
+    for (int t = 0; t < 3; ++t) {
+      const int rc = run_attention_stream(tries[t][0], q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64,
+                                          sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, tries[t][1], stream);
+      if (rc != BX_ENOFIT) return rc;
     }
   }
   if (variant == 5 || variant == 6)
     return run_attention_stream(variant == 5 ? 8 : 4, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64,
-                                sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, 0,
-                                cluster_size == 0 ? 1 : cluster_size, stream);
+                                sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, 0, stream);
   // 1 direct loads, 2 TMA-staged, 3 TMA + tcgen05 p.V with 8 consumer warps, 4 the same with 4 consumer warps
   const int kind = variant != 0 ? variant : (tma_ok ? ((bs <= 32 && (int64_t)R * HKV >= 64) ? 4 : 3) : 1);
   const int nw = kind == 4 ? 4 : 8;

@@ -998,11 +998,6 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 // per group, release / acquire), so V stages drain while the rest of the weight pass is still running.
 // Pairs are dealt round robin (pair = block index + k * grid size): handing them out through a global ticket counter
 // was measured and lost more to the extra hand-over per pair than it gained on ragged batches.
-// Long contexts: the kernel may be launched as clusters of CS CTAs; a cluster walks the pairs together, CTA `rank`
-// owning the rank-th slice of the pair's keys (its scores fit in shared memory again). The two exchanges of a pair
-// (row maxima after sweep 1, partial num / den at the end) go through remote shared-memory stores followed by a
-// remote mbarrier arrival (release at cluster scope) and a bounded local wait, NOT through barrier.cluster: only the
-// consumer warps take part, so the producer and MMA warps still run ahead across pairs.
 //
 // V tiles: [V limb 0 | V limb 1] (cache bytes 192..319) and [V limb 1 | V limb 2] (bytes 256..383), both 128-byte
 // swizzled rows, so no byte outside the limbs is fetched; TMEM lanes 0..63 of the second accumulator repeat limb 1
@@ -1019,46 +1014,10 @@ struct Attn6Small {
   uint64_t full[ATT6_MAXNS];
   uint64_t empty[ATT6_MAXNS];
   uint64_t acc_done;
-  uint64_t xbar[2];                        // cluster form: the CS row-maximum messages of a pair have arrived
-  uint64_t rbar[2];                        // cluster form, rank 0: the CS partial results of a pair have arrived
   uint32_t tmem_base;
   uint32_t abort_flag;
-  i64 peer_max[2][ATT_MAXCS][4];           // written by the peers (pairs alternate between the two buffers)
-  i64 rden[2][ATT_MAXCS][4];
   uint32_t ptag[ATT6_MAXGROUPS];           // ordinal + 1 of the pair whose weights the group's p tile holds
 };
-
-// Address of the same shared-memory object in CTA `rank` of the cluster, a remote 8-byte store, a remote arrival
-// that releases this thread's earlier (remote) stores, and the matching local wait with cluster-scope acquire.
-__device__ __forceinline__ uint32_t cluster_addr(const void* local, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_i64(uint32_t raddr, i64 v) {
-  asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(raddr), "l"(v) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t raddr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(raddr) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
-  const long long t0 = clock64();
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      uint32_t ok;
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t"
-          "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-          "selp.u32 %0, 1, 0, p;\n\t}"
-          : "=r"(ok)
-          : "r"(smem_u32(bar)), "r"(parity)
-          : "memory");
-      if (ok) return true;
-    }
-    if (clock64() - t0 > BX_WAIT_CYCLES) return false;
-  }
-}
 
 __device__ __forceinline__ void flag_release(uint32_t* f, uint32_t v) {
   asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(f)), "r"(v) : "memory");
@@ -1091,21 +1050,12 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att_smem) + 1023) & ~uintptr_t(1023));
   i64* scores = reinterpret_cast<i64*>(ring + (size_t)NS * STAGE_BYTES);   // later, in place: the p-limb tiles
   Attn6Small* sm = reinterpret_cast<Attn6Small*>(reinterpret_cast<uint8_t*>(scores) + (size_t)p.chunk_cap * 32);
-  i64* rpart = reinterpret_cast<i64*>(sm + 1);          // cluster form: [2][CS][4][64] partial numerators (rank 0 reads)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  cg::cluster_group cluster = cg::this_cluster();
-  const int CS = (int)cluster.num_blocks();
-  const int rank = (int)cluster.block_rank();
-  const int64_t first_pair = blockIdx.x / CS, pair_step = gridDim.x / CS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&sm->full[s], 1);
       mbar_init(&sm->empty[s], NW);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&sm->xbar[b], CS);
-      mbar_init(&sm->rbar[b], CS);
     }
     mbar_init(&sm->acc_done, 1);
     sm->abort_flag = 0;
@@ -1121,22 +1071,16 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (CS > 1) cluster.sync();                           // every CTA's barriers exist before a peer may signal them
   const uint32_t tmem = sm->tmem_base;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(&sm->abort_flag);
   constexpr uint32_t IDESC = umma_idesc_i8_amn(16);
 
-  // Keys [lo, lo + n) of pair pz belong to this CTA: the rank-th slice of the visible keys, a multiple of KEYS long
-  // except for the last one.
-  auto slice_of = [&](int64_t pz, i64& lo) -> i64 {
+  auto keys_of = [&](int64_t pz) -> i64 {
     const int64_t r = pz / p.HKV;
     i64 kend = 0;
     for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[r * p.M + g] + 1);
     kend = imin(kend, (i64)p.nblk * p.bs);
-    i64 chunk = ((kend + CS - 1) / CS + KEYS - 1) / KEYS * KEYS;
-    chunk = imin(chunk, (i64)p.chunk_cap);
-    lo = imin((i64)rank * chunk, kend);
-    return imin(lo + chunk, kend) - lo;
+    return imin(kend, (i64)p.chunk_cap);
   };
 
   if (warp == NW) {
@@ -1144,21 +1088,19 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     const int pages_per_stage = KEYS / p.bs;
     bool ok = true;
     uint32_t gidx = 0;                                               // stages issued so far, over all pairs
-    for (int64_t pz = first_pair; pz < npairs; pz += pair_step) {
+    for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x) {
       const int64_t r = pz / p.HKV;
       const int h = (int)(pz % p.HKV);
-      i64 lo;
-      const i64 n = slice_of(pz, lo);
-      const int nst = (int)((n + KEYS - 1) / KEYS);
+      const i64 hi = keys_of(pz);
+      const int nst = (int)((hi + KEYS - 1) / KEYS);
       const i64 brow = p.rmap ? p.rmap[r] : r;
-      const int npg = (int)((n + p.bs - 1) / p.bs);
-      const i64 pg0 = lo / p.bs;
+      const int npg = (int)((hi + p.bs - 1) / p.bs);
       // Block-table entries, 32 pages per fetch (one per lane), handed out by shuffles.
       auto load_bt = [&](int block) -> i64 {
         const int rel = block * 32 + lane;
         if (rel >= npg) return 0;
-        return p.bt64 ? reinterpret_cast<const i64*>(p.bt)[brow * p.sbt + pg0 + rel]
-                      : (i64) reinterpret_cast<const int32_t*>(p.bt)[brow * p.sbt + pg0 + rel];
+        return p.bt64 ? reinterpret_cast<const i64*>(p.bt)[brow * p.sbt + rel]
+                      : (i64) reinterpret_cast<const int32_t*>(p.bt)[brow * p.sbt + rel];
       };
       int cur_block = 0;
       i64 my_bt = load_bt(0);
@@ -1191,17 +1133,20 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
       }
     }
     if (!ok && lane == 0) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
-  } else if (warp == NW + 1) {
+    __syncthreads();                                                 // TMEM release point of the CTA
+    return;
+  }
+
+  if (warp == NW + 1) {
     // ---------------- MMA warp: one thread streams the staged V tiles through tcgen05 ----------------
     if (lane == 0) {
       bool ok = true;
       uint32_t gidx = 0, item = 0;
       constexpr int GPS = KEYS / 32;                                 // groups per stage
-      for (int64_t pz = first_pair; pz < npairs; pz += pair_step, ++item) {
-        i64 lo;
-        const i64 n = slice_of(pz, lo);
-        const int nst = (int)((n + KEYS - 1) / KEYS);
-        const int ngroups = (int)((n + 31) / 32);
+      for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x, ++item) {
+        const i64 hi = keys_of(pz);
+        const int nst = (int)((hi + KEYS - 1) / KEYS);
+        const int ngroups = (int)((hi + 31) / 32);
         gidx += (uint32_t)nst;                                       // the K stages of the pair
         for (int st = 0; st < nst; ++st, ++gidx) {
           const uint32_t slot = gidx % (uint32_t)NS, use = gidx / (uint32_t)NS;
@@ -1236,18 +1181,18 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
       if (!ok) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
     }
     __syncwarp();
-  } else {
+    __syncthreads();                                                 // TMEM release point of the CTA
+    return;
+  }
+
   // ---------------- consumer warps ----------------
   bool ok = true;
   uint32_t gidx = 0;
   uint32_t item = 0;
-  uint32_t ndone = 0;                                                // accumulator hand-overs so far (acc_done phases)
-  for (int64_t pz = first_pair; pz < npairs; pz += pair_step, ++item) {
+  for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x, ++item) {
     const int64_t r = pz / p.HKV;
-    i64 lo;
-    const i64 n = slice_of(pz, lo);
-    const int nst = (int)((n + KEYS - 1) / KEYS);
-    const uint32_t buf = item & 1, xpar = (item >> 1) & 1;
+    const i64 hi = keys_of(pz);
+    const int nst = (int)((hi + KEYS - 1) / KEYS);
 
     uint32_t afrag[2][4];
     {
@@ -1287,11 +1232,11 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
       ok = ok && (*abort_flag == 0);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
-        const i64 kb = (i64)st * KEYS + 8 * warp;                    // relative to lo
-        if (kb < n) {
+        const i64 kb = (i64)st * KEYS + 8 * warp;
+        if (kb < hi) {
           const uint8_t* kp = ring + (size_t)slot * STAGE_BYTES + (8 * warp + (lane >> 2)) * ATT2_HALF + 16 * (lane & 3);
           int acc[3][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
-          const bool kvalid = kb + (lane >> 2) < n;
+          const bool kvalid = kb + (lane >> 2) < hi;
 #pragma unroll
           for (int j = 0; j < 3; ++j) {
             uint4 w = make_uint4(0, 0, 0, 0);
@@ -1311,9 +1256,9 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
             if (lane < 16) {
               const i64 raw = slo[c] + shl(mid, 8) + shl(shi[c], 16);
               const i64 kk = kb + (lane & 3) * 2 + c;
-              if (kk < n) {
+              if (kk < hi) {
                 scores[kk * 4 + (lane >> 2)] = raw;
-                if (lo + kk <= qp_s1) mymax[c] = imax(mymax[c], raw);
+                if (kk <= qp_s1) mymax[c] = imax(mymax[c], raw);
               }
             }
           }
@@ -1335,34 +1280,11 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     i64 mx = ATT_NEG;
 #pragma unroll
     for (int w = 0; w < NW; ++w) mx = imax(mx, sm->wmax[w][g2]);
-    if (CS > 1) {
-      // every CTA sends its four row maxima to every CTA of the cluster (itself included), then takes the maximum
-      if (threadIdx.x == 0) {
-        i64 m4[4];
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          i64 m = ATT_NEG;
-          for (int w = 0; w < NW; ++w) m = imax(m, sm->wmax[w][g]);
-          m4[g] = m;
-        }
-        for (int c = 0; c < CS; ++c) {
-          const uint32_t dst = cluster_addr(&sm->peer_max[buf][rank][0], (uint32_t)c);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) st_cluster_i64(dst + 8 * g, m4[g]);
-          mbar_arrive_cluster(cluster_addr(&sm->xbar[buf], (uint32_t)c));
-        }
-      }
-      if (ok) ok = mbar_wait_cluster(&sm->xbar[buf], xpar);
-      ok = __all_sync(0xffffffffu, ok);
-      mx = ATT_NEG;
-      if (ok)
-        for (int c = 0; c < CS; ++c) mx = imax(mx, sm->peer_max[buf][c][g2]);
-    }
     const bool gok = g2 < p.M;
     const i64 qp2 = gok ? p.qpos[r * p.M + g2] : -1;
     const i64 rowshift = (gok && p.sh) ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
     i64 den = 0;
-    const int ngroups = (int)((n + 31) / 32);
+    const int ngroups = (int)((hi + 31) / 32);
     for (int grp = warp; grp < ngroups; grp += NW) {
       i64 sc[4];
 #pragma unroll
@@ -1374,7 +1296,7 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
         const int kl = 8 * j + (lane >> 2);
         const i64 key = (i64)grp * 32 + kl;
         i64 pv = 0;
-        if (key < n && lo + key <= qp2) pv = attn_weight_any(p, sc[j], mx, rowshift);
+        if (key < hi && key <= qp2) pv = attn_weight_any(p, sc[j], mx, rowshift);
         den += pv;
         int pr = (int)pv;
         const int off = (kl >> 4) * 256 + (kl & 15) + g2 * 16;
@@ -1398,7 +1320,7 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     i64 part[4] = {0, 0, 0, 0};
     if (warp < 4) {
       bool done = ok && nst > 0;
-      if (done) done = mbar_wait(&sm->acc_done, ndone & 1);
+      if (done) done = mbar_wait(&sm->acc_done, item & 1);
       done = done && (*abort_flag == 0);
       done = __all_sync(0xffffffffu, done);
       if (done) {
@@ -1422,69 +1344,25 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
       }
       tc_fence_before();
     }
-    if (nst > 0) ++ndone;
     if (warp < 2) {
 #pragma unroll
       for (int g = 0; g < 4; ++g) sm->cnum[g][warp * 32 + lane] = part[g];
     }
     asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");     // cnum, pden written; accumulators and p tiles read
-    if (CS == 1) {
-      if (warp >= 2 && warp < 4) {
-        const int d = (warp - 2) * 32 + lane;
+    if (warp >= 2 && warp < 4) {
+      const int d = (warp - 2) * 32 + lane;
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          if (g < p.M) p.num[(pz * p.M + g) * ATT_HD + d] = sm->cnum[g][d] + part[g];
-      }
-      if (threadIdx.x < p.M) {
-        i64 t = 0;
-        for (int w = 0; w < NW; ++w) t += sm->pden[w][threadIdx.x];
-        p.den[pz * p.M + threadIdx.x] = t;
-      }
-    } else {
-      // partial num / den of this CTA's keys go to rank 0, which adds the CS parts (integer sums: any order)
-      if (warp >= 2 && warp < 4) {
-        const int d = (warp - 2) * 32 + lane;
-#pragma unroll
-        for (int g = 0; g < 4; ++g)
-          st_cluster_i64(cluster_addr(&rpart[(((size_t)buf * CS + rank) * 4 + g) * ATT_HD + d], 0),
-                         sm->cnum[g][d] + part[g]);
-        asm volatile("fence.acq_rel.cluster;" ::: "memory");
-      }
-      if (threadIdx.x < 4) {
-        i64 t = 0;
-        for (int w = 0; w < NW; ++w) t += sm->pden[w][threadIdx.x];
-        st_cluster_i64(cluster_addr(&sm->rden[buf][rank][threadIdx.x], 0), t);
-        asm volatile("fence.acq_rel.cluster;" ::: "memory");
-      }
-      asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");   // every store of the CTA is issued and fenced
-      if (threadIdx.x == 0) mbar_arrive_cluster(cluster_addr(&sm->rbar[buf], 0));
-      if (rank == 0) {
-        if (ok) ok = mbar_wait_cluster(&sm->rbar[buf], xpar);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-          for (int t = threadIdx.x; t < 4 * ATT_HD; t += CTHREADS) {
-            const int g = t >> 6, d = t & 63;
-            if (g < p.M) {
-              i64 acc = 0;
-              for (int c = 0; c < CS; ++c) acc += rpart[(((size_t)buf * CS + c) * 4 + g) * ATT_HD + d];
-              p.num[(pz * p.M + g) * ATT_HD + d] = acc;
-            }
-          }
-          if (threadIdx.x < p.M) {
-            i64 t = 0;
-            for (int c = 0; c < CS; ++c) t += sm->rden[buf][c][threadIdx.x];
-            p.den[pz * p.M + threadIdx.x] = t;
-          }
-        }
-      }
+      for (int g = 0; g < 4; ++g)
+        if (g < p.M) p.num[(pz * p.M + g) * ATT_HD + d] = sm->cnum[g][d] + part[g];
     }
-    if (!ok) sm->abort_flag = 1;
+    if (threadIdx.x < p.M) {
+      i64 t = 0;
+      for (int w = 0; w < NW; ++w) t += sm->pden[w][threadIdx.x];
+      p.den[pz * p.M + threadIdx.x] = t;
+    }
     asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");     // cnum / pden / wmax are free for the next pair
   }
-  if (!ok && threadIdx.x == 0) atomicAdd(&g_wait_timeouts, 1);
-  }
   __syncthreads();
-  if (CS > 1) cluster.sync();                           // no peer may still write into this CTA's shared memory
   if (warp == 0) {
     __syncwarp();
     tc_fence_after();

@@ -170,7 +170,7 @@ def test_attention_seeded_random_masks_and_padding(lim):
         q = rng.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, M, HD)).astype(np.int64)
         sh = rng.randint(-40, -10, (R, HKV, M)).astype(np.int64)
         wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, rmap, lut_np)
-        for variant, ns in ((1, None), (1, 8), (2, None), (2, 4), (3, None), (3, 4), (4, None), (4, 1), (4, 2), (4, 8), (5, None), (6, None), (5, 4), (6, 8)):
+        for variant, ns in ((1, None), (1, 8), (2, None), (2, 4), (3, None), (3, 4), (4, None), (4, 1), (4, 2), (4, 8), (5, None), (6, None)):
             num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), T(rmap), lut,
                                              ox.L2E28, nsplit=ns, variant=variant)
             assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), (R, M, P, variant, ns)
@@ -202,11 +202,9 @@ def test_attention_persistent_streaming(lim):
             sh = rng.randint(-40, -10, (R, HKV, M)).astype(np.int64)
             wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, rmap, lut_np)
             for variant in (5, 6):
-                for ns in (None, 2, 4, 8):                               # clusters of CTAs that split the keys of a pair
-                    num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), T(rmap), lut,
-                                                     ox.L2E28, nsplit=ns, variant=variant)
-                    assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), \
-                        (bs, R, M, P, width, variant, ns)
+                num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), T(rmap), lut,
+                                                 ox.L2E28, variant=variant)
+                assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), (bs, R, M, P, width, variant)
     from bitexact_llm_b200 import _native as nv
     assert nv.device_status() == 0
 
