@@ -269,6 +269,26 @@ int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_
   if (!y || !lut || !q || !sh || !flag || N < 0 || FF <= 0 || FF > SILU_THREADS * 28) return BX_EARG;
   if (N == 0) return BX_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (FF <= 8 * SILU_P_THREADS && N >= 64) {        // one persistent CTA per SM, 2^-f table in shared memory
+    static bool configured = false;
+    static int sms = 0;
+    const int smem = SILU_TABLE * 8;
+    if (!configured) {
+      int dev = 0;
+      if (cudaFuncSetAttribute(silu_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+              cudaSuccess ||
+          cudaGetDevice(&dev) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return BX_ELAUNCH;
+      configured = true;
+    }
+    // equal rounds: with 256 rows, 128 CTAs of two rows each rather than 148 CTAs of one or two
+    const int rounds = (N + sms - 1) / sms;
+    const int grid = (N + rounds - 1) / rounds;
+    silu_persistent_kernel<8><<<grid, SILU_P_THREADS, smem, st>>>((const i64*)y, (const i64*)lut, q, (i64*)sh, a8, flag,
+                                                                  N, FF);
+    return launched(1);
+  }
   if (FF == SILU_CL * SILU_CL_THREADS * 8 && N <= 4096) {          // decode batches of the 1B model: cluster form
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(SILU_CL * N, 1, 1);

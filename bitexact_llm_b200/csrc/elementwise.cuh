@@ -35,11 +35,13 @@ __device__ __forceinline__ i64 div_round_recip(i64 a, i64 p, u64 r, u64 inv) {
   i64 left = imax(p, 0);
 #pragma unroll
   for (int i = 0; i < NIT; ++i) {
-    const int c = (int)imin(left, 28);
-    const u64 q1 = uqr_recip((u64)R << c, r, inv, rem);
-    Q = shl(Q, c) + (i64)q1;
-    R = (i64)rem;
-    left -= c;
+    if (left > 0) {                                    // a step with nothing left to shift in would change nothing
+      const int c = (int)imin(left, 28);
+      const u64 q1 = uqr_recip((u64)R << c, r, inv, rem);
+      Q = shl(Q, c) + (i64)q1;
+      R = (i64)rem;
+      left -= c;
+    }
   }
   if (p >= 0) return Q + (2 * R >= (i64)r ? 1 : 0);
   const int k = (int)iclamp(-p, 1, 62);
@@ -87,13 +89,14 @@ __device__ __forceinline__ i64 block_reduce(i64 v, i64* buf) {
 
 // 2^-t at out_bits for t >= 0 at 26 fractional bits: table 2^-f at 2^60 (step 2^-14) + linear interpolation
 // (exact/ops.py:108-116).
+template <bool SMEM_TABLE = false>
 __device__ __forceinline__ i64 exp2neg_lut(i64 t, const i64* __restrict__ lut, int out_bits) {
   const i64 n = t >> FT2;
   const i64 f = t & ((1ll << FT2) - 1);
   const int idx = (int)(f >> (FT2 - EXP2_BITS));
   const i64 rr = f & ((1ll << (FT2 - EXP2_BITS)) - 1);
-  const i64 a = __ldg(lut + idx);
-  const i64 b = __ldg(lut + idx + 1);
+  const i64 a = SMEM_TABLE ? lut[idx] : __ldg(lut + idx);
+  const i64 b = SMEM_TABLE ? lut[idx + 1] : __ldg(lut + idx + 1);
   const i64 v = a + rshs<FT2 - EXP2_BITS>((b - a) * rr);
   return rshc(v, (i64)(EXP2_ONE - out_bits) + n);
 }
@@ -320,10 +323,11 @@ attn_out_kernel(const i64* __restrict__ num, const i64* __restrict__ den, int32_
 // ---- SiLU(g) * u + quant(., -2 FR) (segs.silu_y + quant_silu; exact/ops.py:119-130; _silu_kernel) ----
 constexpr int SILU_THREADS = 512;
 
+template <bool SMEM_TABLE = false>
 __device__ __forceinline__ i64 silu_p(i64 g, i64 u, const i64* __restrict__ lut, bool& bad) {
   const i64 a = imin(iabs(g), 64ll << FR);
   const i64 t = rshs<FR + 30 - FT2>(a * L2E30);
-  const i64 E = exp2neg_lut(t, lut, 30);
+  const i64 E = exp2neg_lut<SMEM_TABLE>(t, lut, 30);
   const i64 den = (1ll << 30) + E;
   const i64 nume = g >= 0 ? (1ll << 60) : shl(E, 30);
   const i64 sig = fdiv_pos_est(2 * nume + den, 2 * den);          // rdiv
@@ -417,6 +421,54 @@ silu_cluster_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, int3
     if (a8) store_limb_planes(a8, plane, row * FF + c, qv);
   }
   cluster.sync();                                   // peers may still be reading cta_max
+}
+
+// Persistent form of silu_kernel with the 2^-f table (131 KB) in shared memory: one 1024-thread CTA per SM walks the
+// rows. The table gathers are what the other forms wait for (they miss L1); from shared memory they cost a few
+// cycles, and a CTA fetches the table once for all its rows.
+constexpr int SILU_P_THREADS = 1024;
+constexpr int SILU_TABLE = (1 << EXP2_BITS) + 1;
+
+template <int EPT>
+__global__ void __launch_bounds__(SILU_P_THREADS, 1)
+silu_persistent_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, int32_t* __restrict__ q,
+                       i64* __restrict__ sh_out, int8_t* __restrict__ a8, int32_t* flag, int M, int FF) {
+  extern __shared__ __align__(16) uint8_t silu_smem[];
+  i64* tab = reinterpret_cast<i64*>(silu_smem);
+  __shared__ i64 red[33];
+  for (int i = threadIdx.x; i < SILU_TABLE; i += SILU_P_THREADS) tab[i] = __ldg(lut + i);
+  __syncthreads();
+  const int64_t plane = (int64_t)M * FF;
+  bool anybad = false;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const i64* yr = y + row * (2 * (int64_t)FF);
+    i64 P[EPT];
+    i64 pmax = 0;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      const int c = threadIdx.x + k * SILU_P_THREADS;
+      P[k] = 0;
+      if (c < FF) {
+        bool bad;
+        P[k] = silu_p<true>(yr[c], yr[FF + c], tab, bad);
+        anybad |= bad;
+        pmax = imax(pmax, iabs(P[k]));
+      }
+    }
+    pmax = block_reduce<true>(pmax, red);
+    const i64 sh = quant_sh(pmax, -2 * FR);
+    if (threadIdx.x == 0) sh_out[row] = sh;
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      const int c = threadIdx.x + k * SILU_P_THREADS;
+      if (c < FF) {
+        const int qv = (int)rshc(P[k], sh + 2 * FR);
+        q[row * FF + c] = qv;
+        if (a8) store_limb_planes(a8, plane, row * FF + c, qv);
+      }
+    }
+  }
+  if (anybad) *flag = 1;
 }
 
 // ---- SiLU * up + quant in two kernels, for a gate / up projection sharded by output column over several GPUs ----
