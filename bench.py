@@ -103,8 +103,12 @@ def run_reference(args, rank):
             "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int64 (float64 GEMM of int8 limbs)", "data": "synthetic",
             "impl": "reference",
-            "config": {"workload": "exact-mode decode step, random-init Llama-3.2-1B, CPU sample", "rows": 64,
-                       "context": 640},
+            "config": {"workload": f"BASELINE config 4: random-init Llama-3.2-1B exact-mode decode, "
+                                   f"{args.prompt}-token uniform random prompts, batch {args.batch} per GPU, "
+                                   f"T=0.7 integer Gumbel sampler",
+                       "batch_per_gpu": args.batch, "prompt": args.prompt, "layers": args.layers, "page": 16,
+                       "sample": "one decoder layer + LM head on 64 token rows of this workload per step, scaled to "
+                                 "the full step (see cpu_baseline.sample)"},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}

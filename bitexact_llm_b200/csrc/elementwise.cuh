@@ -48,13 +48,13 @@ __device__ __forceinline__ i64 div_round_recip(i64 a, i64 p, u64 r, u64 inv) {
   return (Q + (1ll << (k - 1))) >> k;
 }
 
-// floor(num / den) for 0 <= num < 2^62, 1 <= den <= 2^33: float64 estimate, exact integer fix-up.
+// floor(num / den) for 0 <= num < 2^62 and 2^31 <= den <= 2^33 (quotient below 2^31): float64 estimate, exact integer
+// fix-up. The conversion of num loses at most 2^8, i.e. 2^-23 of a quotient unit, and the division rounds by less
+// than 2^-22, so the truncated estimate is the floor or one off; one correction each way settles it.
 __device__ __forceinline__ i64 fdiv_pos_est(i64 num, i64 den) {
   i64 q = (i64)((double)num / (double)den);
   i64 r = num - q * den;
   if (r < 0) { q -= 1; r += den; }
-  if (r < 0) { q -= 1; r += den; }
-  if (r >= den) { q += 1; r -= den; }
   if (r >= den) { q += 1; }
   return q;
 }
@@ -325,15 +325,17 @@ constexpr int SILU_THREADS = 512;
 
 template <bool SMEM_TABLE = false>
 __device__ __forceinline__ i64 silu_p(i64 g, i64 u, const i64* __restrict__ lut, bool& bad) {
-  const i64 a = imin(iabs(g), 64ll << FR);
-  const i64 t = rshs<FR + 30 - FT2>(a * L2E30);
+  const i64 a = imin(iabs(g), 64ll << FR);                       // <= 2^30: the product below is 32 x 32 -> 64 bits
+  const i64 t = rshs<FR + 30 - FT2>((i64)((u64)(uint32_t)a * (u64)(uint32_t)L2E30));
   const i64 E = exp2neg_lut<SMEM_TABLE>(t, lut, 30);
   const i64 den = (1ll << 30) + E;
   const i64 nume = g >= 0 ? (1ll << 60) : shl(E, 30);
   const i64 sig = fdiv_pos_est(2 * nume + den, 2 * den);          // rdiv
   const i64 gc = iclamp(g, -(1ll << 32), 1ll << 32);
   const i64 s = rshs<30>(gc * sig);
-  bad = (bitlen(iabs(s)) + bitlen(iabs(u)) > 62) | (iabs(g) > (1ll << 32));
+  const u64 as = (u64)iabs(s), au = (u64)iabs(u);
+  bad = iabs(g) > (1ll << 32);
+  if ((as | au) >> 31) bad |= bitlen((i64)as) + bitlen((i64)au) > 62;      // both below 2^31: 62 bits cannot be passed
   return (i64)((u64)s * (u64)u);
 }
 
