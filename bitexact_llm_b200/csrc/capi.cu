@@ -7,6 +7,7 @@
 
 #include "../../include/bitexact_b200.h"
 #include "exact_linear.cuh"
+#include "exact_linear_splitk.cuh"
 #include "int8_linear.cuh"
 #include "int8_stages.cuh"
 #include "elementwise.cuh"
@@ -72,6 +73,35 @@ int launch_exact(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiPar
   const int m_tiles = (ep.M + TA - 1) / TA;
   const int n_tiles = (ep.N + WROWS - 1) / WROWS;
   exact_linear_kernel<TA><<<m_tiles * n_tiles, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, m_tiles);
+  return launched(1);
+}
+
+template <int TA>
+int launch_exact_splitk(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiParams& ep, int K, int split,
+                        cudaStream_t st) {
+  using Cfg = GemmCfg<3, 3, TA>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(exact_linear_splitk_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::SMEM_BYTES) != cudaSuccess)
+      return BX_ELAUNCH;
+    configured = true;
+  }
+  const int m_tiles = (ep.M + TA - 1) / TA;
+  const int n_tiles = (ep.N + WROWS - 1) / WROWS;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(m_tiles * n_tiles * split), 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, exact_linear_splitk_kernel<TA>, mw, ma, ep, K, m_tiles) != cudaSuccess) return BX_ELAUNCH;
   return launched(1);
 }
 
@@ -188,10 +218,34 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
     if (ta <= 48 && n_tiles * ((M + ta - 1) / ta) > 2 * 148) persistent = true;
     if (ta == 64 && K <= 4096 && n_tiles * ((M + 47) / 48) > 2 * 148) { ta = 48; persistent = true; }
   }
+  // Split-K over a cluster of CTAs (200 + activation rows per tile asks for it; automatic for small batches whose
+  // tile list covers less than half of the SMs): as many K slices as keep the CTA count within the 148 SMs.
+  int split = 0;
+  if (ta >= 200) {
+    ta -= 200;
+    split = SPLITK_MAX;
+    if (ta != 16 && ta != 32 && ta != 64) return BX_EARG;
+  } else if (tile_rows == 0 && !persistent && M <= 128 && (ta == 16 || ta == 32 || ta == 64)) {
+    const long tiles = ((N + WROWS - 1) / WROWS) * ((M + ta - 1) / ta);
+    if (tiles * 2 <= 148) split = (int)(148 / tiles);
+  }
+  if (split > 0) {
+    const int nkb = (K + BKB - 1) / BKB;
+    const int lim = ta == 16 ? splitk_limit<16>() : ta == 32 ? splitk_limit<32>() : splitk_limit<64>();
+    if (split > lim) split = lim;
+    if (split > nkb / 2) split = nkb / 2;                      // at least two K blocks per slice
+  }
   CUtensorMap mw, ma;
   if (!make_map(&mw, limbs, (uint64_t)K, (uint64_t)N, 3, WROWS)) return BX_ELAUNCH;
   if (!make_map(&ma, scratch, (uint64_t)K, (uint64_t)M, 3, (uint32_t)ta)) return BX_ELAUNCH;
   ExactEpiParams ep{q, ldq, sh, d, g, cnt, ec, ev, R, y, flag, M, N, checked};
+  if (split >= 2) {
+    switch (ta) {
+      case 16: return launch_exact_splitk<16>(mw, ma, ep, K, split, st);
+      case 32: return launch_exact_splitk<32>(mw, ma, ep, K, split, st);
+      default: return launch_exact_splitk<64>(mw, ma, ep, K, split, st);
+    }
+  }
   if (persistent) {
     switch (ta) {
       case 16: return launch_exact_persistent<16>(mw, ma, ep, K, st);

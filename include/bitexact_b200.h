@@ -43,7 +43,10 @@ int bx_clear_device_status(void);
  *   y      int64 [M, N] contiguous;  flag int32 [1], set to 1 when `checked` and a result lost bits or left
  *          (-2^62, 2^62)
  *   tile_rows  activation rows per CTA tile: 0 = automatic, else one of 16, 32, 48, 64, 80; -16, -32, -48 select
- *              that tile size on the persistent kernel (one CTA per SM, overlapped epilogue). No effect on results.
+ *              that tile size on the persistent kernel (one CTA per SM, overlapped epilogue); 216, 232, 264 select
+ *              16, 32, 64 rows with the K dimension split over a cluster of up to 8 CTAs (partial sums through
+ *              distributed shared memory), the automatic choice for M <= 128 when the tile list covers less than
+ *              half of the SMs. No effect on results.
  */
 size_t bx_exact_linear_scratch_bytes(int M, int K);
 int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,

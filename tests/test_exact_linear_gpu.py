@@ -32,7 +32,8 @@ def test_golden_linear_with_residual_and_extreme_shifts():
     z = np.load(os.path.join(GOLD, "exact_ops.npz"))
     dec = {k: z["lin_" + k] for k in ("limbs", "g", "d", "rr", "rc", "rv")}
     fl = _lin(dec)
-    for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48):      # negative: the persistent kernel
+    # negative: the persistent kernel; 200 + rows: split-K over a cluster of CTAs
+    for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48, 216, 232, 264):
         y, flag = _run(fl, z["lin_q"], z["lin_sh"], True, tile)
         assert np.array_equal(y, z["lin_y"]), tile
         assert flag == bool(z["lin_flag"])
@@ -45,7 +46,7 @@ def test_golden_linear_with_residual_and_extreme_shifts():
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 256, 2048), (7, 3072, 2048), (37, 512, 8192), (300, 1024, 2048),
-                                   (17, 200, 272), (81, 136, 128)])
+                                   (17, 200, 272), (81, 136, 128), (64, 2048, 8192), (5, 130, 1040)])
 def test_seeded_shapes_against_oracle(M, N, K):
     rng = np.random.RandomState(M * 1000 + N)
     W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
@@ -61,7 +62,7 @@ def test_seeded_shapes_against_oracle(M, N, K):
     sh = rng.randint(-45, -8, M).astype(np.int64)
     want, wflag = ox.linear(q, sh, dec, checked=True)
     fl = _lin(dec)
-    for tile in (None, 16, 80, -48) if M > 16 else (None, 64, -16):
+    for tile in (None, 16, 80, -48, 216, 232, 264) if M > 16 else (None, 64, -16, 216, 264):
         y, flag = _run(fl, q, sh, True, tile)
         assert np.array_equal(y, want), (tile, int((y != want).sum()))
         assert flag == wflag
