@@ -211,10 +211,20 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
     persistent = true;
     if (ta != 16 && ta != 32 && ta != 48) return BX_EARG;
   } else if (ta == 0) {
-    // Activation rows per CTA: 64 when that still gives most SMs a tile, else 32 (more, smaller tiles); a tile
-    // list of more than two waves goes to the persistent kernel (48 rows, overlapped epilogue).
+    // Activation rows per CTA: the size that needs the fewest wave-rows (below); a tile list of more than two waves
+    // goes to the persistent kernel (48 rows, overlapped epilogue).
     const long n_tiles = (N + WROWS - 1) / WROWS;
-    ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 48 ? 48 : (n_tiles * ((M + 63) / 64) >= 90 ? 64 : 32);
+    ta = M <= 16 ? 16 : M <= 32 ? 32 : 48;
+    if (M > 48) {
+      // waves of 148 CTAs x (rows of a tile + a fixed cost of about 16 rows' worth of prologue and epilogue)
+      long best = -1;
+      const int cand[3] = {64, 48, 32};
+      for (int i = 0; i < 3; ++i) {
+        const long tiles = n_tiles * ((M + cand[i] - 1) / cand[i]);
+        const long cost = ((tiles + 147) / 148) * (cand[i] + 16);
+        if (best < 0 || cost < best) { best = cost; ta = cand[i]; }
+      }
+    }
     if (ta <= 48 && n_tiles * ((M + ta - 1) / ta) > 2 * 148) persistent = true;
     if (ta == 64 && K <= 4096 && n_tiles * ((M + 47) / 48) > 2 * 148) { ta = 48; persistent = true; }
   }
