@@ -170,3 +170,38 @@ class ShardedHead:
                                  best.data_ptr(), idx.data_ptr(), M, Vl, self.v0, fr, nv.stream())
         nv.check(rc, "bx_sample_shard")
         return combine_argmax(best, idx, self.group)
+
+
+class ShardedHeadInt8:
+    """Column-sharded LM head + sampler of int8 mode: rank r holds rows [v0, v1) of the int8 LM-head weight and of its
+    per-channel multipliers; logits (16 fractional bits) never leave the shard unless `full_logits` is called."""
+
+    def __init__(self, c, device, group=None, nl=2):
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        V = c["lm"].shape[0]
+        self.v0, self.v1 = column_bounds(V, self.world, self.rank)
+        self.w = c["lm"][self.v0:self.v1].to(device).contiguous()
+        self.m = c["lm.m"][self.v0:self.v1].to(device).contiguous()
+        self.fmsh = int(c["lm.fm"]) + 8 * (nl - 1) - 24
+
+    def local_logits(self, a8, mant, e, flag):
+        from .int8.gemm_skinny import linear_post
+        return linear_post(a8, self.w, self.m, self.fmsh, mant, e, flag, True)
+
+    def full_logits(self, a8, mant, e, flag):
+        return gather_columns(self.local_logits(a8, mant, e, flag), self.group)
+
+    def sample(self, a8, mant, e, flag, rows, lnt):
+        """rows int64 [M, 4] = (seed, t, tn, td) on the device -> tokens int64 [M] (identical on every rank)."""
+        from . import _native as nv
+        lg = self.local_logits(a8, mant, e, flag)
+        M, Vl = lg.shape
+        lib = nv.lib()
+        best = torch.empty(M, dtype=torch.long, device=lg.device)
+        idx = torch.empty(M, dtype=torch.long, device=lg.device)
+        scratch = torch.empty(max(1, lib.bx_sample_scratch_bytes(M, Vl)), dtype=torch.uint8, device=lg.device)
+        rc = lib.bx_sample_shard(lg.data_ptr(), lg.stride(0), rows.data_ptr(), lnt.data_ptr(), scratch.data_ptr(),
+                                 best.data_ptr(), idx.data_ptr(), M, Vl, self.v0, 16, nv.stream())
+        nv.check(rc, "bx_sample_shard")
+        return combine_argmax(best, idx, self.group)

@@ -65,6 +65,25 @@ def _worker(rank, world, port, ret):
         for b, i in enumerate(mine):
             ok &= toks[b].tolist() == z[f"p{i}_t07_tok"].tolist() and shas[b] == z[f"p{i}_t07_sha"].tolist()
         eng.check()
+        # (3) int8 mode: sequence-sharded decode against the reference's hashes, column-sharded LM head and sampler
+        from bitexact_llm_b200.int8 import consts as consts8
+        from bitexact_llm_b200.int8.engine import IntEngine
+        from bitexact_llm_b200.vllm_plugin import tri_fuse
+        z8 = np.load(os.path.join(ROOT, "tests", "golden", "tiny_model_int8.npz"))
+        t8 = {"cos": torch.zeros(2048, 32, dtype=torch.long), "sin": torch.zeros(2048, 32, dtype=torch.long)}
+        t8["cos"][:128], t8["sin"][:128] = torch.from_numpy(z8["cos"]), torch.from_numpy(z8["sin"])
+        c8 = consts8.build(TINY, tiny_state_dict(), tables=t8)
+        eng8 = IntEngine(c8, dev)
+        toks, shas = generate(eng8, ids, 8, 7, 10, seeds=mine, lens=lens, max_len=64)
+        for b, i in enumerate(mine):
+            ok &= toks[b].tolist() == z8[f"p{i}_t07_tok"].tolist() and shas[b] == z8[f"p{i}_t07_sha"].tolist()
+        h8 = torch.randint(-(1 << 18), 1 << 18, (7, eng8.D), generator=g).to(dev)
+        pre = tri_fuse.pre_norm(eng8, h8, eng8.gf)
+        full8 = eng8.logits(h8)
+        head8 = par.ShardedHeadInt8(c8, dev)
+        ok &= torch.equal(head8.full_logits(*pre, eng8.fl), full8)
+        ok &= torch.equal(head8.sample(*pre, eng8.fl, rows, eng8.ln), sampler.sample_rows(full8, rows, eng8.ln, 16))
+        eng8.check()
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
