@@ -37,6 +37,9 @@ _SIGNATURES = {
     "bx_kv_store": (I, [P, L, L, L, I, P, P, L, L, P, L, L, I, I, I, P]),
     "bx_exact_attn_out": (I, [P, P, P, P, P, I, I, I, P]),
     "bx_exact_silu_quant": (I, [P, P, P, P, P, P, I, I, P]),
+    "bx_attention_scratch_bytes": (Z, [I, I]),
+    "bx_exact_attention_ws": (I, [P, P, P, P, L, L, L, L, I, P, I, L, I, P, P, L, P, P, I, I, I, I, I, I, P, Z, P]),
+    "bx_int8_attention_ws": (I, [P, P, P, L, L, L, L, I, P, I, L, I, P, P, P, P, I, I, I, I, I, I, P, Z, P]),
     "bx_exact_attention": (I, [P, P, P, P, L, L, L, L, I, P, I, L, I, P, P, L, P, P, I, I, I, I, I, I, P]),
     "bx_int8_attention": (I, [P, P, P, L, L, L, L, I, P, I, L, I, P, P, P, P, I, I, I, I, I, I, P]),
     "bx_int8_norm": (I, [I, P, P, P, P, P, P, P, P, P, I, I, I, P]),

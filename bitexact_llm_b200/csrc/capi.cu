@@ -386,16 +386,20 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
                                 int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt,
                                 int bt_is_int64, int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut,
                                 int64_t l2e, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
-                                int min_per_sm, void* stream) {
+                                int min_per_sm, void* spill, size_t spill_bytes, void* stream) {
   const bool forced = min_per_sm == 0;                          // an explicit variant: any fit will do
   const int KEYS = 8 * NW, STAGE = KEYS * 256;
   const int64_t max_keys = (int64_t)nblk * bs;
   const int64_t npairs = (int64_t)R * HKV;
   if (bs > KEYS || KEYS % bs != 0 || 32 % bs != 0) return forced ? BX_EARG : BX_ENOFIT;
   if (!forced && npairs < 2 * 148) return BX_ENOFIT;
-  const int64_t cap = (max_keys + KEYS - 1) / KEYS * KEYS;
+  // Scores in shared memory for the whole context, or (scratch given) chunks of 512 keys with the scores of longer
+  // pairs in the caller's scratch buffer, one slice per CTA.
+  const int64_t spill_keys = (max_keys + 63) / 64 * 64;
+  const bool chunked = spill != nullptr;
+  const int64_t cap = chunked ? 512 : (max_keys + KEYS - 1) / KEYS * KEYS;     // chunks: a multiple of 32 NW keys
   if (cap / 32 > ATT6_MAXGROUPS) return forced ? BX_EARG : BX_ENOFIT;
-  const int64_t fixed = 1024 + cap * 32 + (int64_t)sizeof(Attn6Small);
+  const int64_t fixed = 1024 + cap * 32 + (int64_t)sizeof(Attn6Small) + 1024 /* request order */;
   int per_sm = NW == 4 ? 4 : 2, ns = 0;
   for (; per_sm >= 1; --per_sm) {                               // most CTAs per SM that still leave a ring of 4 stages
     const int64_t budget = 227 * 1024 / per_sm - 1024;
@@ -433,10 +437,13 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return BX_ELAUNCH;
   const int64_t grid = npairs < (int64_t)per_sm * 148 ? npairs : (int64_t)per_sm * 148;
+  if (chunked && (size_t)grid * (size_t)spill_keys * 32 > spill_bytes) return forced ? BX_EARG : BX_ENOFIT;
   if (NW == 8)
-    exact_attention_stream_kernel<8><<<(unsigned)grid, 320, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+    exact_attention_stream_kernel<8><<<(unsigned)grid, 320, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs,
+                                                                                          (i64*)spill, spill_keys);
   else
-    exact_attention_stream_kernel<4><<<(unsigned)grid, 192, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs);
+    exact_attention_stream_kernel<4><<<(unsigned)grid, 192, smem, (cudaStream_t)stream>>>(tk, tv, p, ns, npairs,
+                                                                                          (i64*)spill, spill_keys);
   if (cudaGetLastError() != cudaSuccess) return BX_ELAUNCH;
   return launched(1);
 }
@@ -445,7 +452,7 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
                          int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
                          int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e,
                          const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M, int HD,
-                         int cluster_size, int variant, void* stream) {
+                         int cluster_size, int variant, void* spill, size_t spill_bytes, void* stream) {
   if (!q || !qpos || !cache || !bt || !num || !den) return BX_EARG;
   if (!ptab && (!sh || !lut)) return BX_EARG;
   if (R < 0 || HKV <= 0 || M < 1 || M > 4 || HD != ATT_HD || bs <= 0 || nblk <= 0 || nb <= 0) return BX_EARG;
@@ -465,13 +472,19 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
     const int tries[3][2] = {{4, 4}, {8, 2}, {4, 2}};
     for (int t = 0; t < 3; ++t) {
       const int rc = run_attention_stream(tries[t][0], q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64,
-                                          sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, tries[t][1], stream);
+                                          sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, tries[t][1], nullptr, 0,
+                                          stream);
+      if (rc != BX_ENOFIT) return rc;
+    }
+    if (spill) {                                                // long contexts: chunks of 512 keys, scores in scratch
+      const int rc = run_attention_stream(4, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
+                                          rmap, lut, l2e, ptab, num, den, R, HKV, M, 3, spill, spill_bytes, stream);
       if (rc != BX_ENOFIT) return rc;
     }
   }
   if (variant == 5 || variant == 6)
     return run_attention_stream(variant == 5 ? 8 : 4, q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64,
-                                sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, 0, stream);
+                                sbt, nblk, rmap, lut, l2e, ptab, num, den, R, HKV, M, 0, spill, spill_bytes, stream);
   // 1 direct loads, 2 TMA-staged, 3 TMA + tcgen05 p.V with 8 consumer warps, 4 the same with 4 consumer warps
   const int kind = variant != 0 ? variant : (tma_ok ? ((bs <= 32 && (int64_t)R * HKV >= 64) ? 4 : 3) : 1);
   const int nw = kind == 4 ? 4 : 8;
@@ -565,7 +578,32 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
                        int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream) {
   if (!sh || !lut) return BX_EARG;
   return run_attention(q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, lut, l2e,
-                       nullptr, num, den, R, HKV, M, HD, cluster_size, variant, stream);
+                       nullptr, num, den, R, HKV, M, HD, cluster_size, variant, nullptr, 0, stream);
+}
+
+size_t bx_attention_scratch_bytes(int nblk, int bs) {
+  if (nblk <= 0 || bs <= 0) return 0;
+  const size_t keys = ((size_t)nblk * bs + 63) / 64 * 64;
+  return (size_t)4 * 148 * keys * 32;
+}
+
+int bx_exact_attention_ws(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
+                          int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
+                          int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
+                          int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* scratch,
+                          size_t scratch_bytes, void* stream) {
+  if (!sh || !lut) return BX_EARG;
+  return run_attention(q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, lut, l2e,
+                       nullptr, num, den, R, HKV, M, HD, cluster_size, variant, scratch, scratch_bytes, stream);
+}
+
+int bx_int8_attention_ws(const int32_t* q, const int64_t* qpos, const int8_t* cache, int64_t nb, int64_t sc_nb,
+                         int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
+                         const int64_t* rmap, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
+                         int HD, int cluster_size, int variant, void* scratch, size_t scratch_bytes, void* stream) {
+  if (!ptab) return BX_EARG;
+  return run_attention(q, nullptr, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, nullptr,
+                       0, ptab, num, den, R, HKV, M, HD, cluster_size, variant, scratch, scratch_bytes, stream);
 }
 
 int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache, int64_t nb, int64_t sc_nb,
@@ -574,7 +612,7 @@ int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache
                       int HD, int cluster_size, int variant, void* stream) {
   if (!ptab) return BX_EARG;
   return run_attention(q, nullptr, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, nullptr,
-                       0, ptab, num, den, R, HKV, M, HD, cluster_size, variant, stream);
+                       0, ptab, num, den, R, HKV, M, HD, cluster_size, variant, nullptr, 0, stream);
 }
 
 int bx_int8_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gamma,

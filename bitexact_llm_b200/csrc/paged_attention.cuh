@@ -997,7 +997,16 @@ exact_attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 // A separate warp issues the MMAs: it takes a 32-key group as soon as the group's weights are written (a tagged flag
 // per group, release / acquire), so V stages drain while the rest of the weight pass is still running.
 // Pairs are dealt round robin (pair = block index + k * grid size): handing them out through a global ticket counter
-// was measured and lost more to the extra hand-over per pair than it gained on ragged batches.
+// was measured and lost more to the extra hand-over per pair than it gained on ragged batches. With up to 512
+// requests every CTA first ranks the requests by context length (longest first, ties by index: the same order in
+// every CTA), so that the round robin hands every CTA a like mix of long and short pairs.
+//
+// Long contexts: a pair whose scores do not fit the shared-memory buffer (C keys) keeps them in a per-CTA slice of a
+// caller-provided scratch buffer instead (written in sweep 1, read back once by the weight pass: 64 extra bytes per
+// key, mostly L2 traffic), and sweep 2 runs in chunks of C keys: the weights of a chunk are written as p-limb tiles
+// into the shared-memory buffer, the MMA warp consumes the chunk's V stages, and the buffer is reused for the next
+// chunk once the chunk's MMAs have completed (acc_done is committed per chunk). One CTA therefore owns a pair of
+// any length, with no cluster and no cross-CTA exchange, and the CTAs stay small enough for three or four per SM.
 //
 // V tiles: [V limb 0 | V limb 1] (cache bytes 192..319) and [V limb 1 | V limb 2] (bytes 256..383), both 128-byte
 // swizzled rows, so no byte outside the limbs is fetched; TMEM lanes 0..63 of the second accumulator repeat limb 1
@@ -1042,7 +1051,7 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* f, uint32_t want) {
 template <int NW>
 __global__ void __launch_bounds__(32 * NW + 64, NW == 4 ? 4 : 2)
 exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                              const AttnParams p, int NS, int64_t npairs) {
+                              const AttnParams p, int NS, int64_t npairs, i64* spill, int64_t spill_keys) {
   constexpr int KEYS = 8 * NW;                  // keys per stage
   constexpr int STAGE_BYTES = KEYS * 256;       // two V tiles of 128-byte rows (the K sweep uses 192 B per key)
   constexpr int CTHREADS = 32 * NW;             // consumer threads
@@ -1050,7 +1059,13 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(att_smem) + 1023) & ~uintptr_t(1023));
   i64* scores = reinterpret_cast<i64*>(ring + (size_t)NS * STAGE_BYTES);   // later, in place: the p-limb tiles
   Attn6Small* sm = reinterpret_cast<Attn6Small*>(reinterpret_cast<uint8_t*>(scores) + (size_t)p.chunk_cap * 32);
+  uint16_t* order = reinterpret_cast<uint16_t*>(sm + 1);             // requests, longest context first (or unused)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int C = p.chunk_cap;                                          // keys whose scores / p tiles fit in shared memory
+  const int GPC = C / 32;                                             // 32-key groups per chunk (a multiple of NW)
+  i64* my_spill = spill ? spill + (size_t)blockIdx.x * spill_keys * 4 : nullptr;
+  const int64_t nreq = npairs / p.HKV;
+  bool ranked = nreq <= 512 && C >= 128;                              // the sort's tables borrow the score buffer
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -1064,6 +1079,59 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     tma_prefetch_desc(&tmap_v);
   }
   for (int i = threadIdx.x; i < ATT6_MAXGROUPS; i += blockDim.x) sm->ptag[i] = 0;
+  if (ranked) {
+    // Requests by context length, longest first, in buckets of 128 keys (ties by index): a counting sort whose
+    // placement step runs in one warp over 32 requests at a time (match_any gives each lane its place among the lanes
+    // of the same bucket), so every CTA computes the same order. The score buffer is still free: it holds the table.
+    int* lens = reinterpret_cast<int*>(scores);                       // [512] bucket of each request
+    int* base = lens + 512;                                           // [512] running start of each bucket
+    for (int t = threadIdx.x; t < 512; t += blockDim.x) base[t] = 0;
+    __syncthreads();
+    for (int t = threadIdx.x; t < nreq; t += blockDim.x) {
+      i64 kend = 0;
+      for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[(int64_t)t * p.M + g] + 1);
+      kend = imin(imax(kend, 0), (i64)p.nblk * p.bs);
+      lens[t] = 511 - (int)imin(kend >> 7, 511);                       // bucket 0 = the longest contexts
+    }
+    __syncthreads();
+    bool same = true;
+    for (int t = threadIdx.x; t < nreq; t += blockDim.x) {
+      const int b = lens[t];
+      same &= b == lens[0];
+      atomicAdd(&base[b], 1);
+    }
+    // every request in one bucket (a batch of like contexts): the given order is as good as any
+    ranked = !__syncthreads_and(same);
+    if (ranked && warp == 0) {
+      // exclusive prefix of the 512 bucket counts: 16 per lane, then a warp scan
+      int cnt[16], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { cnt[i] = base[16 * lane + i]; sum += cnt[i]; }
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      int run = incl - sum;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { base[16 * lane + i] = run; run += cnt[i]; }
+      __syncwarp();
+      for (int t0 = 0; t0 < nreq; t0 += 32) {
+        const int t = t0 + lane;
+        const bool live = t < nreq;
+        const int b = live ? lens[t] : -1 - lane;                     // dead lanes: buckets of their own
+        const unsigned same = __match_any_sync(0xffffffffu, b);
+        const int place = __popc(same & ((1u << lane) - 1));
+        int start = 0;
+        if (live) start = base[b];
+        __syncwarp();
+        if (live && place == 0) base[b] = start + __popc(same);
+        __syncwarp();
+        if (live) order[start + place] = (uint16_t)t;
+      }
+    }
+  }
   if (warp == 0) {
     tmem_alloc(&sm->tmem_base, ATT3_TMEM_COLS);
     tmem_relinquish();
@@ -1075,12 +1143,17 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(&sm->abort_flag);
   constexpr uint32_t IDESC = umma_idesc_i8_amn(16);
 
+  // the w-th piece of work: heads of the w / HKV-th longest request
+  auto pair_of = [&](int64_t w) -> int64_t {
+    if (!ranked) return w;
+    return (int64_t)order[w / p.HKV] * p.HKV + w % p.HKV;
+  };
   auto keys_of = [&](int64_t pz) -> i64 {
     const int64_t r = pz / p.HKV;
     i64 kend = 0;
     for (int g = 0; g < p.M; ++g) kend = imax(kend, p.qpos[r * p.M + g] + 1);
     kend = imin(kend, (i64)p.nblk * p.bs);
-    return imin(kend, (i64)p.chunk_cap);
+    return imin(kend, my_spill ? (i64)spill_keys : (i64)C);
   };
 
   if (warp == NW) {
@@ -1088,7 +1161,8 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     const int pages_per_stage = KEYS / p.bs;
     bool ok = true;
     uint32_t gidx = 0;                                               // stages issued so far, over all pairs
-    for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x) {
+    for (int64_t w = blockIdx.x; w < npairs; w += gridDim.x) {
+      const int64_t pz = pair_of(w);
       const int64_t r = pz / p.HKV;
       const int h = (int)(pz % p.HKV);
       const i64 hi = keys_of(pz);
@@ -1141,19 +1215,23 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     // ---------------- MMA warp: one thread streams the staged V tiles through tcgen05 ----------------
     if (lane == 0) {
       bool ok = true;
-      uint32_t gidx = 0, item = 0;
+      uint32_t gidx = 0, wave = 0;                                   // wave: chunks handed over so far, over all pairs
       constexpr int GPS = KEYS / 32;                                 // groups per stage
-      for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x, ++item) {
+      for (int64_t w = blockIdx.x; w < npairs; w += gridDim.x) {
+        const int64_t pz = pair_of(w);
         const i64 hi = keys_of(pz);
         const int nst = (int)((hi + KEYS - 1) / KEYS);
         const int ngroups = (int)((hi + 31) / 32);
         gidx += (uint32_t)nst;                                       // the K stages of the pair
+        int ck = 0, cbase = 0;                                       // chunk of the stage's groups and its first group
         for (int st = 0; st < nst; ++st, ++gidx) {
           const uint32_t slot = gidx % (uint32_t)NS, use = gidx / (uint32_t)NS;
+          const int g0 = GPS * st;                                   // first group of the stage
+          if (g0 - cbase >= GPC) { ++ck; cbase += GPC; }             // (kept by counting: no division per stage)
           // The group's weights come first: they exist only after sweep 1 of this pair has consumed every K stage,
           // so the slot is at most one use behind and the parity wait below cannot mistake an older phase of the
           // barrier for this one.
-          if (ok) ok = flag_wait(&sm->ptag[GPS * st], item + 1);
+          if (ok) ok = flag_wait(&sm->ptag[g0 - cbase], wave + ck + 1);
           if (ok) ok = mbar_wait(&sm->full[slot], use & 1);
           ok = ok && (*abort_flag == 0);
           if (!ok) continue;
@@ -1161,11 +1239,12 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
 #pragma unroll
           for (int kg = 0; kg < GPS; ++kg) {
             const int grp = GPS * st + kg;
+            const int place = grp - cbase;                           // GPC is a multiple of GPS: same chunk as g0
             if (grp < ngroups && ok) {
-              if (kg > 0) ok = flag_wait(&sm->ptag[grp], item + 1);
+              if (kg > 0) ok = flag_wait(&sm->ptag[place], wave + ck + 1);
               if (ok) {
                 tc_fence_after();
-                const uint64_t bdesc = umma_desc_kmajor_plain(smem_u32(scores) + grp * 1024, 256, 128);
+                const uint64_t bdesc = umma_desc_kmajor_plain(smem_u32(scores) + place * 1024, 256, 128);
                 const uint32_t accum = grp > 0 ? 1u : 0u;
                 umma_i8(tmem, umma_desc_sw128(vbase + kg * 4096), bdesc, IDESC, accum);
                 umma_i8(tmem + 16, umma_desc_sw128(vbase + KEYS * 128 + kg * 4096), bdesc, IDESC, accum);
@@ -1175,8 +1254,11 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
           if (!ok) continue;
           umma_commit(&sm->empty[slot]);                             // one of the NW arrivals of the slot's phase
           for (int a = 1; a < NW; ++a) mbar_arrive(&sm->empty[slot]);
-          if (st == nst - 1) umma_commit(&sm->acc_done);
+          // the chunk's last group (or the pair's): its p tiles may be overwritten, the accumulators read
+          const int gend = GPS * (st + 1) < ngroups ? GPS * (st + 1) : ngroups;
+          if (st == nst - 1 || gend - cbase == GPC) umma_commit(&sm->acc_done);
         }
+        wave += (uint32_t)((ngroups + GPC - 1) / GPC);
       }
       if (!ok) { atomicAdd(&g_wait_timeouts, 1); sm->abort_flag = 1; }
     }
@@ -1188,11 +1270,13 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
   // ---------------- consumer warps ----------------
   bool ok = true;
   uint32_t gidx = 0;
-  uint32_t item = 0;
-  for (int64_t pz = blockIdx.x; pz < npairs; pz += gridDim.x, ++item) {
+  uint32_t wave = 0;                                                 // chunks handed over so far (acc_done phases)
+  for (int64_t w = blockIdx.x; w < npairs; w += gridDim.x) {
+    const int64_t pz = pair_of(w);
     const int64_t r = pz / p.HKV;
     const i64 hi = keys_of(pz);
     const int nst = (int)((hi + KEYS - 1) / KEYS);
+    const bool spilled = hi > C;                                     // the scores of this pair live in the scratch slice
 
     uint32_t afrag[2][4];
     {
@@ -1257,7 +1341,8 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
               const i64 raw = slo[c] + shl(mid, 8) + shl(shi[c], 16);
               const i64 kk = kb + (lane & 3) * 2 + c;
               if (kk < hi) {
-                scores[kk * 4 + (lane >> 2)] = raw;
+                if (spilled) my_spill[kk * 4 + (lane >> 2)] = raw;
+                else scores[kk * 4 + (lane >> 2)] = raw;
                 if (kk <= qp_s1) mymax[c] = imax(mymax[c], raw);
               }
             }
@@ -1285,28 +1370,42 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     const i64 rowshift = (gok && p.sh) ? (i64)(FK + 3 - FZ) - p.sh[pz * p.M + g2] : 0;
     i64 den = 0;
     const int ngroups = (int)((hi + 31) / 32);
-    for (int grp = warp; grp < ngroups; grp += NW) {
-      i64 sc[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) sc[j] = scores[((i64)grp * 32 + 8 * j + (lane >> 2)) * 4 + g2];
-      __syncwarp();
-      uint8_t* pt = reinterpret_cast<uint8_t*>(scores) + (size_t)grp * 1024;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kl = 8 * j + (lane >> 2);
-        const i64 key = (i64)grp * 32 + kl;
-        i64 pv = 0;
-        if (key < hi && key <= qp2) pv = attn_weight_any(p, sc[j], mx, rowshift);
-        den += pv;
-        int pr = (int)pv;
-        const int off = (kl >> 4) * 256 + (kl & 15) + g2 * 16;
-        pt[off] = (uint8_t)split8(pr);                                // row g      (limb 0)
-        pt[off + 64] = (uint8_t)split8(pr);                           // row 4 + g  (limb 1)
-        pt[off + 128] = (uint8_t)split8(pr);                          // row 8 + g  (limb 2)
+    const int nchunks = (ngroups + GPC - 1) / GPC;
+    for (int ck = 0; ck < nchunks; ++ck) {
+      if (ck > 0) {
+        // the p tiles of the previous chunk are still being read by its MMAs until they are committed
+        if (ok) ok = mbar_wait(&sm->acc_done, (wave + ck - 1) & 1);
+        ok = ok && (*abort_flag == 0);
+        ok = __all_sync(0xffffffffu, ok);
       }
-      fence_proxy_async_smem();                                       // the tile is read by tcgen05 (async proxy)
-      __syncwarp();
-      if (lane == 0) flag_release(&sm->ptag[grp], item + 1);
+      const int gtop = (ck + 1) * GPC < ngroups ? (ck + 1) * GPC : ngroups;
+      for (int grp = ck * GPC + warp; grp < gtop; grp += NW) {
+        const int place = grp - ck * GPC;
+        i64 sc[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const i64 at = ((i64)grp * 32 + 8 * j + (lane >> 2)) * 4 + g2;
+          sc[j] = spilled ? my_spill[at] : scores[at];
+        }
+        __syncwarp();
+        uint8_t* pt = reinterpret_cast<uint8_t*>(scores) + (size_t)place * 1024;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kl = 8 * j + (lane >> 2);
+          const i64 key = (i64)grp * 32 + kl;
+          i64 pv = 0;
+          if (key < hi && key <= qp2) pv = attn_weight_any(p, sc[j], mx, rowshift);
+          den += pv;
+          int pr = (int)pv;
+          const int off = (kl >> 4) * 256 + (kl & 15) + g2 * 16;
+          pt[off] = (uint8_t)split8(pr);                              // row g      (limb 0)
+          pt[off + 64] = (uint8_t)split8(pr);                         // row 4 + g  (limb 1)
+          pt[off + 128] = (uint8_t)split8(pr);                        // row 8 + g  (limb 2)
+        }
+        fence_proxy_async_smem();                                     // the tile is read by tcgen05 (async proxy)
+        __syncwarp();
+        if (lane == 0) flag_release(&sm->ptag[place], wave + ck + 1);
+      }
     }
     gidx += (uint32_t)nst;                                            // the V stages belong to the MMA warp
 
@@ -1320,7 +1419,7 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
     i64 part[4] = {0, 0, 0, 0};
     if (warp < 4) {
       bool done = ok && nst > 0;
-      if (done) done = mbar_wait(&sm->acc_done, item & 1);
+      if (done) done = mbar_wait(&sm->acc_done, (wave + nchunks - 1) & 1);
       done = done && (*abort_flag == 0);
       done = __all_sync(0xffffffffu, done);
       if (done) {
@@ -1360,6 +1459,7 @@ exact_attention_stream_kernel(const __grid_constant__ CUtensorMap tmap_k, const 
       for (int w = 0; w < NW; ++w) t += sm->pden[w][threadIdx.x];
       p.den[pz * p.M + threadIdx.x] = t;
     }
+    wave += (uint32_t)nchunks;
     asm volatile("bar.sync 1, %0;" ::"r"(CTHREADS) : "memory");     // cnum / pden / wmax are free for the next pair
   }
   __syncthreads();

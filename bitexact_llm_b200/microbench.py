@@ -92,15 +92,20 @@ def attn(args):
     num = torch.empty(B, HKV, G, HD, dtype=torch.long, device=dev)
     den = torch.empty(B, HKV, G, dtype=torch.long, device=dev)
     st = torch.cuda.current_stream().cuda_stream
+    ws = None
+    if not args.no_scratch:
+        ws = torch.empty(lib.bx_attention_scratch_bytes(nblk, bs), dtype=torch.uint8, device=dev)
 
     def run(variant=None, outs=None):
         n_, d_ = outs if outs is not None else (num, den)
-        rc = lib.bx_exact_attention(q.data_ptr(), sh.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0], cache.stride(0),
-                                    cache.stride(1), cache.stride(2), bs, bt.data_ptr(), 0, bt.stride(0), nblk, None,
-                                    lut.data_ptr(), 387270501, n_.data_ptr(), d_.data_ptr(), B, HKV, G, HD,
-                                    args.cluster if variant is None else 0, args.variant if variant is None else variant,
-                                    st)
-        nv.check(rc, "bx_exact_attention")
+        rc = lib.bx_exact_attention_ws(q.data_ptr(), sh.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0],
+                                       cache.stride(0), cache.stride(1), cache.stride(2), bs, bt.data_ptr(), 0,
+                                       bt.stride(0), nblk, None, lut.data_ptr(), 387270501, n_.data_ptr(), d_.data_ptr(), B,
+                                       HKV, G, HD, args.cluster if variant is None else 0,
+                                       args.variant if variant is None else variant,
+                                       ws.data_ptr() if (ws is not None and variant is None) else None,
+                                       ws.numel() if (ws is not None and variant is None) else 0, st)
+        nv.check(rc, "bx_exact_attention_ws")
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(2):
         run()
@@ -204,6 +209,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=4128)
     ap.add_argument("--cluster", type=int, default=0)
     ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--no-scratch", action="store_true", help="attn: no scratch buffer (long contexts: cluster kernels)")
     ap.add_argument("--fixed", action="store_true", help="attn: every request has exactly --ctx keys")
     args = ap.parse_args()
     {"gemm": gemm, "attn": attn, "stages": stages}[args.what](args)

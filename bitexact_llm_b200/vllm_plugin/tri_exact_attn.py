@@ -6,6 +6,15 @@ import torch
 from .. import _native as nv
 
 
+def _scratch(device, pairs, nblk, bs):
+    """Scratch for the scores of contexts beyond the shared-memory buffer of the streaming kernel: only when the
+    block table is wide enough to need it and there are enough (request, KV head) pairs for that kernel."""
+    if nblk * bs <= 896 or pairs < 296:
+        return None, 0
+    n = nv.lib().bx_attention_scratch_bytes(nblk, bs)
+    return torch.empty(n, dtype=torch.uint8, device=device), n
+
+
 def attend(q, sh, qpos, cache, bt, rmap, lut, l2e, nsplit=None, bn=64, warps=4, variant=0):
     """q int32 [R, HKV, M, HD] (M <= 4, |q| <= 2^22), sh int64 [R, HKV, M], qpos int64 [R, M] (key s visible to
     query i iff s <= qpos[r, i]), cache int8 limb planes [nb, HKV, bs, 8 HD], bt [*, nblk] block table, rmap int64
@@ -25,10 +34,12 @@ def attend(q, sh, qpos, cache, bt, rmap, lut, l2e, nsplit=None, bn=64, warps=4, 
         cs = 1
         while cs < min(int(nsplit), 8):
             cs *= 2
-    rc = nv.lib().bx_exact_attention(q.data_ptr(), sh.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0], cache.stride(0),
-                                     cache.stride(1), cache.stride(2), cache.shape[2], bt.data_ptr(),
-                                     int(bt.dtype == torch.int64), bt.stride(0), bt.shape[1],
-                                     nv.ptr(rmap.long().contiguous() if rmap is not None else None), lut.data_ptr(),
-                                     int(l2e), num.data_ptr(), den.data_ptr(), R, HKV, M, HD, cs, variant, nv.stream())
-    nv.check(rc, "bx_exact_attention")
+    ws, ws_bytes = _scratch(q.device, R * HKV, bt.shape[1], cache.shape[2])
+    rc = nv.lib().bx_exact_attention_ws(q.data_ptr(), sh.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0],
+                                        cache.stride(0), cache.stride(1), cache.stride(2), cache.shape[2], bt.data_ptr(),
+                                        int(bt.dtype == torch.int64), bt.stride(0), bt.shape[1],
+                                        nv.ptr(rmap.long().contiguous() if rmap is not None else None), lut.data_ptr(),
+                                        int(l2e), num.data_ptr(), den.data_ptr(), R, HKV, M, HD, cs, variant,
+                                        nv.ptr(ws), ws_bytes, nv.stream())
+    nv.check(rc, "bx_exact_attention_ws")
     return num, den

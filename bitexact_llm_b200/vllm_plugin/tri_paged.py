@@ -58,10 +58,13 @@ def attend(q, qpos, cache, bt, ptab, nsplit=None, bm=None, bn=None, warps=4, rma
         cs = 1
         while cs < min(int(nsplit), 8):
             cs *= 2
-    rc = nv.lib().bx_int8_attention(q32.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0], cache.stride(0),
-                                    cache.stride(1), cache.stride(2), cache.shape[2], bt.data_ptr(),
-                                    int(bt.dtype == torch.int64), bt.stride(0), bt.shape[1],
-                                    nv.ptr(rmap.long().contiguous() if rmap is not None else None), ptab.data_ptr(),
-                                    num.data_ptr(), den.data_ptr(), R, HKV, M, HD, cs, variant, nv.stream())
-    nv.check(rc, "bx_int8_attention")
+    from .tri_exact_attn import _scratch
+    ws, ws_bytes = _scratch(q.device, R * HKV, bt.shape[1], cache.shape[2])
+    rc = nv.lib().bx_int8_attention_ws(q32.data_ptr(), qpos.data_ptr(), cache.data_ptr(), cache.shape[0], cache.stride(0),
+                                       cache.stride(1), cache.stride(2), cache.shape[2], bt.data_ptr(),
+                                       int(bt.dtype == torch.int64), bt.stride(0), bt.shape[1],
+                                       nv.ptr(rmap.long().contiguous() if rmap is not None else None), ptab.data_ptr(),
+                                       num.data_ptr(), den.data_ptr(), R, HKV, M, HD, cs, variant, nv.ptr(ws), ws_bytes,
+                                       nv.stream())
+    nv.check(rc, "bx_int8_attention_ws")
     return num, den

@@ -177,6 +177,21 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
                        int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
                        int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream);
 
+/* The same with a scratch buffer (no counterpart in the reference, whose kernels re-read K instead): with scratch of
+ * bx_attention_scratch_bytes(nblk, bs) bytes, 16-byte aligned, the persistent streaming kernel also serves contexts
+ * whose scores do not fit in shared memory (it keeps them in the scratch, one slice per CTA, and runs its second sweep
+ * in chunks of 512 keys). The buffer carries nothing between calls. NULL scratch = bx_exact_attention. */
+size_t bx_attention_scratch_bytes(int nblk, int bs);
+int bx_exact_attention_ws(const int32_t* q, const int64_t* sh, const int64_t* qpos, const int8_t* cache, int64_t nb,
+                          int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
+                          int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
+                          int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* scratch,
+                          size_t scratch_bytes, void* stream);
+int bx_int8_attention_ws(const int32_t* q, const int64_t* qpos, const int8_t* cache, int64_t nb, int64_t sc_nb,
+                         int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
+                         const int64_t* rmap, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
+                         int HD, int cluster_size, int variant, void* scratch, size_t scratch_bytes, void* stream);
+
 /* ---- int8-mode attention and element-wise stages -------------------------------------------------------
  * Fixed points of int8 mode: residual stream / linear outputs / logits 16 bits, gamma 12, cos / sin 16, q / k / v 14,
  * attention weights 20. A linear's input is always (a8, mant, e): activation limb planes int8 [2, M, K] (limb i of

@@ -209,6 +209,42 @@ def test_attention_persistent_streaming(lim):
     assert nv.device_status() == 0
 
 
+def test_attention_long_contexts_with_score_scratch():
+    """Enough pairs for the persistent kernel and block tables wider than its shared-memory score buffer: the scores of
+    long pairs live in the scratch buffer and sweep 2 runs in chunks of 512 keys (contexts from 3 to 3000 keys in one
+    batch, chunk boundaries hit exactly, requests ranked by length)."""
+    from bitexact_llm_b200.vllm_plugin import tri_exact_attn, tri_paged
+    rng = np.random.RandomState(77)
+    nb, bs, HKV, HD = 220, 16, 8, 64
+    lim = 1 << 12
+    c32 = rng.randint(-lim, lim + 1, (nb, HKV, bs, 2 * HD)).astype(np.int64)
+    planes = np.zeros((nb, HKV, bs, 8 * HD), dtype=np.int8)
+    for part, o in ((c32[..., :HD], 0), (c32[..., HD:], 3)):
+        for i, lo in enumerate(ox.split_limbs(part, 3)[0]):
+            planes[..., (o + i) * HD:(o + i + 1) * HD] = lo.astype(np.int8)
+    lut_np = ox.exp2_table()
+    R, M = 40, 4
+    bt = rng.randint(1, nb, (R, 192)).astype(np.int32)                     # 3072 keys wide
+    ctx = rng.randint(3, 3001, R)
+    ctx[:6] = [512, 513, 1024, 1025, 3000, 511]
+    qpos = np.repeat((ctx - 1)[:, None], M, 1).astype(np.int64)
+    qpos[7, 1] = 5                                                          # one query of a long row sees few keys
+    q = rng.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, M, HD)).astype(np.int64)
+    sh = rng.randint(-40, -10, (R, HKV, M)).astype(np.int64)
+    wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, np.arange(R), lut_np)
+    for variant in (0, 6, 5):
+        num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), None, T(lut_np), ox.L2E28,
+                                         variant=variant)
+        assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), variant
+    from oracle import int8 as o8
+    expt = o8.exp_table()
+    w8n, w8d = o8.paged_attention(q >> 9, qpos, planes, bt, np.arange(R), expt)
+    num, den = tri_paged.attend(T(q >> 9), T(qpos), T(planes), T(bt), T(o8.weight_table(expt), torch.int32))
+    assert np.array_equal(N_(num), w8n) and np.array_equal(N_(den), w8d)
+    from bitexact_llm_b200 import _native as nv
+    assert nv.device_status() == 0
+
+
 def test_attention_bound_stress_equal_scores_at_limb_extremes():
     """All K, V at +LIM3, all q at 2^22, 8192 equal-score keys (the p.V partial-sum bound case)."""
     from bitexact_llm_b200.vllm_plugin import tri_exact_attn
