@@ -397,7 +397,10 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
   // pairs in the caller's scratch buffer, one slice per CTA.
   const int64_t spill_keys = (max_keys + 63) / 64 * 64;
   const bool chunked = spill != nullptr;
-  const int64_t cap = chunked ? 512 : (max_keys + KEYS - 1) / KEYS * KEYS;     // chunks: a multiple of 32 NW keys
+#ifndef BX_ATT_CHUNK
+#define BX_ATT_CHUNK 512
+#endif
+  const int64_t cap = chunked ? BX_ATT_CHUNK : (max_keys + KEYS - 1) / KEYS * KEYS;     // chunks: a multiple of 32 NW keys
   if (cap / 32 > ATT6_MAXGROUPS) return forced ? BX_EARG : BX_ENOFIT;
   const int64_t fixed = 1024 + cap * 32 + (int64_t)sizeof(Attn6Small) + 1024 /* request order */;
   int per_sm = NW == 4 ? 4 : 2, ns = 0;
