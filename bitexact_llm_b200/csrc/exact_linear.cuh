@@ -39,6 +39,22 @@ struct ExactEpilogue {
     const int d = nok ? (int)p.d[n] : 0;
     const i64 gd = nok ? p.g[n] - (i64)d + FR : 0;
     const int cnt = (nok && p.cnt) ? p.cnt[n] : 0;
+    // The residual list of weight row n (a handful of entries in a few per cent of the rows) is read once per thread;
+    // per output only the gathers from q remain, independent of each other. A warp without any residual row (and
+    // every warp of a linear without residual) skips the whole term.
+    constexpr int RMAX = 4;
+    int ecr[RMAX];
+    i64 evr[RMAX];
+#pragma unroll
+    for (int j = 0; j < RMAX; ++j) {
+      ecr[j] = 0;
+      evr[j] = 0;
+      if (j < cnt) {
+        ecr[j] = p.ec[(i64)n * p.R + j];
+        evr[j] = p.ev[(i64)n * p.R + j];
+      }
+    }
+    const bool warp_res = __any_sync(0xffffffffu, cnt > 0);
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
@@ -56,8 +72,13 @@ struct ExactEpilogue {
                   shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
           if (!has_k) T = 0;
           i64 B = 0;
-          for (int j = 0; j < cnt; ++j)
-            B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
+          if (warp_res) {
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j)
+              if (j < cnt) B += (i64)p.q[(i64)m * p.ldq + ecr[j]] * evr[j];
+            for (int j = RMAX; j < cnt; ++j)
+              B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
+          }
           bool bad;
           const i64 yv = round_shift_hl(T, B, d, p.sh[m] + gd, bad);
           any_bad |= bad;

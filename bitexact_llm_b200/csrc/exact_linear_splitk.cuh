@@ -188,6 +188,19 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     const int d = nok ? (int)ep.d[n] : 0;
     const i64 gd = nok ? ep.g[n] - (i64)d + FR : 0;
     const int cnt = (nok && ep.cnt) ? ep.cnt[n] : 0;
+    constexpr int RMAX = 4;                                          // residual list of row n, read once (see ExactEpilogue)
+    int ecr[RMAX];
+    i64 evr[RMAX];
+#pragma unroll
+    for (int j = 0; j < RMAX; ++j) {
+      ecr[j] = 0;
+      evr[j] = 0;
+      if (j < cnt) {
+        ecr[j] = ep.ec[(i64)n * ep.R + j];
+        evr[j] = ep.ev[(i64)n * ep.R + j];
+      }
+    }
+    const bool warp_res = __any_sync(0xffffffffu, cnt > 0);
     bool any_bad = false;
 #pragma unroll 1
     for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
@@ -208,8 +221,13 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
                 shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
           for (int r = 1; r < S; ++r) T += partial[((size_t)(r - 1) * TA + c0 + i) * WROWS + row];
           i64 B = 0;
-          for (int j = 0; j < cnt; ++j)
-            B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)n * ep.R + j]] * ep.ev[(i64)n * ep.R + j];
+          if (warp_res) {
+#pragma unroll
+            for (int j = 0; j < RMAX; ++j)
+              if (j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
+            for (int j = RMAX; j < cnt; ++j)
+              B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)n * ep.R + j]] * ep.ev[(i64)n * ep.R + j];
+          }
           bool bad;
           const i64 yv = round_shift_hl(T, B, d, ep.sh[m] + gd, bad);
           any_bad |= bad;
