@@ -54,7 +54,8 @@ struct ExactEpilogue {
         evr[j] = p.ev[(i64)n * p.R + j];
       }
     }
-    const bool warp_res = __any_sync(0xffffffffu, cnt > 0);
+    const int wcnt = __reduce_max_sync(0xffffffffu, cnt);              // longest list in the warp (uniform)
+    const bool warp_res = wcnt > 0;
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
@@ -75,7 +76,7 @@ struct ExactEpilogue {
           if (warp_res) {
 #pragma unroll
             for (int j = 0; j < RMAX; ++j)
-              if (j < cnt) B += (i64)p.q[(i64)m * p.ldq + ecr[j]] * evr[j];
+              if (j < wcnt && j < cnt) B += (i64)p.q[(i64)m * p.ldq + ecr[j]] * evr[j];
             for (int j = RMAX; j < cnt; ++j)
               B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
           }

@@ -200,7 +200,8 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         evr[j] = ep.ev[(i64)n * ep.R + j];
       }
     }
-    const bool warp_res = __any_sync(0xffffffffu, cnt > 0);
+    const int wcnt = __reduce_max_sync(0xffffffffu, cnt);              // longest list in the warp (uniform)
+    const bool warp_res = wcnt > 0;
     bool any_bad = false;
 #pragma unroll 1
     for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
@@ -224,7 +225,7 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
           if (warp_res) {
 #pragma unroll
             for (int j = 0; j < RMAX; ++j)
-              if (j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
+              if (j < wcnt && j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
             for (int j = RMAX; j < cnt; ++j)
               B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)n * ep.R + j]] * ep.ev[(i64)n * ep.R + j];
           }

@@ -1,11 +1,15 @@
 """Kernel micro-benchmarks through the C ABI (CUDA-event timing, inputs larger than L2 or L2 flushed).
 
     python -m bitexact_llm_b200.microbench gemm [--m 1,16,256,4096] [--tile 0] [--iters 20] [--shapes decode|all]
+    python -m bitexact_llm_b200.microbench gemmr [--m 256] [--iters 10]
     python -m bitexact_llm_b200.microbench attn [--batch 256] [--ctx 4128] [--iters 10]
     python -m bitexact_llm_b200.microbench stages [--batch 256] [--iters 10]
 
 gemm: the exact-mode fused linear on the projection shapes of one Llama-3.2-1B layer and the LM head
       (int8-equivalent ops = 2 * 9 * M * N * K; algorithmic bytes = 3 N K + 4 M K + 8 M N).
+gemmr: the fused projections of one layer with REAL constants (bf16 weights from N(0, 0.02^2), decomposed into limbs
+      and the sparse residual lists, as the engine holds them) through `FusedLin` with producer-written limb planes,
+      timed as a CUDA graph over enough weight sets to exceed L2, with and without the residual lists.
 attn: exact-mode paged decode attention, 8 KV heads x 4 query heads, head_dim 64, 16-token pages, context lengths
       uniform in [64, 2 ctx - 64] (algorithmic bytes = 384 per key and KV head).
 stages: add + RMSNorm + quant (D 2048: 16 D read + 15 D written per row), SiLU * up + quant (FF 8192: 16 FF read,
@@ -69,6 +73,44 @@ def gemm(args):
             out.append(rec)
             print(json.dumps(rec), flush=True)
             del limbs, y, q, scratch
+    return out
+
+
+def gemmr(args):
+    from .exact.consts import decompose
+    from .exact.model import Lin
+    from .vllm_plugin.exact_gemm import FusedLin
+    lib, dev = nv.lib(), "cuda"
+    g = torch.Generator().manual_seed(0)
+    out = []
+    for M in [int(v) for v in args.m.split(",")]:
+        for name, (N, K) in FUSED.items():
+            if name == "lm":
+                continue
+            w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+            d0 = decompose(w.to(dev))
+            nsets = max(2, (200 << 20) // (3 * N * K) + 1)
+            sets = [FusedLin(Lin({k: (v.clone() if torch.is_tensor(v) else v) for k, v in d0.items()}, None, dev))
+                    for _ in range(nsets)]
+            q = torch.randint(-(1 << 22), (1 << 22) + 1, (M, K), dtype=torch.int32, device=dev)
+            planes = torch.empty(3, M, K, dtype=torch.int8, device=dev)
+            nv.check(lib.bx_split_limbs(q.data_ptr(), K, planes.data_ptr(), M, K, nv.stream()), "bx_split_limbs")
+            q._bx_planes = planes
+            sh = torch.full((M,), -14, dtype=torch.long, device=dev)
+            fl = torch.zeros(1, dtype=torch.int32, device=dev)
+            for tag in ("residual", "none"):
+                saved = [f.cnt for f in sets]
+                if tag == "none":
+                    for f in sets:
+                        f.cnt = None
+                ms = _graph_time(lambda i: sets[i](q, sh, fl, False), nsets, args.iters)
+                for f, c in zip(sets, saved):
+                    f.cnt = c
+                rec = {"kernel": "exact_linear", "proj": name, "M": M, "N": N, "K": K, "residual": tag,
+                       "entries": int(d0["rr"].numel()), "us": ms * 1e3, "int8_tops": 18.0 * M * N * K / ms / 1e9}
+                out.append(rec)
+                print(json.dumps(rec), flush=True)
+            del sets
     return out
 
 
@@ -200,7 +242,7 @@ def stages(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "stages"])
+    ap.add_argument("what", choices=["gemm", "gemmr", "attn", "stages"])
     ap.add_argument("--m", default="1,16,256,4096")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -212,7 +254,7 @@ def main():
     ap.add_argument("--no-scratch", action="store_true", help="attn: no scratch buffer (long contexts: cluster kernels)")
     ap.add_argument("--fixed", action="store_true", help="attn: every request has exactly --ctx keys")
     args = ap.parse_args()
-    {"gemm": gemm, "attn": attn, "stages": stages}[args.what](args)
+    {"gemm": gemm, "gemmr": gemmr, "attn": attn, "stages": stages}[args.what](args)
     if nv.device_status() != 0:
         raise SystemExit("device-side wait timed out")
 
