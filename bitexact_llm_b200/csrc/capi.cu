@@ -13,6 +13,7 @@
 #include "elementwise.cuh"
 #include "paged_attention.cuh"
 #include "sampler.cuh"
+#include "logp.cuh"
 #include "unfused.cuh"
 
 namespace {
@@ -725,6 +726,84 @@ int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, cons
                     int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream) {
   if (!best) return BX_EARG;
   return run_sample(logits, ld, rows, lnt, scratch, idx, best, M, V_local, v_offset, bits, stream);
+}
+
+// ---- integer log p ----------------------------------------------------------------------------------------------
+static void logp_plan(int M, int V, int& ch, int& nch) {
+  const int nch0 = sample_chunks(M, V);
+  ch = (V + nch0 - 1) / nch0;
+  nch = (V + ch - 1) / ch;
+}
+
+size_t bx_logp_scratch_bytes(int M, int V) {
+  return (size_t)2 * 8 * (size_t)(M > 0 ? M : 0) * sample_chunks(M, V > 0 ? V : 1);
+}
+
+static bool logp_args_ok(const void* lg, int64_t ld, const void* scratch, int M, int V) {
+  return lg && scratch && M >= 0 && M <= 65535 && V > 0 && ld >= V;
+}
+
+int bx_logp_pair_table(const int64_t* tab, int tab_len, int64_t* tab2, void* stream) {
+  if (!tab || !tab2 || tab_len != LSE_LAST + 1 || ((uintptr_t)tab2 & 15)) return BX_EARG;
+  logp_pair_table_kernel<<<(tab_len + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const i64*)tab, (longlong2*)tab2, tab_len);
+  return launched(1);
+}
+
+int bx_logp_rowmax(const int64_t* logits, int64_t ld, void* scratch, int64_t* rowmax, int M, int V, void* stream) {
+  if (!logp_args_ok(logits, ld, scratch, M, V) || !rowmax) return BX_EARG;
+  if (M == 0) return BX_OK;
+  int ch, nch;
+  logp_plan(M, V, ch, nch);
+  cudaStream_t st = (cudaStream_t)stream;
+  i64* pmax = (i64*)scratch;
+  logp_max_kernel<<<dim3(nch, M), LOGP_THREADS, 0, st>>>((const i64*)logits, ld, pmax, V, ch, nch);
+  logp_rowfold_kernel<<<(M + 127) / 128, 128, 0, st>>>(pmax, nch, (i64*)rowmax, M, 0);
+  return launched(2);
+}
+
+int bx_logp_rowsum(const int64_t* logits, int64_t ld, const int64_t* rowmax, const int64_t* tab2, int tab_len,
+                   void* scratch, int64_t* S, int M, int V, int fr, void* stream) {
+  if (!logp_args_ok(logits, ld, scratch, M, V) || !rowmax || !tab2 || ((uintptr_t)tab2 & 15) || !S || tab_len != LSE_LAST + 1 || fr <= LSE_STEP ||
+      fr > 24)
+    return BX_EARG;
+  if (M == 0) return BX_OK;
+  int ch, nch;
+  logp_plan(M, V, ch, nch);
+  cudaStream_t st = (cudaStream_t)stream;
+  i64* psum = (i64*)scratch;
+  logp_sum_kernel<<<dim3(nch, M), LOGP_THREADS, 0, st>>>((const i64*)logits, ld, (const i64*)rowmax, nullptr, 0, nullptr,
+                                                        (const longlong2*)tab2, psum, V, ch, nch, fr);
+  logp_rowfold_kernel<<<(M + 127) / 128, 128, 0, st>>>(psum, nch, (i64*)S, M, 1);
+  return launched(2);
+}
+
+int bx_logp_finish(const int64_t* S, const int64_t* zt, const int64_t* lnt, int64_t* out, int M, int fr, void* stream) {
+  if (!S || !zt || !lnt || !out || M < 0 || fr <= LSE_STEP || fr > 24) return BX_EARG;
+  if (M == 0) return BX_OK;
+  logp_finish_kernel<<<(M + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const i64*)S, 1, (const i64*)zt, nullptr, 0, nullptr,
+                                                                        nullptr, (const i64*)lnt, (i64*)out, M, 0, fr);
+  return launched(1);
+}
+
+int bx_int_logp(const int64_t* logits, int64_t ld, const int64_t* tok, const int64_t* lnt, const int64_t* tab2,
+                int tab_len, void* scratch, int64_t* out, int M, int V, int fr, void* stream) {
+  if (!logp_args_ok(logits, ld, scratch, M, V) || !tok || !lnt || !tab2 || ((uintptr_t)tab2 & 15) || !out || tab_len != LSE_LAST + 1 ||
+      fr <= LSE_STEP || fr > 24)
+    return BX_EARG;
+  if (M == 0) return BX_OK;
+  int ch, nch;
+  logp_plan(M, V, ch, nch);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nch0 = sample_chunks(M, V);
+  i64* pmax = (i64*)scratch;                       // chunk maxima, then (entry 0 of each row) the row maximum
+  i64* psum = pmax + (size_t)M * nch0;
+  logp_max_kernel<<<dim3(nch, M), LOGP_THREADS, 0, st>>>((const i64*)logits, ld, pmax, V, ch, nch);
+  // the row maxima go to out[], which the last kernel overwrites after reading them
+  logp_sum_kernel<<<dim3(nch, M), LOGP_THREADS, 0, st>>>((const i64*)logits, ld, nullptr, pmax, nch, (i64*)out,
+                                                        (const longlong2*)tab2, psum, V, ch, nch, fr);
+  logp_finish_kernel<<<(M + 127) / 128, 128, 0, st>>>(psum, nch, nullptr, (const i64*)logits, ld, (const i64*)tok,
+                                                      (const i64*)out, (const i64*)lnt, (i64*)out, M, V, fr);
+  return launched(3);
 }
 
 int bx_exact_silu_prod(const int64_t* y, const int64_t* lut, int64_t* P, int64_t* rowmax, int32_t* flag, int N, int FFl,

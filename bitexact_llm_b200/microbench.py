@@ -12,7 +12,7 @@ gemmr: the fused projections of one layer with REAL constants (bf16 weights from
       timed as a CUDA graph over enough weight sets to exceed L2, with and without the residual lists.
 attn: exact-mode paged decode attention, 8 KV heads x 4 query heads, head_dim 64, 16-token pages, context lengths
       uniform in [64, 2 ctx - 64] (algorithmic bytes = 384 per key and KV head).
-stages: add + RMSNorm + quant (D 2048: 16 D read + 15 D written per row), SiLU * up + quant (FF 8192: 16 FF read,
+stages (the last line: integer log p, two passes of 8 V bytes per row): add + RMSNorm + quant (D 2048: 16 D read + 15 D written per row), SiLU * up + quant (FF 8192: 16 FF read,
       7 FF written), attention output division (2048 columns: 8 read, 7 written per element) and the seeded
       Gumbel-max sampler (V 128256: 8 V read per row), on random in-range rows.
 """
@@ -236,6 +236,11 @@ def stages(args):
     ls = sets(n, lambda: R(-(1 << 28), 1 << 28, M, V))
     rows = torch.stack([R(0, 1 << 40, M), R(0, 1000, M), R(1, 9, M), R(1, 9, M)], 1)
     report("sample", _graph_time(lambda i: sample_rows(ls[i], rows, lnt, 24), n, args.iters), 8.0 * M * V)
+    from .vllm_plugin.rl import int_logp_q
+    toks = R(0, V, M)
+    l16 = [x >> 8 for x in ls]                                                     # logits at 16 bits in (-16, 16)
+    del ls
+    report("int_logp", _graph_time(lambda i: int_logp_q(l16[i], toks, lnt, 16), n, args.iters), 16.0 * M * V)
     print(json.dumps({"bound_flag": int(fl)}))
     return out
 

@@ -88,6 +88,43 @@ def allreduce_max(x, group=None):
     return x
 
 
+def allreduce_sum(x, group=None):
+    """Integer sum over the ranks, in place (exact in any order while the total stays below 2^63)."""
+    if dist.get_world_size(group) > 1:
+        dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+    return x
+
+
+def sharded_logp_q(lg, v0, tok, lnt, fr=16, group=None):
+    """Integer log p (int64 [M] at 2^-40, identical on every rank) of tok [M] from a COLUMN SHARD of the logits:
+    lg int64 [M, V_local] holds vocabulary entries v0 .. v0 + V_local - 1 of every row. Three exchanges on [M]: the
+    integer maximum of the shard maxima, the integer sum of the shards' e^(l - max) sums, and the target term from the
+    one rank that holds the token. The bits are those of `vllm_plugin.rl.int_logp_q` on the gathered rows."""
+    from . import _native as nv
+    from .vllm_plugin.rl import pair_table
+    M, Vl = lg.shape
+    assert lg.dtype == torch.int64 and lg.stride(1) == 1
+    lib, dev, st = nv.lib(), lg.device, nv.stream()
+    tab = pair_table(dev)
+    scratch = torch.empty(max(1, lib.bx_logp_scratch_bytes(M, Vl)), dtype=torch.uint8, device=dev)
+    mx = torch.empty(M, dtype=torch.long, device=dev)
+    nv.check(lib.bx_logp_rowmax(lg.data_ptr(), lg.stride(0), scratch.data_ptr(), mx.data_ptr(), M, Vl, st),
+             "bx_logp_rowmax")
+    allreduce_max(mx, group)
+    S = torch.empty(M, dtype=torch.long, device=dev)
+    nv.check(lib.bx_logp_rowsum(lg.data_ptr(), lg.stride(0), mx.data_ptr(), tab.data_ptr(), tab.shape[0],
+                                scratch.data_ptr(), S.data_ptr(), M, Vl, fr, st), "bx_logp_rowsum")
+    allreduce_sum(S, group)
+    loc = tok.long() - v0
+    mine = (loc >= 0) & (loc < Vl)
+    zt = torch.where(mine, lg.gather(1, loc.clamp(0, Vl - 1)[:, None])[:, 0] - mx, torch.full_like(mx, -(1 << 63)))
+    allreduce_max(zt, group)                                  # exactly one rank holds the token's column
+    out = torch.empty(M, dtype=torch.long, device=dev)
+    nv.check(lib.bx_logp_finish(S.data_ptr(), zt.data_ptr(), lnt.data_ptr(), out.data_ptr(), M, fr, st),
+             "bx_logp_finish")
+    return out
+
+
 def shard_gate_up_constants(c, name, FF, f0, f1):
     """Constants of the fused gate / up linear `name` (weight rows [0, FF) = gate, [FF, 2 FF) = up) restricted to the
     intermediate columns [f0, f1): the rank's gate rows followed by its up rows."""

@@ -279,6 +279,30 @@ int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int6
 int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
                     int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream);
 
+/* ---- integer log p ---------------------------------------------------------------------------------------------
+ * Integer log p of tok [M] under int64 logits rows [M, V] (row stride ld) at fr fractional bits (13..24; the
+ * reference's int8 mode uses 16): out int64 [M] = the value at 2^-40; the caller converts to float64 as the
+ * reference does. lnt = ln table int64 [65537] at 40 bits; tab = e^x at 44 bits for x in [-40, 0] at step 2^-12,
+ * int64 [tab_len = 163841] (rl.lse_table, rl.py:32-40), handed over as tab2 = int64 [tab_len][2], 16-byte aligned,
+ * tab2[i] = (tab[i], tab[min(i + 1, tab_len - 1)]) (bx_logp_pair_table builds it on the device, once per table);
+ * scratch: bx_logp_scratch_bytes(M, V) bytes. A token outside [0, V) gives INT64_MIN in
+ * its row (the reference's gather raises there). Replaces rl.int_logp (src/bitexact/vllm_plugin/rl.py:43-65) and
+ * tri_logp.logp (src/bitexact/vllm_plugin/tri_logp.py:70-91). */
+size_t bx_logp_scratch_bytes(int M, int V);
+int bx_logp_pair_table(const int64_t* tab, int tab_len, int64_t* tab2, void* stream);
+int bx_int_logp(const int64_t* logits, int64_t ld, const int64_t* tok, const int64_t* lnt, const int64_t* tab2,
+                int tab_len, void* scratch, int64_t* out, int M, int V, int fr, void* stream);
+/* The same computation in steps, for a COLUMN SHARD of the vocabulary: the shard's row maxima; the shard's sum of
+ * e^(l - rowmax) terms against the maximum of the full row (the caller's all-reduce MAX of the shard maxima); and,
+ * on [M], log p from the full sum S (the all-reduce SUM of the shard sums, < 2^62) and the target term
+ * zt = l_tok - rowmax. Integer max and sum: every sharding gives the bits of the full row. The reference never
+ * shards the vocabulary; its chunked kernels (_stat_kernel / _sum_kernel, tri_logp.py:27-67) are the same split
+ * inside one GPU. */
+int bx_logp_rowmax(const int64_t* logits, int64_t ld, void* scratch, int64_t* rowmax, int M, int V, void* stream);
+int bx_logp_rowsum(const int64_t* logits, int64_t ld, const int64_t* rowmax, const int64_t* tab2, int tab_len,
+                   void* scratch, int64_t* S, int M, int V, int fr, void* stream);
+int bx_logp_finish(const int64_t* S, const int64_t* zt, const int64_t* lnt, int64_t* out, int M, int fr, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

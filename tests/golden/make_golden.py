@@ -146,6 +146,28 @@ def sampler():
                         logits=n(logits), tok_greedy=n(tok_g), tok_t07=n(tok_t))
 
 
+def logp():
+    """Integer log p (rl.int_logp) of seeded int64 logits rows at 16 bits: ordinary, peaked, flat and far-below rows."""
+    import hashlib
+    from bitexact.llama import ln_table
+    from bitexact.vllm_plugin import rl
+    g = torch.Generator().manual_seed(31)
+    lnt = ln_table(40)
+    V = 3001
+    lg = torch.randint(-(12 << 16), 12 << 16, (7, V), generator=g)
+    lg[1] = lg[1] >> 6                                          # a nearly flat row
+    lg[2, 17] = 90 << 16                                        # a peaked row: everything else below the table's range
+    lg[3] = 5 << 16                                             # all equal
+    lg[4, ::3] = -(1 << 40)                                     # far below: the clamp of the table argument
+    lg[5, 5] = -(1 << 58)                                       # the target's clamp at -2^36
+    lg[6] = lg[6] * 37 + 11                                     # remainders of every size
+    tok = torch.tensor([0, 3000, 17, 1234, 3, 5, 77])
+    tab = rl.lse_table("cpu")
+    lp = rl.int_logp(lg, tok, lnt)
+    np.savez_compressed(os.path.join(HERE, "logp.npz"), logits=n(lg), tok=n(tok), logp=n(lp),
+                        tab_sha=np.array(hashlib.sha256(n(tab).tobytes()).hexdigest()), tab_sample=n(tab[::997]))
+
+
 def int8_ops():
     """int8-mode linear through the reference's CPU path: quant_rows -> imm -> post."""
     from bitexact.int8 import ops as iops
@@ -252,6 +274,7 @@ def tiny_model_int8():
 if __name__ == "__main__":
     exact_ops()
     sampler()
+    logp()
     int8_ops()
     tiny_model()
     tiny_model_int8()

@@ -1,5 +1,6 @@
 """2, 4 or 8 ranks over NCCL (the largest of these that the box has GPUs for; skipped below 2): the column-sharded LM head gathers to the single-GPU
-logits bit for bit and the sharded sampler picks the single-GPU tokens; the column-sharded MLP (gate / up and down
+logits bit for bit, the sharded sampler picks the single-GPU tokens and the sharded integer log p gives the
+single-GPU integers; the column-sharded MLP (gate / up and down
 split by output column, integer all-reduce MAX of the SiLU row maxima) gives the single-GPU output; sequence-sharded decode of a batch split
 over the ranks reproduces the reference's tokens and logits hashes of every sequence."""
 
@@ -44,6 +45,11 @@ def _worker(rank, world, port, ret):
         ok &= torch.equal(head.full_logits(q, sh, eng.fl), full)
         rows = torch.tensor([[r, 2 * r, (7 if r % 2 else 0), (10 if r % 2 else 1)] for r in range(7)], device=dev)
         ok &= torch.equal(head.sample(q, sh, eng.fl, rows, eng.ln), sampler.sample_rows(full, rows, eng.ln))
+        # (1a) integer log p from the column shard of the logits: the bits of the full rows
+        from bitexact_llm_b200.vllm_plugin import rl
+        tk = torch.tensor([0, 5, 128255, 70000, 16032, 16031, 99], device=dev)
+        ok &= torch.equal(par.sharded_logp_q(head.local_logits(q, sh, eng.fl), head.v0, tk, eng.ln, 24),
+                          rl.int_logp_q(full, tk, eng.ln, 24))
         # (1b) column-sharded MLP of layer 0: the single-GPU wgu -> silu_quant -> wd output on every rank
         hq = torch.randint(-(1 << 22), (1 << 22) + 1, (6, eng.D), generator=g).to(torch.int32).to(dev)
         hs = torch.randint(-40, -30, (6,), generator=g).to(dev)

@@ -212,3 +212,26 @@ def test_gumbel_noise_is_monotone_in_the_uniform():
             sel = (u > lo) & (u <= t)
             gt = osamp.gumbel(np.array([t], dtype=np.int64) << 11, lnt, bits)[0]
             assert (g[sel] <= gt).all(), j
+
+
+def test_golden_integer_logp_and_table():
+    """oracle.logp against rl.int_logp of the reference (ordinary, flat, peaked, constant and far-below rows, the two
+    clamps), the e^x table against the reference's (hash and samples), for the oracle's numpy table and the package's."""
+    import torch
+    from bitexact_llm_b200.vllm_plugin import rl
+    from oracle import logp as ol
+    z = np.load(os.path.join(GOLD, "logp.npz"))
+    tab = ol.lse_table()
+    assert hashlib.sha256(tab.tobytes()).hexdigest() == str(z["tab_sha"])
+    assert np.array_equal(tab[::997], z["tab_sample"])
+    assert torch.equal(rl.lse_table("cpu"), torch.from_numpy(tab))
+    lnt = ox.ln_table(40)
+    got = ol.int_logp(z["logits"], z["tok"], lnt, tab)
+    assert np.array_equal(got, z["logp"])
+    # shards of the vocabulary: integer max of maxima, integer sum of sums -> the same integer
+    lg = z["logits"].astype(np.int64)
+    q = ol.int_logp_q(lg, z["tok"], lnt, tab)
+    mx = lg.max(1, keepdims=True)
+    S = sum(ol.shard_sum(lg[:, a:b], mx, tab) for a, b in ((0, 1000), (1000, 1001), (1001, 3001)))
+    zt = np.take_along_axis(lg, z["tok"][:, None], 1)[:, 0] - mx[:, 0]
+    assert np.array_equal(ol.finish(S, zt, lnt), q)
