@@ -92,6 +92,8 @@ def gemmr(args):
             nsets = max(2, (200 << 20) // (3 * N * K) + 1)
             sets = [FusedLin(Lin({k: (v.clone() if torch.is_tensor(v) else v) for k, v in d0.items()}, None, dev))
                     for _ in range(nsets)]
+            for f in sets:
+                f.cfg = args.tile or None
             q = torch.randint(-(1 << 22), (1 << 22) + 1, (M, K), dtype=torch.int32, device=dev)
             planes = torch.empty(3, M, K, dtype=torch.int8, device=dev)
             nv.check(lib.bx_split_limbs(q.data_ptr(), K, planes.data_ptr(), M, K, nv.stream()), "bx_split_limbs")
