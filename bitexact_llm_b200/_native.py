@@ -56,6 +56,8 @@ _SIGNATURES = {
     "bx_sample_scratch_bytes": (Z, [I, I]),
     "bx_sample": (I, [P, L, P, P, P, P, I, I, I, P]),
     "bx_sample_shard": (I, [P, L, P, P, P, P, P, I, I, L, I, P]),
+    "bx_decompose_rows": (I, [P, L, P, P, P, P, P, I, I, P]),
+    "bx_decompose_residual": (I, [P, L, P, P, P, P, P, P, I, I, P]),
     "bx_logp_scratch_bytes": (Z, [I, I]),
     "bx_logp_pair_table": (I, [P, I, P, P]),
     "bx_int_logp": (I, [P, L, P, P, P, I, P, P, I, I, I, P]),

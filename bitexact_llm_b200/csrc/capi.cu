@@ -14,6 +14,7 @@
 #include "paged_attention.cuh"
 #include "sampler.cuh"
 #include "logp.cuh"
+#include "decompose.cuh"
 #include "unfused.cuh"
 
 namespace {
@@ -726,6 +727,24 @@ int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, cons
                     int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream) {
   if (!best) return BX_EARG;
   return run_sample(logits, ld, rows, lnt, scratch, idx, best, M, V_local, v_offset, bits, stream);
+}
+
+// ---- weight preparation (load time) ----
+int bx_decompose_rows(const uint16_t* w, int64_t ldw, int8_t* limbs, int64_t* g, int64_t* d, int32_t* cnt, int32_t* flag,
+                      int N, int K, void* stream) {
+  if (!w || !limbs || !g || !d || !cnt || !flag || N < 0 || K <= 0 || ldw < K) return BX_EARG;
+  if (N == 0) return BX_OK;
+  decompose_rows_kernel<<<N, DEC_THREADS, 0, (cudaStream_t)stream>>>(w, ldw, limbs, (i64*)g, (i64*)d, cnt, flag, N, K);
+  return launched(1);
+}
+
+int bx_decompose_residual(const uint16_t* w, int64_t ldw, const int64_t* g, const int64_t* d, const int64_t* start,
+                          int64_t* rr, int64_t* rc, int64_t* rv, int N, int K, void* stream) {
+  if (!w || !g || !d || !start || !rr || !rc || !rv || N < 0 || K <= 0 || ldw < K) return BX_EARG;
+  if (N == 0) return BX_OK;
+  decompose_residual_kernel<<<N, DEC_THREADS, 0, (cudaStream_t)stream>>>(w, ldw, (const i64*)g, (const i64*)d,
+                                                                         (const i64*)start, (i64*)rr, (i64*)rc, (i64*)rv, K);
+  return launched(1);
 }
 
 // ---- integer log p ----------------------------------------------------------------------------------------------

@@ -1,8 +1,9 @@
 """Weight preparation of exact mode: bf16 weights -> 3 dense int8 limbs + sparse low-bit residual.
 
 Mirrors the interface of the reference's `bitexact.exact.consts` (`bf16_parts`, `decompose`, constants;
-src/bitexact/exact/consts.py:23-107) and produces the same tensors.  Written with torch ops so that it runs on
-the device that holds the weights (it is a load-time step, not part of the decode path).
+src/bitexact/exact/consts.py:23-107) and produces the same tensors.  Weights that live on a GPU are decomposed by
+two sm_100a kernels (`bx_decompose_rows`, `bx_decompose_residual`); the torch-op form below serves host tensors
+(it is a load-time step, not part of the decode path).
 """
 
 import torch
@@ -45,6 +46,8 @@ def decompose(w, row_chunk=4096):
     (consts.py:67-107)."""
     N, K = w.shape
     dev = w.device
+    if w.is_cuda:
+        return _decompose_device(w)
     smax = _smax_table(dev)
     limbs = torch.empty(3, N, K, dtype=torch.int8, device=dev)
     gs, ds, rrs, rcs, rvs = [], [], [], [], []
@@ -87,6 +90,41 @@ def decompose(w, row_chunk=4096):
         gs.append(g), ds.append(d), rrs.append(rr + r0), rcs.append(rc), rvs.append(rv)
     return {"limbs": limbs, "g": torch.cat(gs), "d": torch.cat(ds), "rr": torch.cat(rrs), "rc": torch.cat(rcs),
             "rv": torch.cat(rvs)}
+
+
+def _decompose_device(w):
+    """`decompose` of a bf16 tensor that lives on a GPU: two row-parallel kernels (limbs, g, d, counts; then the
+    coordinate list at the offsets of the counts' prefix sum). One host sync for the number of entries."""
+    from .. import _native as nv
+    N, K = w.shape
+    assert w.dtype == torch.bfloat16
+    w = w.contiguous()
+    dev, lib, st = w.device, nv.lib(), nv.stream()
+    limbs = torch.empty(3, N, K, dtype=torch.int8, device=dev)
+    g = torch.empty(N, dtype=torch.long, device=dev)
+    d = torch.empty(N, dtype=torch.long, device=dev)
+    cnt = torch.empty(N, dtype=torch.int32, device=dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    nv.check(lib.bx_decompose_rows(w.data_ptr(), w.stride(0), limbs.data_ptr(), g.data_ptr(), d.data_ptr(),
+                                   cnt.data_ptr(), flag.data_ptr(), N, K, st), "bx_decompose_rows")
+    incl = torch.cumsum(cnt.long(), 0)
+    f = int(flag)
+    if f & 1:
+        raise ValueError("inf/nan weight")
+    if f & 2:
+        raise ValueError("residual grid too fine")
+    if f & 4:
+        raise ValueError("limb split left a remainder")
+    total = int(incl[-1]) if N else 0
+    rr = torch.empty(total, dtype=torch.long, device=dev)
+    rc = torch.empty(total, dtype=torch.long, device=dev)
+    rv = torch.empty(total, dtype=torch.long, device=dev)
+    if total:
+        start = (incl - cnt).contiguous()
+        nv.check(lib.bx_decompose_residual(w.data_ptr(), w.stride(0), g.data_ptr(), d.data_ptr(), start.data_ptr(),
+                                           rr.data_ptr(), rc.data_ptr(), rv.data_ptr(), N, K, st),
+                 "bx_decompose_residual")
+    return {"limbs": limbs, "g": g, "d": d, "rr": rr, "rc": rc, "rv": rv}
 
 
 def exp2_table(device="cpu"):

@@ -279,6 +279,18 @@ int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int6
 int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
                     int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream);
 
+/* ---- weight preparation (load time) ----------------------------------------------------------------------------
+ * bf16 weights w [N, K] (raw 16-bit patterns, row stride ldw) -> the constants of the exact-mode linear layer:
+ * limbs int8 [3][N][K], per-row grid exponent g and residual depth d (int64 [N]), cnt int32 [N] = residual entries
+ * of each row. flag (int32, OR-ed): 1 = inf / nan weight, 2 = residual grid finer than 30 bits, 4 = a value that
+ * three limbs do not hold (the host code raises ValueError in these cases). Then, with start = the exclusive prefix
+ * sum of cnt, bx_decompose_residual writes the coordinate list (rr, rc, rv int64 [sum cnt]) in row-major order.
+ * Replaces exact.consts.decompose / bf16_parts (src/bitexact/exact/consts.py:33-107), which run on the host. */
+int bx_decompose_rows(const uint16_t* w, int64_t ldw, int8_t* limbs, int64_t* g, int64_t* d, int32_t* cnt, int32_t* flag,
+                      int N, int K, void* stream);
+int bx_decompose_residual(const uint16_t* w, int64_t ldw, const int64_t* g, const int64_t* d, const int64_t* start,
+                          int64_t* rr, int64_t* rc, int64_t* rv, int N, int K, void* stream);
+
 /* ---- integer log p ---------------------------------------------------------------------------------------------
  * Integer log p of tok [M] under int64 logits rows [M, V] (row stride ld) at fr fractional bits (13..24; the
  * reference's int8 mode uses 16): out int64 [M] = the value at 2^-40; the caller converts to float64 as the
