@@ -168,6 +168,43 @@ def logp():
                         tab_sha=np.array(hashlib.sha256(n(tab).tobytes()).hexdigest()), tab_sample=n(tab[::997]))
 
 
+def plan_meta():
+    """The step description used for the batch-layout fixture: 7 requests (decodes, prefill chunks of several
+    lengths, one request without query tokens), 3 padding rows."""
+    from types import SimpleNamespace
+    qlen = [1, 5, 1, 0, 17, 5, 1]
+    seq = [9, 5, 40, 3, 30, 12, 1]
+    qsl = [0]
+    for q in qlen:
+        qsl.append(qsl[-1] + q)
+    n = qsl[-1]
+    g = torch.Generator().manual_seed(77)
+    bt = torch.randint(1, 50, (len(qlen), 4), generator=g, dtype=torch.int32)
+    slot = torch.randint(16, 800, (n + 3,), generator=g)
+    pos = torch.cat([torch.arange(s - q, s) for q, s in zip(qlen, seq)] + [torch.zeros(3, dtype=torch.long)])
+    meta = SimpleNamespace(query_start_loc=torch.tensor(qsl, dtype=torch.int32), seq_lens=torch.tensor(seq, dtype=torch.int32),
+                           block_table=bt, slot_mapping=slot)
+    return meta, n + 3, pos
+
+
+def plan():
+    """paged.make_plan / Plan.groups of the reference on plan_meta(), with a small group cap so that the prefill
+    requests split into two groups."""
+    from bitexact.vllm_plugin import paged
+    meta, N, pos = plan_meta()
+    out = {}
+    for tag, cap in (("a", paged.GROUP_BYTES), ("b", 2 * 17 * 2048 * 8 - 1)):
+        paged.GROUP_BYTES = cap
+        p = paged.make_plan(meta, N, pos)
+        out.update({f"{tag}_n": np.array(p.n), f"{tag}_slot": n(p.slot), f"{tag}_bt": n(p.block_table),
+                    f"{tag}_dec_req": n(p.dec_req), f"{tag}_dec_tok": n(p.dec_tok), f"{tag}_pre": np.array(p.pre),
+                    f"{tag}_ngroups": np.array(len(p.groups()))})
+        for i, gr in enumerate(p.groups()):
+            out.update({f"{tag}_g{i}_req": n(gr.req), f"{tag}_g{i}_idx": n(gr.idx), f"{tag}_g{i}_pos": n(gr.pos),
+                        f"{tag}_g{i}_valid": n(gr.valid), f"{tag}_g{i}_dst": n(gr.dst)})
+    np.savez_compressed(os.path.join(HERE, "plan.npz"), **out)
+
+
 def int8_ops():
     """int8-mode linear through the reference's CPU path: quant_rows -> imm -> post."""
     from bitexact.int8 import ops as iops
@@ -275,6 +312,7 @@ if __name__ == "__main__":
     exact_ops()
     sampler()
     logp()
+    plan()
     int8_ops()
     tiny_model()
     tiny_model_int8()
