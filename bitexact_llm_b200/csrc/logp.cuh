@@ -94,10 +94,15 @@ __global__ void __launch_bounds__(LOGP_THREADS) logp_sum_kernel(const i64* __res
   const i64* x = lg + (i64)row * ld;
   i64 acc = 0;
   int c = c0 + threadIdx.x;
-  for (; c + 3 * LOGP_THREADS < c1; c += 4 * LOGP_THREADS) {
-    const i64 a0 = __ldg(x + c), a1 = __ldg(x + c + LOGP_THREADS), a2 = __ldg(x + c + 2 * LOGP_THREADS),
-              a3 = __ldg(x + c + 3 * LOGP_THREADS);
-    acc += lse_term(a0, mx, tab, fr) + lse_term(a1, mx, tab, fr) + lse_term(a2, mx, tab, fr) + lse_term(a3, mx, tab, fr);
+  constexpr int U = 8;                                     // gathers in flight per thread: the pass is latency bound
+  for (; c + (U - 1) * LOGP_THREADS < c1; c += U * LOGP_THREADS) {
+    i64 a[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) a[k] = __ldg(x + c + k * LOGP_THREADS);
+#pragma unroll
+    for (int k = 0; k < U; ++k) a[k] = lse_term(a[k], mx, tab, fr);
+#pragma unroll
+    for (int k = 0; k < U; ++k) acc += a[k];
   }
   for (; c < c1; c += LOGP_THREADS) acc += lse_term(__ldg(x + c), mx, tab, fr);
 #pragma unroll
