@@ -32,8 +32,8 @@ def _worker(rank, world, port, ret):
         z = np.load(os.path.join(ROOT, "tests", "golden", "tiny_model.npz"))
         tables = {"cos": torch.zeros(4096, 32, dtype=torch.long), "sin": torch.zeros(4096, 32, dtype=torch.long)}
         tables["cos"][:128], tables["sin"][:128] = torch.from_numpy(z["cos"]), torch.from_numpy(z["sin"])
-        c = consts.build(TINY, tiny_state_dict(), tables=tables)
         dev = torch.device("cuda", rank)
+        c = consts.build(TINY, {k: v.to(dev) for k, v in tiny_state_dict().items()}, tables=tables)   # device decompose
         eng = ExactEngine(c, dev)
         ok = True
         # (1) column-sharded head: same hidden rows on every rank
