@@ -124,6 +124,13 @@ norm_kernel(const void* __restrict__ xin, const i64* __restrict__ yin, const i64
   __shared__ i64 red[33];
   const int64_t row = blockIdx.x;
   i64 x[EPT];
+  i64 gmr[EPT], ger[EPT];          // gamma, loaded up front: their latency overlaps the row's loads and reductions
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) {
+    const int c = threadIdx.x + k * NT;
+    gmr[k] = (do_norm && c < D) ? __ldg(gm + c) : 0;
+    ger[k] = (do_norm && c < D) ? __ldg(ge + c) : 0;
+  }
   i64 ax = 0;
 #pragma unroll
   for (int k = 0; k < EPT; ++k) {
@@ -163,7 +170,7 @@ norm_kernel(const void* __restrict__ xin, const i64* __restrict__ yin, const i64
   for (int k = 0; k < EPT; ++k) {
     const int c = threadIdx.x + k * NT;
     if (c < D) {
-      x[k] = div_round_recip<3>(x[k] * gm[c], ge[c] - FR - er + FN, (u64)r, inv);
+      x[k] = div_round_recip<3>(x[k] * gmr[k], ger[k] - FR - er + FN, (u64)r, inv);
       pmax = imax(pmax, iabs(x[k]));
     }
   }

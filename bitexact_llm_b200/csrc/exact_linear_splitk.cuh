@@ -73,6 +73,13 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
   bool acc_ok = false;                                                // epilogue warps: accumulators complete
+  // leader's epilogue threads: constants of weight row n (see ExactEpilogue), loaded before the accumulators exist
+  constexpr int RMAX = 4;
+  bool nok = false;
+  int d = 0, cnt = 0, wcnt = 0;
+  i64 gd = 0;
+  int ecr[RMAX] = {0, 0, 0, 0};
+  i64 evr[RMAX] = {0, 0, 0, 0};
 
   if (warp == 0) {
     if (lane == 0 && !dead) {
@@ -139,6 +146,23 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
     }
   } else {
+    // ---- epilogue warps of the leader: the per-row constants and the residual list of weight row n do not depend on
+    //      the accumulators; at decode sizes this kernel is a latency chain, so their loads start before the wait ----
+    if (rank == 0) {
+      const int n = n0 + (warp & 3) * 32 + lane;
+      nok = n < ep.N;
+      d = nok ? (int)ep.d[n] : 0;
+      gd = nok ? ep.g[n] - (i64)d + FR : 0;
+      cnt = (nok && ep.cnt) ? ep.cnt[n] : 0;
+#pragma unroll
+      for (int j = 0; j < RMAX; ++j) {
+        if (j < cnt) {
+          ecr[j] = ep.ec[(i64)n * ep.R + j];
+          evr[j] = ep.ev[(i64)n * ep.R + j];
+        }
+      }
+      wcnt = __reduce_max_sync(0xffffffffu, cnt);                      // longest list in the warp (uniform)
+    }
     // ---- epilogue warps: wait for this CTA's accumulators ----
     bool ok = !dead;
     if (ok && nkb > 0) ok = mbar_wait(&sh->acc_full, 0);
@@ -184,24 +208,6 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   if (warp >= 2 && rank == 0) {
     // ---- the leader: own sums + the slices, then the epilogue of exact_linear_kernel ----
     const int n = n0 + row;
-    const bool nok = n < ep.N;
-    const int d = nok ? (int)ep.d[n] : 0;
-    const i64 gd = nok ? ep.g[n] - (i64)d + FR : 0;
-    const int cnt = (nok && ep.cnt) ? ep.cnt[n] : 0;
-    constexpr int RMAX = 4;                                          // residual list of row n, read once (see ExactEpilogue)
-    int ecr[RMAX];
-    i64 evr[RMAX];
-#pragma unroll
-    for (int j = 0; j < RMAX; ++j) {
-      ecr[j] = 0;
-      evr[j] = 0;
-      if (j < cnt) {
-        ecr[j] = ep.ec[(i64)n * ep.R + j];
-        evr[j] = ep.ev[(i64)n * ep.R + j];
-      }
-    }
-    const int wcnt = __reduce_max_sync(0xffffffffu, cnt);              // longest list in the warp (uniform)
-    const bool warp_res = wcnt > 0;
     bool any_bad = false;
 #pragma unroll 1
     for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
@@ -222,7 +228,7 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
                 shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
           for (int r = 1; r < S; ++r) T += partial[((size_t)(r - 1) * TA + c0 + i) * WROWS + row];
           i64 B = 0;
-          if (warp_res) {
+          if (wcnt > 0) {
 #pragma unroll
             for (int j = 0; j < RMAX; ++j)
               if (j < wcnt && j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
