@@ -247,6 +247,10 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
     const int lim = ta == 16 ? splitk_limit<16>() : ta == 32 ? splitk_limit<32>() : splitk_limit<64>();
     if (split > lim) split = lim;
     if (split > nkb / 2) split = nkb / 2;                      // at least two K blocks per slice
+    while (split & (split - 1)) --split;   // clusters of 2, 4 or 8: a cluster of 6 ran 1.6 x slower than one of 4
+    // automatic choice: at most 4 (clusters of 8 measured 1.3 - 1.5 x slower on these shapes: fewer of them are
+    // resident at a time); an explicit request (tile_rows 2xx) may still take 8
+    if (tile_rows == 0 && split > 4) split = 4;
   }
   CUtensorMap mw, ma;
   if (!make_map(&mw, limbs, (uint64_t)K, (uint64_t)N, 3, WROWS)) return BX_ELAUNCH;

@@ -3,10 +3,12 @@
 // With one CTA per 128 weight rows, the down projection (N = 2048, K = 8192) has 16 CTAs: 16 of 148 SMs stream the
 // 50 MB of weight limbs and a batch-1 decode step runs at a fraction of the HBM rate. Here a thread-block CLUSTER of S
 // CTAs shares an output tile: CTA `rank` runs the tcgen05 main loop of limb_gemm.cuh over its slice of the K blocks;
-// the int32 limb sums of the slices are joined to int64 in each CTA and the S - 1 partial tiles travel through
-// distributed shared memory (st.shared::cluster into the leader's idle TMA ring, between two cluster barriers); the
-// leader adds them (integer sums: exact in any order) and runs the usual epilogue (sparse residual, one rounding,
-// flag). Same integers as exact_linear_kernel.
+// the int32 limb sums of the slices are joined to int64 in each CTA and reduce-scattered through distributed shared
+// memory: activation row (accumulator column) c of the tile belongs to CTA c mod S, every CTA stores its partial sums
+// of column c into that CTA's idle TMA ring (st.shared::cluster, between two cluster barriers), and every CTA adds
+// the S partial columns it owns (integer sums: exact in any order) and runs the usual epilogue on them (sparse
+// residual, one rounding, flag). The tail of the kernel is shared by the S CTAs instead of falling on one.
+// Same integers as exact_linear_kernel.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -17,12 +19,13 @@ namespace bx {
 
 constexpr int SPLITK_MAX = 8;
 
-// Most K slices a tile of TA activation rows can take: the S - 1 partial tiles (TA x 128 int64) live in the ring.
+// Most K slices a tile of TA activation rows can take: a CTA's ring holds S partial copies of its ceil(TA / S)
+// columns (128 int64 each), at most (TA + S - 1) x 1 KB.
 template <int TA>
 __host__ __device__ constexpr int splitk_limit() {
   using Cfg = GemmCfg<3, 3, TA>;
-  constexpr int fit = 1 + (Cfg::STAGES * Cfg::STAGE_BYTES) / (TA * WROWS * 8);
-  return fit < SPLITK_MAX ? fit : SPLITK_MAX;
+  static_assert((TA + SPLITK_MAX - 1) * WROWS * 8 <= Cfg::STAGES * Cfg::STAGE_BYTES, "partial columns fit in the ring");
+  return SPLITK_MAX;
 }
 
 template <int TA>
@@ -31,11 +34,10 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
                            const ExactEpiParams ep, int K, int m_tiles) {
   namespace cg = cooperative_groups;
   using Cfg = GemmCfg<3, 3, TA>;
-  static_assert((splitk_limit<TA>() - 1) * TA * WROWS * 8 <= Cfg::STAGES * Cfg::STAGE_BYTES, "partial tiles fit in the ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmShared* sh = reinterpret_cast<GemmShared*>(ring + Cfg::STAGES * Cfg::STAGE_BYTES);
-  i64* partial = reinterpret_cast<i64*>(ring);                        // leader: [S - 1][TA][128] after the main loops
+  i64* partial = reinterpret_cast<i64*>(ring);                        // after the main loops: [S sources][owned column][128]
 
   cg::cluster_group cluster = cg::this_cluster();
   const int S = (int)cluster.num_blocks();
@@ -73,7 +75,7 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
   bool acc_ok = false;                                                // epilogue warps: accumulators complete
-  // leader's epilogue threads: constants of weight row n (see ExactEpilogue), loaded before the accumulators exist
+  // epilogue threads: constants of weight row n (see ExactEpilogue), loaded before the accumulators exist
   constexpr int RMAX = 4;
   bool nok = false;
   int d = 0, cnt = 0, wcnt = 0;
@@ -146,9 +148,9 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
     }
   } else {
-    // ---- epilogue warps of the leader: the per-row constants and the residual list of weight row n do not depend on
-    //      the accumulators; at decode sizes this kernel is a latency chain, so their loads start before the wait ----
-    if (rank == 0) {
+    // ---- epilogue warps: the per-row constants and the residual list of weight row n do not depend on the
+    //      accumulators; at decode sizes this kernel is a latency chain, so their loads start before the wait ----
+    {
       const int n = n0 + (warp & 3) * 32 + lane;
       nok = n < ep.N;
       d = nok ? (int)ep.d[n] : 0;
@@ -173,7 +175,7 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     acc_ok = ok && nkb > 0;
   }
 
-  // Every CTA of the cluster has finished its main loop: the leader's ring is idle and can take the partial tiles.
+  // Every CTA of the cluster has finished its main loop: the rings are idle and can take the partial columns.
   tc_fence_before();
   __syncthreads();
   cluster.sync();
@@ -181,9 +183,9 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   const int quarter = warp & 3, group = (warp - 2) >> 2;
   const int row = quarter * 32 + lane;                                // TMEM lane = weight row of the tile
   const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
-  if (warp >= 2 && rank != 0) {
-    // ---- a slice CTA: join its limb sums and send them to the leader ----
-    i64* dst = cluster.map_shared_rank(partial, 0) + (size_t)(rank - 1) * TA * WROWS;
+  const int own = (TA + S - 1) / S;                                   // columns a CTA owns at most
+  if (warp >= 2) {
+    // ---- join this CTA's limb sums and send column c to CTA c mod S, slot [this rank][c / S] ----
 #pragma unroll 1
     for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
       if (m0 + c0 >= ep.M) break;
@@ -195,52 +197,41 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
+        const int c = c0 + i;
+        if (m0 + c >= ep.M) break;
         i64 T = 0;
         if (acc_ok)
           T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +
               shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
-        dst[(size_t)(c0 + i) * WROWS + row] = T;
+        i64* dst = cluster.map_shared_rank(partial, c % S);
+        dst[((size_t)rank * own + c / S) * WROWS + row] = T;
       }
     }
   }
-  cluster.sync();                                                     // partial tiles are in the leader's shared memory
+  cluster.sync();                                                     // every partial column is in its owner's ring
 
-  if (warp >= 2 && rank == 0) {
-    // ---- the leader: own sums + the slices, then the epilogue of exact_linear_kernel ----
+  if (warp >= 2) {
+    // ---- the columns this CTA owns: sum of the S partials, then the epilogue of exact_linear_kernel ----
     const int n = n0 + row;
     bool any_bad = false;
-#pragma unroll 1
-    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
-      if (m0 + c0 >= ep.M) break;
-      uint32_t acc[5][8];
-      if (acc_ok) {
+    for (int k = group; k < own; k += EPI_GROUPS) {
+      const int c = rank + k * S;
+      const int m = m0 + c;
+      if (c >= TA || m >= ep.M || !nok) continue;
+      i64 T = 0;
+      for (int r = 0; r < S; ++r) T += partial[((size_t)r * own + k) * WROWS + row];
+      i64 B = 0;
+      if (wcnt > 0) {
 #pragma unroll
-        for (int b = 0; b < 5; ++b) tmem_ld8(tbase + b * TA + c0, acc[b]);
-        tmem_ld_wait();
+        for (int j = 0; j < RMAX; ++j)
+          if (j < wcnt && j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
+        for (int j = RMAX; j < cnt; ++j)
+          B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)n * ep.R + j]] * ep.ev[(i64)n * ep.R + j];
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int m = m0 + c0 + i;
-        if (m < ep.M && nok) {
-          i64 T = 0;
-          if (acc_ok)
-            T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +
-                shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
-          for (int r = 1; r < S; ++r) T += partial[((size_t)(r - 1) * TA + c0 + i) * WROWS + row];
-          i64 B = 0;
-          if (wcnt > 0) {
-#pragma unroll
-            for (int j = 0; j < RMAX; ++j)
-              if (j < wcnt && j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
-            for (int j = RMAX; j < cnt; ++j)
-              B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)n * ep.R + j]] * ep.ev[(i64)n * ep.R + j];
-          }
-          bool bad;
-          const i64 yv = round_shift_hl(T, B, d, ep.sh[m] + gd, bad);
-          any_bad |= bad;
-          ep.y[(i64)m * ep.N + n] = yv;
-        }
-      }
+      bool bad;
+      const i64 yv = round_shift_hl(T, B, d, ep.sh[m] + gd, bad);
+      any_bad |= bad;
+      ep.y[(i64)m * ep.N + n] = yv;
     }
     if (ep.checked && any_bad) *ep.flag = 1;
   }
