@@ -283,8 +283,8 @@ __global__ void kv_store_kernel(int8_t* cache, const i64* __restrict__ slot, con
 }
 
 // ---- attention output: o = div_round(num, 5, den), quant(o, -FR) (segs.attn_div + quant; _attn_out_kernel) ----
-constexpr int AO_THREADS = 256;
-constexpr int AO_EPT = 16;     // H * HD <= 4096
+constexpr int AO_THREADS = 512;  // a row is a latency chain: more threads, fewer serial divisions each
+constexpr int AO_EPT = 8;      // H * HD <= 4096
 constexpr int AO_MAXH = 64;
 
 __global__ void __launch_bounds__(AO_THREADS)
@@ -294,21 +294,25 @@ attn_out_kernel(const i64* __restrict__ num, const i64* __restrict__ den, int32_
   __shared__ u64 dens[AO_MAXH], invs[AO_MAXH];
   const int64_t row = blockIdx.x;
   const int nh = K2 / HD;
+  i64 o[AO_EPT];
+#pragma unroll
+  for (int k = 0; k < AO_EPT; ++k) {                  // the numerators are in flight while the reciprocals are made
+    const int c = threadIdx.x + k * AO_THREADS;
+    o[k] = c < K2 ? num[row * K2 + c] : 0;
+  }
   if (threadIdx.x < nh) {
     const u64 dv = (u64)den[row * nh + threadIdx.x];
     dens[threadIdx.x] = dv;
     invs[threadIdx.x] = dv ? ~0ull / dv : 0;
   }
   __syncthreads();
-  i64 o[AO_EPT];
   i64 omax = 0;
 #pragma unroll
   for (int k = 0; k < AO_EPT; ++k) {
     const int c = threadIdx.x + k * AO_THREADS;
-    o[k] = 0;
     if (c < K2) {
       const int hd = c / HD;
-      o[k] = dens[hd] ? div_round_recip<1>(num[row * K2 + c], FR - FV, dens[hd], invs[hd]) : 0;
+      o[k] = dens[hd] ? div_round_recip<1>(o[k], FR - FV, dens[hd], invs[hd]) : 0;
       omax = imax(omax, iabs(o[k]));
     }
   }
