@@ -215,14 +215,32 @@ __global__ void qkv_kernel(const QkvParams p) {
   const int dd = threadIdx.x;              // 0 .. HH-1
   const int64_t NT = (int64_t)(p.H + 2 * p.HKV) * p.HD;
   const i64 pos = p.pos[row];
+  const i64* yr = p.y + row * NT;
+  // Everything the thread reads is requested before the first use: the row's q / k / v values and the slot are in
+  // flight together with the position and the rotation pair that depends on it (the kernel is a latency chain).
+  constexpr int GPRE = 8;
+  i64 xa[GPRE], xb[GPRE];
+#pragma unroll
+  for (int g = 0; g < GPRE; ++g) {
+    xa[g] = 0;
+    xb[g] = 0;
+    if (g < G) {
+      const int64_t qc = (int64_t)(h * G + g) * p.HD + dd;
+      xa[g] = yr[qc];
+      xb[g] = yr[qc + HH];
+    }
+  }
+  const int64_t kc = (int64_t)p.H * p.HD + (int64_t)h * p.HD + dd;
+  const int64_t vc = (int64_t)(p.H + p.HKV) * p.HD + (int64_t)h * p.HD + dd;
+  const i64 k1 = yr[kc], k2 = yr[kc + HH];
+  const i64 v1r = yr[vc], v2r = yr[vc + HH];
+  const i64 slot = p.cache ? p.slot[row] : -1;
   const i64 cs = p.cos[pos * HH + dd];
   const i64 sn = p.sin[pos * HH + dd];
-  const i64* yr = p.y + row * NT;
   i64 big = 0;
   i64 shmax = NEG_BIG;
-  for (int g = 0; g < G; ++g) {
+  auto head = [&](int g, i64 x1, i64 x2) {
     const int64_t qc = (int64_t)(h * G + g) * p.HD + dd;
-    const i64 x1 = yr[qc], x2 = yr[qc + HH];
     big = imax(big, imax(iabs(x1), iabs(x2)));
     const i64 p1 = x1 * cs - x2 * sn;
     const i64 p2 = x2 * cs + x1 * sn;
@@ -233,11 +251,14 @@ __global__ void qkv_kernel(const QkvParams p) {
     qo[0] = (int32_t)rshc(p1, sh + (FR + FT));
     qo[HH] = (int32_t)rshc(p2, sh + (FR + FT));
     if (threadIdx.x == 0) p.sh[row * p.H + h * G + g] = sh;
+  };
+#pragma unroll
+  for (int g = 0; g < GPRE; ++g)
+    if (g < G) head(g, xa[g], xb[g]);                   // G is the same for every thread of the grid
+  for (int g = GPRE; g < G; ++g) {
+    const int64_t qc = (int64_t)(h * G + g) * p.HD + dd;
+    head(g, yr[qc], yr[qc + HH]);
   }
-  const int64_t kc = (int64_t)p.H * p.HD + (int64_t)h * p.HD + dd;
-  const int64_t vc = (int64_t)(p.H + p.HKV) * p.HD + (int64_t)h * p.HD + dd;
-  const i64 k1 = yr[kc], k2 = yr[kc + HH];
-  const i64 v1r = yr[vc], v2r = yr[vc + HH];
   big = imax(big, imax(imax(iabs(k1), iabs(k2)), imax(iabs(v1r), iabs(v2r))));
   const i64 k1o = rshs<FR + FT - FK>(k1 * cs - k2 * sn);
   const i64 k2o = rshs<FR + FT - FK>(k2 * cs + k1 * sn);
@@ -248,7 +269,6 @@ __global__ void qkv_kernel(const QkvParams p) {
   const i64 kvmax = block_reduce<true>(kvbig, red);
   if (threadIdx.x == 0 && (big >= (1ll << 31) || kvmax > LIM3 || shmax > FK + 3 - FZ)) *p.flag = 1;
   if (p.cache) {
-    const i64 slot = p.slot[row];
     if (slot >= 0) {
       int8_t* base = p.cache + (slot / p.bs) * p.sc_nb + (int64_t)h * p.sc_h + (slot % p.bs) * p.sc_bs;
       int kk1 = (int)k1o, kk2 = (int)k2o, vv1 = (int)v1, vv2 = (int)v2;
