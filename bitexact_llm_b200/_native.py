@@ -24,6 +24,7 @@ _SIGNATURES = {
     "bx_launch_count": (ctypes.c_longlong, []),
     "bx_device_status": (I, []),
     "bx_clear_device_status": (I, []),
+    "bx_set_device_status": (I, [I]),
     "bx_exact_linear_scratch_bytes": (Z, [I, I]),
     "bx_exact_linear": (I, [P, L, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, P]),
     "bx_exact_linear_planes": (I, [P, P, L, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, P]),
@@ -101,4 +102,22 @@ def stream():
 
 
 def device_status():
+    """Number of device-side waits that gave up since the last clear (synchronises the device)."""
     return lib().bx_device_status()
+
+
+def clear_device_status():
+    check(lib().bx_clear_device_status(), "bx_clear_device_status")
+
+
+class DeviceWaitError(RuntimeError):
+    """A bounded device-side wait gave up: kernels launched since then may have left their outputs unwritten."""
+
+
+def check_device_status():
+    """Raises DeviceWaitError when the device status word is non-zero (the state stays set until
+    `clear_device_status`)."""
+    n = device_status()
+    if n != 0:
+        raise DeviceWaitError(f"{n} device-side wait(s) timed out: results since then are not valid; "
+                              "call clear_device_status() and rerun the step")

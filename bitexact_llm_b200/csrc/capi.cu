@@ -6,6 +6,8 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "../../include/bitexact_b200.h"
 #include "exact_linear.cuh"
 #include "exact_linear_splitk.cuh"
@@ -24,10 +26,55 @@ using namespace bx;
 
 long long g_launches = 0;   // kernels launched through this library (host-side count)
 
+// Host-side shadow of the device status word: non-zero once the host has SEEN a timed-out device-side wait
+// (bx_device_status) or set one (bx_set_device_status). Launching entry points then return BX_EDEVICE without
+// launching, until bx_clear_device_status. Reading the device word itself needs a synchronising copy, which a
+// launch path cannot afford; the engines' check() does that read.
+std::atomic<int> g_status_seen{0};
+
 inline int launched(int n) {
   if (cudaGetLastError() != cudaSuccess) return BX_ELAUNCH;
   g_launches += n;
   return BX_OK;
+}
+
+// Kernel attributes (opt-in dynamic shared memory) and device properties are per device: every cache of them is
+// indexed by the ordinal of the current device. The flags are atomics so that concurrent first calls from several
+// host threads are well defined (they would store the same value).
+constexpr int BX_MAX_DEVICES = 64;
+
+struct PerDevice {
+  std::atomic<int> v[BX_MAX_DEVICES];
+};
+
+inline int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= BX_MAX_DEVICES) return -1;
+  return dev;
+}
+
+// Runs `setup` (returns cudaError_t) once per device; BX_OK or BX_ELAUNCH.
+template <class F>
+inline int once_per_device(PerDevice& done, F&& setup) {
+  const int dev = current_device();
+  if (dev < 0) return BX_ELAUNCH;
+  if (done.v[dev].load(std::memory_order_acquire)) return BX_OK;
+  if (setup() != cudaSuccess) return BX_ELAUNCH;
+  done.v[dev].store(1, std::memory_order_release);
+  return BX_OK;
+}
+
+// Number of SMs of the current device (0 on error).
+inline int device_sms() {
+  static PerDevice sms;
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int n = sms.v[dev].load(std::memory_order_acquire);
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 0;
+    sms.v[dev].store(n, std::memory_order_release);
+  }
+  return n;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -66,13 +113,12 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 template <int TA>
 int launch_exact(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiParams& ep, int K, cudaStream_t st) {
   using Cfg = GemmCfg<3, 3, TA>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(exact_linear_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) !=
-        cudaSuccess)
-      return BX_ELAUNCH;
-    configured = true;
-  }
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(exact_linear_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
   const int m_tiles = (ep.M + TA - 1) / TA;
   const int n_tiles = (ep.N + WROWS - 1) / WROWS;
   exact_linear_kernel<TA><<<m_tiles * n_tiles, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, m_tiles);
@@ -83,13 +129,12 @@ template <int TA>
 int launch_exact_splitk(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiParams& ep, int K, int split,
                         cudaStream_t st) {
   using Cfg = GemmCfg<3, 3, TA>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(exact_linear_splitk_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::SMEM_BYTES) != cudaSuccess)
-      return BX_ELAUNCH;
-    configured = true;
-  }
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(exact_linear_splitk_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
   const int m_tiles = (ep.M + TA - 1) / TA;
   const int n_tiles = (ep.N + WROWS - 1) / WROWS;
   cudaLaunchConfig_t cfg = {};
@@ -112,18 +157,14 @@ template <int TA>
 int launch_exact_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiParams& ep, int K,
                             cudaStream_t st) {
   using Cfg = GemmCfg<3, 3, TA>;
-  static bool configured = false;
-  static int sms = 0;
-  if (!configured) {
-    if (cudaFuncSetAttribute(exact_linear_persistent_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::SMEM_BYTES) != cudaSuccess)
-      return BX_ELAUNCH;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      return BX_ELAUNCH;
-    configured = true;
-  }
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(exact_linear_persistent_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int sms = device_sms();
+  if (sms <= 0) return BX_ELAUNCH;
   const int m_tiles = (ep.M + TA - 1) / TA;
   const int n_tiles = (ep.N + WROWS - 1) / WROWS;
   const int total = m_tiles * n_tiles;
@@ -135,13 +176,12 @@ int launch_exact_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const 
 template <int TA, bool POST>
 int launch_int8(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParams& ep, int K, cudaStream_t st) {
   using Cfg = GemmCfg<1, 2, TA>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(int8_linear_kernel<TA, POST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::SMEM_BYTES) != cudaSuccess)
-      return BX_ELAUNCH;
-    configured = true;
-  }
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(int8_linear_kernel<TA, POST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
   const int m_tiles = (ep.M + TA - 1) / TA;
   const int n_tiles = (ep.N + WROWS - 1) / WROWS;
   int8_linear_kernel<TA, POST><<<m_tiles * n_tiles, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, m_tiles);
@@ -181,17 +221,28 @@ long long bx_launch_count(void) { return g_launches; }
 int bx_device_status(void) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, bx::g_wait_timeouts, sizeof(int)) != cudaSuccess) return BX_ELAUNCH;
+  if (v != 0) g_status_seen.store(1);
   return v;
 }
 
 int bx_clear_device_status(void) {
   int v = 0;
-  return cudaMemcpyToSymbol(bx::g_wait_timeouts, &v, sizeof(int)) == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  if (cudaMemcpyToSymbol(bx::g_wait_timeouts, &v, sizeof(int)) != cudaSuccess) return BX_ELAUNCH;
+  g_status_seen.store(0);
+  return BX_OK;
+}
+
+int bx_set_device_status(int value) {
+  if (value < 0) return BX_EARG;
+  if (cudaMemcpyToSymbol(bx::g_wait_timeouts, &value, sizeof(int)) != cudaSuccess) return BX_ELAUNCH;
+  g_status_seen.store(value != 0);
+  return BX_OK;
 }
 
 size_t bx_exact_linear_scratch_bytes(int M, int K) { return (size_t)3 * (size_t)M * (size_t)K; }
 
 int bx_split_limbs(const int32_t* q, int64_t ldq, int8_t* a8, int M, int K, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!q || !a8 || M < 0 || K <= 0 || K % 16 || ldq % 4 || ldq < K || !aligned16(q) || !aligned16(a8)) return BX_EARG;
   if (M == 0) return BX_OK;
   const int64_t total = (int64_t)M * (K / 16);
@@ -283,6 +334,7 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
 int bx_exact_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gm,
                   const int64_t* ge, int64_t* xo, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag, int M, int D,
                   int do_norm, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!xin || !flag || M < 0 || D < 32 || D > 4096 || (D & (D - 1))) return BX_EARG;
   if ((mode == 0 && !ids) || (mode == 1 && !yin) || mode < 0 || mode > 2) return BX_EARG;
   if (do_norm && (!gm || !ge || !q || !sh)) return BX_EARG;
@@ -306,6 +358,7 @@ int bx_exact_norm(int mode, const void* xin, const int64_t* yin, const int64_t* 
 int bx_exact_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos,
                  const int64_t* slot, int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, int32_t* q,
                  int64_t* sh, int32_t* flag, int N, int H, int HKV, int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!y || !cos || !sin || !pos || !q || !sh || !flag || N < 0) return BX_EARG;
   if ((HD != 64 && HD != 128) || HKV <= 0 || H % HKV || (cache && (!slot || bs <= 0))) return BX_EARG;
   if (N == 0) return BX_OK;
@@ -318,6 +371,7 @@ int bx_exact_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const
 int bx_kv_store(int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const int64_t* slot,
                 const int64_t* k, int64_t skz, int64_t skh, const int64_t* v, int64_t svz, int64_t svh, int N,
                 int HKV, int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!cache || !slot || !k || !v || bs <= 0 || N < 0 || HKV <= 0 || HD <= 0) return BX_EARG;
   if (N == 0) return BX_OK;
   kv_store_kernel<<<dim3(N, HKV), 64, 0, (cudaStream_t)stream>>>(cache, (const i64*)slot, (const i64*)k, (const i64*)v,
@@ -327,6 +381,7 @@ int bx_kv_store(int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int b
 
 int bx_exact_attn_out(const int64_t* num, const int64_t* den, int32_t* q, int64_t* sh, int8_t* a8, int N, int K2,
                       int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!num || !den || !q || !sh || N < 0 || K2 <= 0 || K2 > AO_THREADS * AO_EPT || HD <= 0 || K2 % HD ||
       K2 / HD > AO_MAXH)
     return BX_EARG;
@@ -337,22 +392,19 @@ int bx_exact_attn_out(const int64_t* num, const int64_t* den, int32_t* q, int64_
 
 int bx_exact_silu_quant(const int64_t* y, const int64_t* lut, int32_t* q, int64_t* sh, int8_t* a8, int32_t* flag,
                         int N, int FF, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!y || !lut || !q || !sh || !flag || N < 0 || FF <= 0 || FF > SILU_THREADS * 28) return BX_EARG;
   if (N == 0) return BX_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (FF <= 8 * SILU_P_THREADS && N >= 64) {        // one persistent CTA per SM, 2^-f table in shared memory
-    static bool configured = false;
-    static int sms = 0;
+    static PerDevice configured;
     const int smem = SILU_TABLE * 8;
-    if (!configured) {
-      int dev = 0;
-      if (cudaFuncSetAttribute(silu_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-              cudaSuccess ||
-          cudaGetDevice(&dev) != cudaSuccess ||
-          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-        return BX_ELAUNCH;
-      configured = true;
-    }
+    if (once_per_device(configured, [smem] {
+          return cudaFuncSetAttribute(silu_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        }) != BX_OK)
+      return BX_ELAUNCH;
+    const int sms = device_sms();
+    if (sms <= 0) return BX_ELAUNCH;
     // equal rounds: with 256 rows, 128 CTAs of two rows each rather than 148 CTAs of one or two
     const int rounds = (N + sms - 1) / sms;
     const int grid = (N + rounds - 1) / rounds;
@@ -422,15 +474,15 @@ static int run_attention_stream(int NW, const int32_t* q, const int64_t* sh, con
   const size_t smem = (size_t)fixed + (size_t)ns * STAGE;
   AttnParams p{q, (const i64*)sh, (const i64*)qpos, cache, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk,
                (const i64*)rmap, (const i64*)lut, (i64)l2e, (i64*)num, (i64*)den, M, HKV, (int)cap, ptab};
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(exact_attention_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             227 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(exact_attention_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             227 * 1024) != cudaSuccess)
-      return BX_ELAUNCH;
-    configured = true;
-  }
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        cudaError_t e = cudaFuncSetAttribute(exact_attention_stream_kernel<8>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        return e != cudaSuccess ? e
+                                : cudaFuncSetAttribute(exact_attention_stream_kernel<4>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      }) != BX_OK)
+    return BX_ELAUNCH;
   EncodeTiledFn fn = encode_fn();
   if (!fn) return BX_ELAUNCH;
   CUtensorMap tk, tv;
@@ -533,19 +585,18 @@ static int run_attention(const int32_t* q, const int64_t* sh, const int64_t* qpo
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  static bool configured[5] = {false, false, false, false, false};
-  if (!configured[kind]) {
-    cudaError_t e = kind == 4 ? cudaFuncSetAttribute(exact_attention_tc_kernel<4>,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
-                    : kind == 3 ? cudaFuncSetAttribute(exact_attention_tc_kernel<8>,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
-                    : kind == 2 ? cudaFuncSetAttribute(exact_attention_tma_kernel,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
-                                : cudaFuncSetAttribute(exact_attention_kernel,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
-    if (e != cudaSuccess) return BX_ELAUNCH;
-    configured[kind] = true;
-  }
+  static PerDevice configured[5];
+  if (once_per_device(configured[kind], [kind, smem_limit] {
+        return kind == 4 ? cudaFuncSetAttribute(exact_attention_tc_kernel<4>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
+               : kind == 3 ? cudaFuncSetAttribute(exact_attention_tc_kernel<8>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
+               : kind == 2 ? cudaFuncSetAttribute(exact_attention_tma_kernel,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit)
+                           : cudaFuncSetAttribute(exact_attention_kernel,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
+      }) != BX_OK)
+    return BX_ELAUNCH;
   if (kind >= 3) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return BX_ELAUNCH;
@@ -588,6 +639,7 @@ int bx_exact_attention(const int32_t* q, const int64_t* sh, const int64_t* qpos,
                        int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64,
                        int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
                        int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!sh || !lut) return BX_EARG;
   return run_attention(q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, lut, l2e,
                        nullptr, num, den, R, HKV, M, HD, cluster_size, variant, nullptr, 0, stream);
@@ -604,6 +656,7 @@ int bx_exact_attention_ws(const int32_t* q, const int64_t* sh, const int64_t* qp
                           int64_t sbt, int nblk, const int64_t* rmap, const int64_t* lut, int64_t l2e, int64_t* num,
                           int64_t* den, int R, int HKV, int M, int HD, int cluster_size, int variant, void* scratch,
                           size_t scratch_bytes, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!sh || !lut) return BX_EARG;
   return run_attention(q, sh, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, lut, l2e,
                        nullptr, num, den, R, HKV, M, HD, cluster_size, variant, scratch, scratch_bytes, stream);
@@ -613,6 +666,7 @@ int bx_int8_attention_ws(const int32_t* q, const int64_t* qpos, const int8_t* ca
                          int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
                          const int64_t* rmap, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
                          int HD, int cluster_size, int variant, void* scratch, size_t scratch_bytes, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!ptab) return BX_EARG;
   return run_attention(q, nullptr, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, nullptr,
                        0, ptab, num, den, R, HKV, M, HD, cluster_size, variant, scratch, scratch_bytes, stream);
@@ -622,6 +676,7 @@ int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache
                       int64_t sc_h, int64_t sc_bs, int bs, const void* bt, int bt_is_int64, int64_t sbt, int nblk,
                       const int64_t* rmap, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
                       int HD, int cluster_size, int variant, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!ptab) return BX_EARG;
   return run_attention(q, nullptr, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, nullptr,
                        0, ptab, num, den, R, HKV, M, HD, cluster_size, variant, nullptr, 0, stream);
@@ -630,6 +685,7 @@ int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache
 int bx_int8_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gamma,
                  int64_t* xo, int8_t* a8, int64_t* mant, int64_t* e, int32_t* flag, int M, int D, int do_norm,
                  void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!xin || !flag || M < 0 || D < 1 || D > NORM_THREADS * NORM_EPT || mode < 0 || mode > 2) return BX_EARG;
   if ((mode == 0 && !ids) || (mode == 1 && !yin) || (do_norm && (!gamma || !a8 || !mant || !e))) return BX_EARG;
   if (M == 0) return BX_OK;
@@ -643,6 +699,7 @@ int bx_int8_norm(int mode, const void* xin, const int64_t* yin, const int64_t* i
 int bx_int8_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos, const int64_t* slot,
                 int8_t* cache, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs, int64_t* q64, int32_t* q32,
                 int32_t* flag, int N, int H, int HKV, int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!y || !cos || !sin || !pos || !flag || (!q64 && !q32) || N < 0) return BX_EARG;
   if ((HD != 64 && HD != 128) || HKV <= 0 || H % HKV || (cache && (!slot || bs <= 0))) return BX_EARG;
   if (N == 0) return BX_OK;
@@ -654,6 +711,7 @@ int bx_int8_qkv(const int64_t* y, const int64_t* cos, const int64_t* sin, const 
 
 int bx_int8_attn_out(const int64_t* num, const int64_t* den, int8_t* a8, int64_t* mant, int64_t* e, int N, int K2,
                      int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!num || !den || !a8 || !mant || !e || N < 0 || K2 <= 0 || K2 > AO_THREADS * AO_EPT || HD <= 0 || K2 % HD ||
       K2 / HD > AO_MAXH)
     return BX_EARG;
@@ -664,6 +722,7 @@ int bx_int8_attn_out(const int64_t* num, const int64_t* den, int8_t* a8, int64_t
 
 int bx_int8_silu_quant(const int64_t* y, const int64_t* lut, int8_t* a8, int64_t* mant, int64_t* e, int64_t* scr,
                        int N, int FF, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!y || !lut || !a8 || !mant || !e || N < 0 || FF <= 0 || FF > SILU_THREADS * 28) return BX_EARG;
   if (N == 0) return BX_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -676,6 +735,7 @@ int bx_int8_silu_quant(const int64_t* y, const int64_t* lut, int8_t* a8, int64_t
 
 int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e, int64_t* y,
                  int32_t* flag, int M, int N, int checked, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!c || !mul || !mant || !e || !y || !flag || M < 0 || N <= 0) return BX_EARG;
   if (M == 0) return BX_OK;
   const int64_t total = (int64_t)M * N;
@@ -686,12 +746,14 @@ int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64
 }
 
 int bx_int8_flag_end(int64_t* scr, int32_t* flag, int L, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!scr || !flag || L <= 0) return BX_EARG;
   i8::int8_flag_end_kernel<<<1, 64, 0, (cudaStream_t)stream>>>((i64*)scr, flag, L);
   return launched(1);
 }
 
 int bx_pcg_raw(const int64_t* keys, int64_t* out, int n, int V, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!keys || !out || n < 0 || V <= 0) return BX_EARG;
   if (n == 0) return BX_OK;
   const int run = 16;
@@ -727,11 +789,13 @@ static int run_sample(const int64_t* logits, int64_t ld, const int64_t* rows, co
 
 int bx_sample(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
               int64_t* tok, int M, int V, int bits, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   return run_sample(logits, ld, rows, lnt, scratch, tok, nullptr, M, V, 0, bits, stream);
 }
 
 int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, const int64_t* lnt, void* scratch,
                     int64_t* best, int64_t* idx, int M, int V_local, int64_t v_offset, int bits, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!best) return BX_EARG;
   return run_sample(logits, ld, rows, lnt, scratch, idx, best, M, V_local, v_offset, bits, stream);
 }
@@ -739,6 +803,7 @@ int bx_sample_shard(const int64_t* logits, int64_t ld, const int64_t* rows, cons
 // ---- weight preparation (load time) ----
 int bx_decompose_rows(const uint16_t* w, int64_t ldw, int8_t* limbs, int64_t* g, int64_t* d, int32_t* cnt, int32_t* flag,
                       int N, int K, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!w || !limbs || !g || !d || !cnt || !flag || N < 0 || K <= 0 || ldw < K) return BX_EARG;
   if (N == 0) return BX_OK;
   decompose_rows_kernel<<<N, DEC_THREADS, 0, (cudaStream_t)stream>>>(w, ldw, limbs, (i64*)g, (i64*)d, cnt, flag, N, K);
@@ -747,6 +812,7 @@ int bx_decompose_rows(const uint16_t* w, int64_t ldw, int8_t* limbs, int64_t* g,
 
 int bx_decompose_residual(const uint16_t* w, int64_t ldw, const int64_t* g, const int64_t* d, const int64_t* start,
                           int64_t* rr, int64_t* rc, int64_t* rv, int N, int K, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!w || !g || !d || !start || !rr || !rc || !rv || N < 0 || K <= 0 || ldw < K) return BX_EARG;
   if (N == 0) return BX_OK;
   decompose_residual_kernel<<<N, DEC_THREADS, 0, (cudaStream_t)stream>>>(w, ldw, (const i64*)g, (const i64*)d,
@@ -770,12 +836,14 @@ static bool logp_args_ok(const void* lg, int64_t ld, const void* scratch, int M,
 }
 
 int bx_logp_pair_table(const int64_t* tab, int tab_len, int64_t* tab2, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!tab || !tab2 || tab_len != LSE_LAST + 1 || ((uintptr_t)tab2 & 15)) return BX_EARG;
   logp_pair_table_kernel<<<(tab_len + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const i64*)tab, (longlong2*)tab2, tab_len);
   return launched(1);
 }
 
 int bx_logp_rowmax(const int64_t* logits, int64_t ld, void* scratch, int64_t* rowmax, int M, int V, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!logp_args_ok(logits, ld, scratch, M, V) || !rowmax) return BX_EARG;
   if (M == 0) return BX_OK;
   int ch, nch;
@@ -789,6 +857,7 @@ int bx_logp_rowmax(const int64_t* logits, int64_t ld, void* scratch, int64_t* ro
 
 int bx_logp_rowsum(const int64_t* logits, int64_t ld, const int64_t* rowmax, const int64_t* tab2, int tab_len,
                    void* scratch, int64_t* S, int M, int V, int fr, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!logp_args_ok(logits, ld, scratch, M, V) || !rowmax || !tab2 || ((uintptr_t)tab2 & 15) || !S || tab_len != LSE_LAST + 1 || fr <= LSE_STEP ||
       fr > 24)
     return BX_EARG;
@@ -804,6 +873,7 @@ int bx_logp_rowsum(const int64_t* logits, int64_t ld, const int64_t* rowmax, con
 }
 
 int bx_logp_finish(const int64_t* S, const int64_t* zt, const int64_t* lnt, int64_t* out, int M, int fr, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!S || !zt || !lnt || !out || M < 0 || fr <= LSE_STEP || fr > 24) return BX_EARG;
   if (M == 0) return BX_OK;
   logp_finish_kernel<<<(M + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const i64*)S, 1, (const i64*)zt, nullptr, 0, nullptr,
@@ -813,6 +883,7 @@ int bx_logp_finish(const int64_t* S, const int64_t* zt, const int64_t* lnt, int6
 
 int bx_int_logp(const int64_t* logits, int64_t ld, const int64_t* tok, const int64_t* lnt, const int64_t* tab2,
                 int tab_len, void* scratch, int64_t* out, int M, int V, int fr, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!logp_args_ok(logits, ld, scratch, M, V) || !tok || !lnt || !tab2 || ((uintptr_t)tab2 & 15) || !out || tab_len != LSE_LAST + 1 ||
       fr <= LSE_STEP || fr > 24)
     return BX_EARG;
@@ -834,6 +905,7 @@ int bx_int_logp(const int64_t* logits, int64_t ld, const int64_t* tok, const int
 
 int bx_exact_silu_prod(const int64_t* y, const int64_t* lut, int64_t* P, int64_t* rowmax, int32_t* flag, int N, int FFl,
                        void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!y || !lut || !P || !rowmax || !flag || N < 0 || FFl <= 0) return BX_EARG;
   if (N == 0) return BX_OK;
   silu_prod_kernel<512><<<N, 512, 0, (cudaStream_t)stream>>>((const i64*)y, (const i64*)lut, (i64*)P, (i64*)rowmax, flag,
@@ -843,6 +915,7 @@ int bx_exact_silu_prod(const int64_t* y, const int64_t* lut, int64_t* P, int64_t
 
 int bx_exact_quant_rows(const int64_t* P, const int64_t* rowmax, int fbits, int32_t* q, int64_t ldq, int64_t* sh,
                         int8_t* a8, int64_t plane, int N, int K, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!P || !rowmax || !q || N < 0 || K <= 0 || ldq < K || fbits < 0 || fbits > 62 || (a8 && plane < (int64_t)N * ldq))
     return BX_EARG;
   if (N == 0) return BX_OK;
@@ -853,6 +926,7 @@ int bx_exact_quant_rows(const int64_t* P, const int64_t* rowmax, int fbits, int3
 
 int bx_bmm(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t* c, int Z, int M, int N, int K,
            int64_t saz, int64_t sam, int64_t sak, int64_t sbz, int64_t sbk, int64_t sbn, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!a || !b || !c || Z < 0 || M < 0 || N < 0 || K < 0 || K >= 43690 || Z > 65535) return BX_EARG;
   if (Z == 0 || M == 0 || N == 0) return BX_OK;
   const dim3 grid((N + BMM_T - 1) / BMM_T, (M + BMM_T - 1) / BMM_T, Z);
@@ -872,6 +946,7 @@ int bx_bmm(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t
 int bx_exact_epilogue(const int64_t* T, const int64_t* B, const int32_t* q, int64_t ldq, const int32_t* cnt,
                       const int32_t* ec, const int64_t* ev, int R, const int64_t* d, const int64_t* g,
                       const int64_t* sh, int64_t* y, int32_t* flag, int M, int N, int checked, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!T || !d || !g || !sh || !y || !flag || M < 0 || N <= 0) return BX_EARG;
   if (cnt && (!q || !ec || !ev || R <= 0)) return BX_EARG;
   if (M == 0) return BX_OK;
@@ -885,6 +960,7 @@ int bx_exact_epilogue(const int64_t* T, const int64_t* B, const int32_t* q, int6
 }
 
 int bx_int8_mm(const int8_t* a, const int8_t* w, int32_t* c, int M, int N, int K, int tile_rows, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!c) return BX_EARG;
   Int8EpiParams ep{c, nullptr, 0, nullptr, nullptr, nullptr, nullptr, M, N, 0};
   return run_int8<false>(a, w, ep, K, tile_rows, (cudaStream_t)stream);
@@ -893,6 +969,7 @@ int bx_int8_mm(const int8_t* a, const int8_t* w, int32_t* c, int M, int N, int K
 int bx_int8_linear_post(const int8_t* a, const int8_t* w, const int64_t* mul, int64_t fmsh, const int64_t* mant,
                         const int64_t* e, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
                         void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!mul || !mant || !e || !y || !flag) return BX_EARG;
   Int8EpiParams ep{nullptr, mul, fmsh, mant, e, y, flag, M, N, checked};
   return run_int8<true>(a, w, ep, K, tile_rows, (cudaStream_t)stream);
@@ -902,6 +979,7 @@ int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8
                     const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
                     int8_t* scratch, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
                     void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!q || !sh || !limbs || !d || !g || !scratch || !y || !flag) return BX_EARG;
   if (M < 0 || N <= 0 || K <= 0 || K % 16 || K >= 43690 || !aligned16(limbs) || !aligned16(scratch)) return BX_EARG;
   if (cnt && (!ec || !ev || R <= 0)) return BX_EARG;
@@ -915,6 +993,7 @@ int bx_exact_linear_planes(const int8_t* planes, const int32_t* q, int64_t ldq, 
                            const int64_t* d, const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev,
                            int R, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,
                            void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!planes || !sh || !limbs || !d || !g || !y || !flag) return BX_EARG;
   if (M < 0 || N <= 0 || K <= 0 || K % 16 || K >= 43690 || !aligned16(limbs) || !aligned16(planes)) return BX_EARG;
   if (cnt && (!ec || !ev || R <= 0 || !q)) return BX_EARG;
@@ -932,19 +1011,23 @@ size_t bx_exact_linear_static_max_bytes(void) { return (size_t)BX_STATIC_SCRATCH
 int bx_exact_linear_static(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,
                            const int64_t* g, const int32_t* cnt, const int32_t* ec, const int64_t* ev, int R,
                            int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (M < 0 || K <= 0) return BX_EARG;
   if ((size_t)3 * (size_t)M * (size_t)K > (size_t)BX_STATIC_SCRATCH_BYTES) return BX_ELIMIT;
   // The host-side name of a __device__ array is not a device address; resolve it once per device, with that
   // device current, and hand the real address to the kernels.
-  static int8_t* dev_ptr[64] = {nullptr};
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BX_ELAUNCH;
-  if (!dev_ptr[dev]) {
+  // The table is atomic: first calls that race on one device from several host threads store the same address.
+  static std::atomic<int8_t*> dev_ptr[BX_MAX_DEVICES];
+  const int dev = current_device();
+  if (dev < 0) return BX_ELAUNCH;
+  int8_t* planes = dev_ptr[dev].load(std::memory_order_acquire);
+  if (!planes) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_static_planes) != cudaSuccess || !p) return BX_ELAUNCH;
-    dev_ptr[dev] = static_cast<int8_t*>(p);
+    planes = static_cast<int8_t*>(p);
+    dev_ptr[dev].store(planes, std::memory_order_release);
   }
-  return bx_exact_linear(q, ldq, sh, limbs, d, g, cnt, ec, ev, R, dev_ptr[dev], y, flag, M, N, K, checked, tile_rows,
+  return bx_exact_linear(q, ldq, sh, limbs, d, g, cnt, ec, ev, R, planes, y, flag, M, N, K, checked, tile_rows,
                          stream);
 }
 

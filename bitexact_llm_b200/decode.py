@@ -35,6 +35,21 @@ class Session:
         return self.bt[seq, pos // self.bs].long() * self.bs + pos % self.bs
 
     @torch.no_grad()
+    def import_kv(self, seq, k, v, layers=None):
+        """Loads keys / values of positions 0 .. n - 1 of sequence `seq` (int64 [n, HKV, HD] at 17 / 19 fractional
+        bits, within three limbs) into the paged cache of the given layers (default: all) and sets the sequence's
+        length to n: a prefix computed elsewhere, e.g. by another engine or an earlier session."""
+        from .vllm_plugin import tri_paged
+        dev = self.eng.dev
+        k, v = k.to(dev).long().contiguous(), v.to(dev).long().contiguous()
+        n = k.shape[0]
+        pos = torch.arange(n, device=dev)
+        slot = self._slots(torch.full_like(pos, int(seq)), pos)
+        for i in (range(self.eng.L) if layers is None else layers):
+            tri_paged.store(self.kvs[i], slot, k, v)
+        self.lens[seq] = n
+
+    @torch.no_grad()
     def prefill(self, prompts, lens=None, chunk_rows=4096):
         """prompts: int64 [B, P] right-padded, lens [B] the true lengths (default: all P). Token rows are processed
         in position chunks so that every row's keys are in the cache before it attends. Returns the final residual

@@ -5,6 +5,7 @@ qkv, attention, attn_out, linear, add_norm, linear, silu_quant, linear, add_norm
 
 import torch
 
+from .. import _native as nv
 from ..vllm_plugin import tri_fuse, tri_paged
 from .gemm_skinny import linear_post
 
@@ -34,6 +35,8 @@ class IntEngine:
         self.scr = torch.zeros(self.L, 2, dtype=torch.long, device=self.dev)
 
     def check(self):
+        """OverflowError on a flagged integer bound; `_native.DeviceWaitError` when a device-side wait gave up."""
+        nv.check_device_status()
         if bool(self.fl.item()):
             raise OverflowError("integer bound violated (int8 mode)")
 

@@ -9,6 +9,23 @@ import torch
 from .. import _native as nv
 
 
+def attach_planes(q, planes):
+    """Remembers the limb planes a stage kernel wrote next to q, together with q's version counter and address:
+    `FusedLin` uses them only while q has not been written since (an in-place edit of q bumps the counter)."""
+    q._bx_planes = (planes, q._version, q.data_ptr())
+
+
+def planes_of(q, M, K):
+    """The limb planes attached to q if they still describe it, else None."""
+    rec = getattr(q, "_bx_planes", None)
+    if rec is None:
+        return None
+    planes, version, addr = rec
+    if version != q._version or addr != q.data_ptr() or planes.shape != (3, M, K) or not q.is_contiguous():
+        return None
+    return planes
+
+
 def _norm(m, x, y, ids, gamma, fl, mode, norm, store):
     M, D = (ids.shape[0], m.D) if mode == 0 else x.shape
     assert D & (D - 1) == 0 and 32 <= D <= 4096
@@ -25,7 +42,7 @@ def _norm(m, x, y, ids, gamma, fl, mode, norm, store):
                                 nv.stream())
     nv.check(rc, "bx_exact_norm")
     if norm:
-        q._bx_planes = planes                            # the next fused linear skips its limb-splitting pass
+        attach_planes(q, planes)                         # the next fused linear skips its limb-splitting pass
     return (xo if store else x), q, sh
 
 
@@ -75,7 +92,7 @@ def attn_out(m, num, den):
     rc = nv.lib().bx_exact_attn_out(num.contiguous().data_ptr(), den.contiguous().data_ptr(), q.data_ptr(),
                                     sh.data_ptr(), planes.data_ptr(), N, K2, m.HD, nv.stream())
     nv.check(rc, "bx_exact_attn_out")
-    q._bx_planes = planes
+    attach_planes(q, planes)
     return q, sh
 
 
@@ -88,5 +105,5 @@ def silu_quant(m, y, lut, fl):
     rc = nv.lib().bx_exact_silu_quant(y.contiguous().data_ptr(), lut.data_ptr(), q.data_ptr(), sh.data_ptr(),
                                       planes.data_ptr(), fl.data_ptr(), N, FF, nv.stream())
     nv.check(rc, "bx_exact_silu_quant")
-    q._bx_planes = planes
+    attach_planes(q, planes)
     return q, sh

@@ -45,8 +45,9 @@ class FusedLin:
         return self._run(q, sh, flag, checked, y, M, K)
 
     def _run(self, q, sh, flag, checked, y, M, K):
-        planes = getattr(q, "_bx_planes", None)          # limb planes written by the stage kernel that produced q
-        if planes is not None and planes.shape == (3, M, K) and q.is_contiguous():
+        from .exact_fuse import planes_of
+        planes = planes_of(q, M, K)                      # limb planes written by the stage kernel that produced q
+        if planes is not None:
             rc = nv.lib().bx_exact_linear_planes(planes.data_ptr(), q.data_ptr(), q.stride(0), sh.data_ptr(),
                                                  self.limbs.data_ptr(), self.d.data_ptr(), self.g.data_ptr(),
                                                  nv.ptr(self.cnt), nv.ptr(self.ec), nv.ptr(self.ev), self.R,

@@ -7,6 +7,7 @@ silu_quant, linear, add_norm), device tensors only, no host synchronisation insi
 
 import torch
 
+from .. import _native as nv
 from ..exact.model import Lin
 from . import exact_fuse, tri_exact_attn
 from .exact_gemm import FusedLin
@@ -48,7 +49,9 @@ class ExactEngine:
 
     def check(self):
         """Raises OverflowError when any kernel flagged an integer bound (src/bitexact/exact/model.py:155-157).
-        Synchronises with the device."""
+        Also raises `_native.DeviceWaitError` when a bounded device-side wait gave up since the last clear: the
+        kernels launched after that left their outputs unwritten. Synchronises with the device."""
+        nv.check_device_status()
         if bool(self.fl.item()):
             raise OverflowError("integer bound violated (exact mode)")
 

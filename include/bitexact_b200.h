@@ -22,12 +22,22 @@ extern "C" {
 #define BX_EDEVICE (-3)  /* a bounded device-side wait gave up (see bx_device_status) */
 #define BX_ELIMIT (-4)   /* the request exceeds a fixed capacity of the entry point (see its comment) */
 
-/* Library / device state. bx_device_status: number of device-side waits that timed out since the last clear
- * (0 in a healthy run; synchronises the device). */
+/* Library / device state. Every device-side wait of the kernels is bounded; one that gives up adds 1 to a status
+ * word on the device, and from then on every CTA of the pipelined kernels returns at once WITHOUT writing its
+ * outputs (the word is sticky). The reference has no counterpart: its Triton kernels have no waits of their own.
+ *   bx_device_status        the word (0 in a healthy run); copies it from the device, which synchronises.
+ *   bx_clear_device_status  back to 0.
+ *   bx_set_device_status    writes the word from the host (value >= 0): lets a host application or a test put the
+ *                           library into the failed state without making any wait run out on the device.
+ * Launching entry points do not read the word themselves (that would synchronise every launch). Once the host has
+ * SEEN a non-zero word (bx_device_status returned it, or bx_set_device_status set it) every launching entry
+ * point returns BX_EDEVICE and launches nothing, until bx_clear_device_status. The engines' check() reads the
+ * word. Kernel attributes and device properties are cached per device ordinal (up to 64 devices per process). */
 int bx_version(void);
 long long bx_launch_count(void);   /* kernels launched through this library so far (host-side count) */
 int bx_device_status(void);
 int bx_clear_device_status(void);
+int bx_set_device_status(int value);
 
 /* ---- exact-mode linear -------------------------------------------------------------------------------
  * y[m, n] = round((sum_k q[m, k] W[n, k] * 2^d[n] + B[m, n]) * 2^(sh[m] + g[n] - d[n] + 24)), one rounding,
@@ -73,7 +83,8 @@ int bx_exact_linear_planes(const int8_t* planes, const int32_t* q, int64_t ldq, 
  * until the process exits). Same arguments as bx_exact_linear without `scratch`; same results bit for bit.
  *   - 3 * M * K must not exceed the buffer: larger requests return BX_ELIMIT and launch nothing.
  *   - The first call on each device looks up the buffer's device address (one driver query, no allocation);
- *     make that first call during start-up, before any stream capture begins.
+ *     make that first call during start-up, before any stream capture begins. First calls may come from
+ *     several host threads at once: the address table is atomic and they all store the same value.
  *   - The entry point calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - All calls on a device share the one buffer and it keeps the previous call's contents. Nothing in it has to
  *     start at zero (each call overwrites every byte it later reads), but two calls that run on the GPU at the

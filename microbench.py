@@ -1,9 +1,9 @@
 """Kernel micro-benchmarks through the C ABI (CUDA-event timing, inputs larger than L2 or L2 flushed).
 
-    python -m bitexact_llm_b200.microbench gemm [--m 1,16,256,4096] [--tile 0] [--iters 20] [--shapes decode|all]
-    python -m bitexact_llm_b200.microbench gemmr [--m 256] [--iters 10]
-    python -m bitexact_llm_b200.microbench attn [--batch 256] [--ctx 4128] [--iters 10]
-    python -m bitexact_llm_b200.microbench stages [--batch 256] [--iters 10]
+    python microbench.py gemm [--m 1,16,256,4096] [--tile 0] [--iters 20] [--shapes decode|all]
+    python microbench.py gemmr [--m 256] [--iters 10]
+    python microbench.py attn [--batch 256] [--ctx 4128] [--iters 10]
+    python microbench.py stages [--batch 256] [--iters 10]
 
 gemm: the exact-mode fused linear on the projection shapes of one Llama-3.2-1B layer and the LM head
       (int8-equivalent ops = 2 * 9 * M * N * K; algorithmic bytes = 3 N K + 4 M K + 8 M N).
@@ -20,9 +20,13 @@ stages (the last line: integer log p, two passes of 8 V bytes per row): add + RM
 import argparse
 import json
 
+import os
+import sys
+
 import torch
 
-from . import _native as nv
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from bitexact_llm_b200 import _native as nv  # noqa: E402
 
 SHAPES = {"q": (2048, 2048), "k": (512, 2048), "v": (512, 2048), "o": (2048, 2048), "gate": (8192, 2048),
           "up": (8192, 2048), "down": (2048, 8192)}
@@ -77,9 +81,10 @@ def gemm(args):
 
 
 def gemmr(args):
-    from .exact.consts import decompose
-    from .exact.model import Lin
-    from .vllm_plugin.exact_gemm import FusedLin
+    from bitexact_llm_b200.exact.consts import decompose
+    from bitexact_llm_b200.exact.model import Lin
+    from bitexact_llm_b200.vllm_plugin import exact_fuse
+    from bitexact_llm_b200.vllm_plugin.exact_gemm import FusedLin
     lib, dev = nv.lib(), "cuda"
     g = torch.Generator().manual_seed(0)
     out = []
@@ -97,7 +102,7 @@ def gemmr(args):
             q = torch.randint(-(1 << 22), (1 << 22) + 1, (M, K), dtype=torch.int32, device=dev)
             planes = torch.empty(3, M, K, dtype=torch.int8, device=dev)
             nv.check(lib.bx_split_limbs(q.data_ptr(), K, planes.data_ptr(), M, K, nv.stream()), "bx_split_limbs")
-            q._bx_planes = planes
+            exact_fuse.attach_planes(q, planes)
             sh = torch.full((M,), -14, dtype=torch.long, device=dev)
             fl = torch.zeros(1, dtype=torch.int32, device=dev)
             for tag in ("residual", "none"):
@@ -117,7 +122,7 @@ def gemmr(args):
 
 
 def attn(args):
-    from .exact.consts import exp2_table
+    from bitexact_llm_b200.exact.consts import exp2_table
     lib, dev = nv.lib(), "cuda"
     B, HKV, G, HD, bs = args.batch, 8, 4, 64, 16
     gen = torch.Generator(device=dev).manual_seed(0)
@@ -199,9 +204,9 @@ def _graph_time(run, nsets, iters, reps=4):
 
 def stages(args):
     from types import SimpleNamespace
-    from .exact.consts import exp2_table, ln_table
-    from .vllm_plugin import exact_fuse
-    from .vllm_plugin.sampler import sample_rows
+    from bitexact_llm_b200.exact.consts import exp2_table, ln_table
+    from bitexact_llm_b200.vllm_plugin import exact_fuse
+    from bitexact_llm_b200.vllm_plugin.sampler import sample_rows
     dev, M, D, FF, V = "cuda", args.batch, 2048, 8192, 128256
     gen = torch.Generator(device=dev).manual_seed(0)
     fl = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -238,7 +243,7 @@ def stages(args):
     ls = sets(n, lambda: R(-(1 << 28), 1 << 28, M, V))
     rows = torch.stack([R(0, 1 << 40, M), R(0, 1000, M), R(1, 9, M), R(1, 9, M)], 1)
     report("sample", _graph_time(lambda i: sample_rows(ls[i], rows, lnt, 24), n, args.iters), 8.0 * M * V)
-    from .vllm_plugin.rl import int_logp_q
+    from bitexact_llm_b200.vllm_plugin.rl import int_logp_q
     toks = R(0, V, M)
     l16 = [x >> 8 for x in ls]                                                     # logits at 16 bits in (-16, 16)
     del ls
