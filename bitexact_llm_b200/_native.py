@@ -25,6 +25,7 @@ _SIGNATURES = {
     "bx_device_status": (I, []),
     "bx_clear_device_status": (I, []),
     "bx_set_device_status": (I, [I]),
+    "bx_i8_tensor_peak": (I, [I, I, P, P]),
     "bx_exact_linear_scratch_bytes": (Z, [I, I]),
     "bx_exact_linear": (I, [P, L, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, P]),
     "bx_exact_linear_planes": (I, [P, P, L, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, P]),
@@ -108,6 +109,15 @@ def device_status():
 
 def clear_device_status():
     check(lib().bx_clear_device_status(), "bx_clear_device_status")
+
+
+def i8_tensor_peak(iters=1 << 17, repeats=5):
+    """(best, mean) int8 TOPS of a shared-memory-resident tcgen05 kind::i8 loop on the current device."""
+    import torch
+    out = (ctypes.c_double * 2)()
+    check(lib().bx_i8_tensor_peak(iters, repeats, ctypes.cast(out, ctypes.c_void_p), stream()), "bx_i8_tensor_peak")
+    torch.cuda.synchronize()
+    return out[0], out[1]
 
 
 class DeviceWaitError(RuntimeError):

@@ -19,6 +19,7 @@
 #include "logp.cuh"
 #include "decompose.cuh"
 #include "unfused.cuh"
+#include "peak_probe.cuh"
 
 namespace {
 
@@ -27,7 +28,7 @@ using namespace bx;
 long long g_launches = 0;   // kernels launched through this library (host-side count)
 
 // Host-side shadow of the device status word: non-zero once the host has SEEN a timed-out device-side wait
-// (bx_device_status) or set one (bx_set_device_status). Launching entry points then return BX_EDEVICE without
+// (bx_device_status returned non-zero). Launching entry points then return BX_EDEVICE without
 // launching, until bx_clear_device_status. Reading the device word itself needs a synchronising copy, which a
 // launch path cannot afford; the engines' check() does that read.
 std::atomic<int> g_status_seen{0};
@@ -234,8 +235,49 @@ int bx_clear_device_status(void) {
 
 int bx_set_device_status(int value) {
   if (value < 0) return BX_EARG;
+  // Only the device word: the host-side shadow follows when the host next reads the word, exactly as after a
+  // wait that really ran out on the device.
   if (cudaMemcpyToSymbol(bx::g_wait_timeouts, &value, sizeof(int)) != cudaSuccess) return BX_ELAUNCH;
-  g_status_seen.store(value != 0);
+  return BX_OK;
+}
+
+int bx_i8_tensor_peak(int iters, int repeats, double* tops, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (iters < 4 || iters > (1 << 22) || repeats < 1 || repeats > 64 || !tops) return BX_EARG;
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(i8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PEAK_SMEM);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int sms = device_sms();
+  if (sms <= 0) return BX_ELAUNCH;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaEvent_t e0, e1;
+  if (cudaEventCreate(&e0) != cudaSuccess) return BX_ELAUNCH;
+  if (cudaEventCreate(&e1) != cudaSuccess) { cudaEventDestroy(e0); return BX_ELAUNCH; }
+  const double ops = (double)sms * iters * 4.0 * 2.0 * 128.0 * PEAK_N * 32.0;
+  double best = 0.0, sum = 0.0;
+  int rc = BX_OK;
+  i8_peak_kernel<<<sms, 128, PEAK_SMEM, st>>>(iters / 4);          // warm-up
+  for (int r = 0; r < repeats && rc == BX_OK; ++r) {
+    cudaEventRecord(e0, st);
+    i8_peak_kernel<<<sms, 128, PEAK_SMEM, st>>>(iters);
+    cudaEventRecord(e1, st);
+    float ms = 0.f;
+    if (cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess || ms <= 0.f) {
+      rc = BX_ELAUNCH;
+      break;
+    }
+    const double t = ops / (ms * 1e-3) / 1e12;
+    best = t > best ? t : best;
+    sum += t;
+    g_launches += 1;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (rc != BX_OK || cudaGetLastError() != cudaSuccess) return BX_ELAUNCH;
+  tops[0] = best;
+  tops[1] = sum / repeats;
   return BX_OK;
 }
 

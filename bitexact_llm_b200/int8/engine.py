@@ -33,6 +33,7 @@ class IntEngine:
         self.ptab = tri_paged.weight_table(t("exp"))
         self.fl = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.scr = torch.zeros(self.L, 2, dtype=torch.long, device=self.dev)
+        self.timer = None                                    # optional callable(M, N, K) -> context manager
 
     def check(self):
         """OverflowError on a flagged integer bound; `_native.DeviceWaitError` when a device-side wait gave up."""
@@ -41,6 +42,9 @@ class IntEngine:
             raise OverflowError("integer bound violated (int8 mode)")
 
     def _lin(self, pre, lin):
+        if self.timer is not None:
+            with self.timer(pre[1].shape[0], lin[0].shape[0], lin[0].shape[1]):
+                return linear_post(pre[0], lin[0], lin[1], lin[2], pre[1], pre[2], self.fl, True)
         return linear_post(pre[0], lin[0], lin[1], lin[2], pre[1], pre[2], self.fl, True)
 
     def forward(self, kvs, ids, pos, slot, bt, rmap):

@@ -28,16 +28,23 @@ extern "C" {
  *   bx_device_status        the word (0 in a healthy run); copies it from the device, which synchronises.
  *   bx_clear_device_status  back to 0.
  *   bx_set_device_status    writes the word from the host (value >= 0): lets a host application or a test put the
- *                           library into the failed state without making any wait run out on the device.
+ *                           device into the failed state without making any wait run out on it.
  * Launching entry points do not read the word themselves (that would synchronise every launch). Once the host has
- * SEEN a non-zero word (bx_device_status returned it, or bx_set_device_status set it) every launching entry
- * point returns BX_EDEVICE and launches nothing, until bx_clear_device_status. The engines' check() reads the
+ * SEEN a non-zero word (bx_device_status returned it) every launching entry point returns BX_EDEVICE and
+ * launches nothing, until bx_clear_device_status. The engines' check() reads the
  * word. Kernel attributes and device properties are cached per device ordinal (up to 64 devices per process). */
 int bx_version(void);
 long long bx_launch_count(void);   /* kernels launched through this library so far (host-side count) */
 int bx_device_status(void);
 int bx_clear_device_status(void);
 int bx_set_device_status(int value);
+
+/* Measured int8 tensor-pipe peak of the current device (a measurement utility; no counterpart in the reference):
+ * one CTA per SM issues tcgen05.mma kind::i8 (M 128, N 256, K 32) `iters` x 4 times on operands resident in shared
+ * memory (no TMA, no global memory, no epilogue in the loop); `repeats` timed launches after a warm-up one.
+ * tops (HOST pointer, double [2]) receives the best and the mean rate in int8 TOPS (2 ops per multiply-add).
+ * Synchronises the stream. iters 4 .. 2^22 (2^17 runs about 5 ms on a B200), repeats 1 .. 64. */
+int bx_i8_tensor_peak(int iters, int repeats, double* tops, void* stream);
 
 /* ---- exact-mode linear -------------------------------------------------------------------------------
  * y[m, n] = round((sum_k q[m, k] W[n, k] * 2^d[n] + B[m, n]) * 2^(sh[m] + g[n] - d[n] + 24)), one rounding,

@@ -245,6 +245,49 @@ def test_attention_long_contexts_with_score_scratch():
     assert nv.device_status() == 0
 
 
+def test_attention_decode_batch_with_contexts_up_to_8192_keys():
+    """A decode batch of 48 requests x 8 KV heads (enough pairs for the persistent streaming kernel) whose contexts
+    run from 64 to 8192 keys, a few at 4096 .. 8192 among short ones, random pages, per-query positions that differ
+    inside a request: the automatic choice and both streaming variants, exact and int8 weight rule, full-range
+    values (|K|, |V| up to three limbs)."""
+    from bitexact_llm_b200.vllm_plugin import tri_exact_attn, tri_paged
+    rng = np.random.RandomState(8192)
+    nb, bs, HKV, HD = 640, 16, 8, 64
+    lim = 8355711
+    c32 = np.clip(np.rint(rng.standard_normal((nb, HKV, bs, 2 * HD)) * (1 << 19)), -lim, lim).astype(np.int64)
+    c32[5] = lim
+    c32[6] = -lim
+    planes = np.zeros((nb, HKV, bs, 8 * HD), dtype=np.int8)
+    for part, o in ((c32[..., :HD], 0), (c32[..., HD:], 3)):
+        for i, lo in enumerate(ox.split_limbs(part, 3)[0]):
+            planes[..., (o + i) * HD:(o + i + 1) * HD] = lo.astype(np.int8)
+    planes[..., 6 * HD:] = rng.randint(-128, 128, planes[..., 6 * HD:].shape)
+    lut_np = ox.exp2_table()
+    R, M = 48, 4
+    bt = rng.randint(1, nb, (R, 512)).astype(np.int32)                     # 8192 keys wide
+    ctx = rng.randint(64, 700, R)
+    ctx[[3, 11, 19, 30, 41]] = [8192, 4096, 4097, 6000, 7681]
+    qpos = np.repeat((ctx - 1)[:, None], M, 1).astype(np.int64)
+    qpos[3, 2], qpos[30, 0] = 100, 5999 - 513
+    q = rng.randint(-(1 << 22), (1 << 22) + 1, (R, HKV, M, HD)).astype(np.int64)
+    sh = rng.randint(-34, -16, (R, HKV, M)).astype(np.int64)
+    wnum, wden = ox.paged_attention(q, sh, qpos, planes, bt, np.arange(R), lut_np)
+    for variant in (0, 6, 5):
+        num, den = tri_exact_attn.attend(T(q, torch.int32), T(sh), T(qpos), T(planes), T(bt), None, T(lut_np), ox.L2E28,
+                                         variant=variant)
+        assert np.array_equal(N_(num), wnum) and np.array_equal(N_(den), wden), variant
+    from oracle import int8 as o8
+    expt = o8.exp_table()
+    q8 = q >> 8
+    w8n, w8d = o8.paged_attention(q8, qpos, planes, bt, np.arange(R), expt)
+    for variant in (0, 6, 5):
+        num, den = tri_paged.attend(T(q8), T(qpos), T(planes), T(bt), T(o8.weight_table(expt), torch.int32),
+                                    variant=variant)
+        assert np.array_equal(N_(num), w8n) and np.array_equal(N_(den), w8d), variant
+    from bitexact_llm_b200 import _native as nv
+    assert nv.device_status() == 0
+
+
 def test_attention_bound_stress_equal_scores_at_limb_extremes():
     """All K, V at +LIM3, all q at 2^22, 8192 equal-score keys (the p.V partial-sum bound case)."""
     from bitexact_llm_b200.vllm_plugin import tri_exact_attn
@@ -400,4 +443,28 @@ def test_two_step_silu_equals_the_fused_kernel_for_any_column_split():
             nv.check(lib.bx_exact_quant_rows(P.data_ptr(), rmax.data_ptr(), 48, q[:, a:].data_ptr(), FF, sh.data_ptr(),
                                              planes[:, :, a:].data_ptr(), N * FF, N, int(b - a), nv.stream()), "quant")
         assert np.array_equal(N_(q), wq) and np.array_equal(N_(sh), wsh) and int(fl2) == int(fl)
-        assert np.array_equal(N_(planes), N_(q_full._bx_planes))
+        assert np.array_equal(N_(planes), N_(fz.planes_of(q_full, N, FF)))
+
+
+def test_limb_planes_attached_to_q_are_dropped_when_q_is_edited_in_place():
+    """A stage kernel hands its limb planes to the next fused linear through q. A caller that edits q in place
+    afterwards (masking, padding rows) must get the product of the edited q, not of the stale planes."""
+    from bitexact_llm_b200.exact.consts import decompose
+    from bitexact_llm_b200.exact.model import Lin
+    from bitexact_llm_b200.vllm_plugin import exact_fuse
+    from bitexact_llm_b200.vllm_plugin.exact_gemm import FusedLin
+    g = torch.Generator().manual_seed(4)
+    dec = decompose((torch.randn(256, 128, generator=g) * 0.02).to(torch.bfloat16).cuda())
+    lin = FusedLin(Lin(dec, None, "cuda"))
+    m = model(D=128)
+    x = torch.randint(-(1 << 30), 1 << 30, (6, 128), generator=g).cuda()
+    gm, ge = torch.full((128,), 128, device="cuda"), torch.full((128,), -7, device="cuda")
+    q, sh = exact_fuse.pre_norm(m, x, (gm, ge), flag0())
+    assert exact_fuse.planes_of(q, 6, 128) is not None
+    y0 = lin(q, sh, flag0(), True)
+    q[2:4] = 0                                                     # in-place edit: the planes no longer describe q
+    assert exact_fuse.planes_of(q, 6, 128) is None
+    y1 = lin(q, sh, flag0(), True)
+    assert bool((y1[2:4] == 0).all()) and torch.equal(y1[:2], y0[:2]) and torch.equal(y1[4:], y0[4:])
+    want, _ = ox.linear(N_(q).astype(np.int64), N_(sh), {k: N_(v) for k, v in dec.items()}, checked=True)
+    assert np.array_equal(N_(y1), want)
