@@ -367,7 +367,7 @@ def run_b200(args, rank, world):
     cfg["num_hidden_layers"] = args.layers
     span = R * K + 3 * W + K + 24                                   # decode steps any phase runs from the prompt's end
     timer = LinTimer()
-    eng, c = build_engine(args.mode, cfg, dev, P + span + 64, timer)
+    eng, c = build_engine(args.mode, cfg, dev, max(P + span, SAMPLE_CTX + 40) + 64, timer)
 
     # ---- parity of this engine against the oracle (rank 0), and the CPU baseline timing at N = 1 ----
     parity, cpu_times = None, None

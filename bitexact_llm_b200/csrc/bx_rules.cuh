@@ -133,4 +133,18 @@ __device__ __forceinline__ i64 round_shift_hl(i64 T, i64 B, int d, i64 p, bool& 
   return y;
 }
 
+// round_shift_hl with a short cut for the common case. For a weight row on its own grid (d = 0) without residual
+// entries (B = 0) and a shift of 1 .. 31 bits (p = -k), H 2^32 + L = T and the two-word rule
+// (H << (32 - k)) + ((L + 2^(k-1)) >> k) is (T + 2^(k-1)) >> k, because H 2^32 is a multiple of 2^k. With
+// |T| < 2^61 (|q| <= 2^22, |W| < 2^23, K < 43690) no bit can be lost and |y| < 2^62: the flag stays clear. Same
+// integers as round_shift_hl, a fifth of its instructions.
+__device__ __forceinline__ i64 exact_round(i64 T, i64 B, int d, i64 p, bool plain_row, bool& bad) {
+  if (plain_row && p < 0 && p > -32) {
+    const int k = (int)(-p);
+    bad = false;
+    return (T + (1ll << (k - 1))) >> k;
+  }
+  return round_shift_hl(T, B, d, p, bad);
+}
+
 }  // namespace bx

@@ -11,6 +11,7 @@
 #include "../../include/bitexact_b200.h"
 #include "exact_linear.cuh"
 #include "exact_linear_splitk.cuh"
+#include "exact_linear_rows.cuh"
 #include "int8_linear.cuh"
 #include "int8_stages.cuh"
 #include "elementwise.cuh"
@@ -109,6 +110,20 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t K, uint64_t rows, uint6
   return r == CUDA_SUCCESS;
 }
 
+// The same tensor with boxes of `box_rows` rows of ONE plane (the B-operand chunks of the CTA-pair kernels).
+bool make_map_chunks(CUtensorMap* m, const void* base, uint64_t K, uint64_t rows, uint64_t planes, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {K, rows, planes};
+  cuuint64_t strides[2] = {K, rows * K};
+  cuuint32_t box[3] = {128, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <int TA>
@@ -174,6 +189,70 @@ int launch_exact_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const 
   return launched(1);
 }
 
+// CTA pairs resident at a time for a pair kernel (clusters of 2 with its shared memory), cached per device.
+template <class Kernel>
+int max_active_pairs(Kernel kernel, int smem, PerDevice& cache) {
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int n = cache.v[dev].load(std::memory_order_acquire);
+  if (n > 0) return n;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return 0;
+  }
+  cache.v[dev].store(n, std::memory_order_release);
+  return n;
+}
+
+template <int TA>
+int launch_exact_pair(const CUtensorMap& mw, const CUtensorMap& mb, const ExactEpiParams& ep, int K, cudaStream_t st) {
+  using Cfg = PairCfg<3, 3, TA>;
+  static PerDevice configured, pairs_cache;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(exact_linear_pair_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int pairs = max_active_pairs(exact_linear_pair_kernel<TA>, Cfg::SMEM_BYTES, pairs_cache);
+  if (pairs <= 0) return BX_ELAUNCH;
+  const int m_tiles = (ep.M + TA - 1) / TA;
+  const int n_tiles2 = (ep.N + 2 * WROWS - 1) / (2 * WROWS);
+  const int total = m_tiles * n_tiles2;
+  const int grid = 2 * (total < pairs ? total : pairs);
+  exact_linear_pair_kernel<TA><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, mb, ep, K, n_tiles2, m_tiles);
+  return launched(1);
+}
+
+template <int TN, bool DBL>
+int launch_exact_rows(const CUtensorMap& ma, const CUtensorMap& mw, const ExactEpiParams& ep, int K, cudaStream_t st) {
+  using Cfg = RowsCfg<TN, DBL>;
+  static PerDevice configured, pairs_cache;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(exact_linear_rows_kernel<TN, DBL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int pairs = max_active_pairs(exact_linear_rows_kernel<TN, DBL>, Cfg::SMEM_BYTES, pairs_cache);
+  if (pairs <= 0) return BX_ELAUNCH;
+  const int n_tiles = (ep.N + TN - 1) / TN;
+  const int m_tiles2 = (ep.M + 2 * WROWS - 1) / (2 * WROWS);
+  const long total = (long)n_tiles * m_tiles2;
+  const int grid = 2 * (int)(total < pairs ? total : pairs);
+  exact_linear_rows_kernel<TN, DBL><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, ep, K, n_tiles, m_tiles2);
+  return launched(1);
+}
+
 template <int TA, bool POST>
 int launch_int8(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParams& ep, int K, cudaStream_t st) {
   using Cfg = GemmCfg<1, 2, TA>;
@@ -189,19 +268,54 @@ int launch_int8(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParam
   return launched(1);
 }
 
+template <int TA, bool POST>
+int launch_int8_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParams& ep, int K,
+                           cudaStream_t st) {
+  using Cfg = GemmCfg<1, 2, TA>;
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(int8_linear_persistent_kernel<TA, POST>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int sms = device_sms();
+  if (sms <= 0) return BX_ELAUNCH;
+  const int m_tiles = (ep.M + TA - 1) / TA;
+  const int n_tiles = (ep.N + WROWS - 1) / WROWS;
+  const int total = m_tiles * n_tiles;
+  const int grid = total < sms ? total : sms;
+  int8_linear_persistent_kernel<TA, POST><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mw, ma, ep, K, n_tiles, m_tiles);
+  return launched(1);
+}
+
 template <bool POST>
 int run_int8(const int8_t* a, const int8_t* w, const Int8EpiParams& ep, int K, int tile_rows, cudaStream_t st) {
   const int M = ep.M, N = ep.N;
   if (!a || !w || M < 0 || N <= 0 || K <= 0 || K % 16 || K >= 65536 || !aligned16(a) || !aligned16(w)) return BX_EARG;
   if (M == 0) return BX_OK;
   int ta = tile_rows;
-  if (ta == 0) {
+  bool persistent = false;
+  if (ta < 0) {                       // negative: that tile size on the persistent kernel
+    ta = -ta;
+    persistent = true;
+  } else if (ta == 0) {
     const long n_tiles = (N + WROWS - 1) / WROWS;
     ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : (n_tiles * ((M + 127) / 128) >= 90 ? 128 : 64);
+    // more tiles than SMs: one CTA per SM with the epilogue of a tile behind the MMAs of the next
+    persistent = n_tiles * ((M + ta - 1) / ta) > 148;
   }
   CUtensorMap mw, ma;
   if (!make_map(&mw, w, (uint64_t)K, (uint64_t)N, 1, WROWS)) return BX_ELAUNCH;
   if (!make_map(&ma, a, (uint64_t)K, (uint64_t)M, 2, (uint32_t)ta)) return BX_ELAUNCH;
+  if (persistent) {
+    switch (ta) {
+      case 16: return launch_int8_persistent<16, POST>(mw, ma, ep, K, st);
+      case 32: return launch_int8_persistent<32, POST>(mw, ma, ep, K, st);
+      case 64: return launch_int8_persistent<64, POST>(mw, ma, ep, K, st);
+      case 128: return launch_int8_persistent<128, POST>(mw, ma, ep, K, st);
+      default: return BX_EARG;
+    }
+  }
   switch (ta) {
     case 16: return launch_int8<16, POST>(mw, ma, ep, K, st);
     case 32: return launch_int8<32, POST>(mw, ma, ep, K, st);
@@ -326,6 +440,33 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
   }
   // Split-K over a cluster of CTAs (200 + activation rows per tile asks for it; automatic for small batches whose
   // tile list covers less than half of the SMs): as many K slices as keep the CTA count within the 148 SMs.
+  if (ta == 416 || ta == 432 || ta == 448) {          // 400 + rows: that tile size on the CTA-pair kernel
+    ta -= 400;
+    CUtensorMap mw, mb;
+    if (!make_map(&mw, limbs, (uint64_t)K, (uint64_t)N, 3, WROWS)) return BX_ELAUNCH;
+    if (!make_map_chunks(&mb, scratch, (uint64_t)K, (uint64_t)M, 3, (uint32_t)(ta / 2))) return BX_ELAUNCH;
+    ExactEpiParams ep{q, ldq, sh, d, g, cnt, ec, ev, R, y, flag, M, N, checked};
+    switch (ta) {
+      case 16: return launch_exact_pair<16>(mw, mb, ep, K, st);
+      case 32: return launch_exact_pair<32>(mw, mb, ep, K, st);
+      default: return launch_exact_pair<48>(mw, mb, ep, K, st);
+    }
+  }
+  if (ta == 516 || ta == 532 || ta == 548 || ta == 564 || ta == 580) {
+    // 500 + weight rows per tile: activation rows on the MMA M side, CTA pairs (16 .. 48: two accumulator buffers)
+    ta -= 500;
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, scratch, (uint64_t)K, (uint64_t)M, 3, WROWS)) return BX_ELAUNCH;
+    if (!make_map_chunks(&mw, limbs, (uint64_t)K, (uint64_t)N, 3, (uint32_t)(ta / 2))) return BX_ELAUNCH;
+    ExactEpiParams ep{q, ldq, sh, d, g, cnt, ec, ev, R, y, flag, M, N, checked};
+    switch (ta) {
+      case 16: return launch_exact_rows<16, true>(ma, mw, ep, K, st);
+      case 32: return launch_exact_rows<32, true>(ma, mw, ep, K, st);
+      case 48: return launch_exact_rows<48, true>(ma, mw, ep, K, st);
+      case 64: return launch_exact_rows<64, false>(ma, mw, ep, K, st);
+      default: return launch_exact_rows<80, false>(ma, mw, ep, K, st);
+    }
+  }
   int split = 0;
   if (ta >= 200) {
     ta -= 200;

@@ -7,6 +7,8 @@
 
 #include "bx_rules.cuh"
 #include "limb_gemm.cuh"
+#include "limb_gemm_pair.cuh"
+
 
 namespace bx {
 
@@ -30,32 +32,64 @@ template <int TA>
 struct ExactEpilogue {
   using Params = ExactEpiParams;
 
+  static constexpr int RMAX = 4;
+
+  // What a thread needs about its weight row n (TMEM lane): loaded BEFORE the accumulators are waited for, so the
+  // loads (two dependent levels: the count, then the list) overlap the main loop instead of heading every tile's
+  // epilogue. The residual list of row n (a handful of entries in a few per cent of the rows) is read once.
+  struct Row {
+    int n, d, cnt, wcnt;
+    bool nok;
+    i64 gd;
+    int ecr[RMAX];
+    i64 evr[RMAX];
+  };
+
+  static __device__ __forceinline__ Row load_row(int quarter, int lane, int n0, const Params& p) {
+    Row r;
+    r.n = n0 + quarter * 32 + lane;
+    r.nok = r.n < p.N;
+    r.d = r.nok ? (int)p.d[r.n] : 0;
+    r.gd = r.nok ? p.g[r.n] - (i64)r.d + FR : 0;
+    r.cnt = (r.nok && p.cnt) ? p.cnt[r.n] : 0;
+#pragma unroll
+    for (int j = 0; j < RMAX; ++j) {
+      r.ecr[j] = 0;
+      r.evr[j] = 0;
+      if (j < r.cnt) {
+        r.ecr[j] = p.ec[(i64)r.n * p.R + j];
+        r.evr[j] = p.ev[(i64)r.n * p.R + j];
+      }
+    }
+    r.wcnt = __reduce_max_sync(0xffffffffu, r.cnt);                    // longest list in the warp (uniform)
+    return r;
+  }
+
+  // Pulls what the epilogue of tile rows m0 .. will read per output into L1 while the tile's MMAs still run: the
+  // row exponents (one lane per row) and, for a thread whose weight row has a residual list, its gathers from q.
+  static __device__ __forceinline__ void prefetch(const Row& r, int group, int lane, int m0, const Params& p) {
+#pragma unroll 1
+    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
+      if (m0 + c0 >= p.M) break;
+      if (lane < 8 && m0 + c0 + lane < p.M) prefetch_l1(p.sh + m0 + c0 + lane);
+      if (r.cnt > 0) {
+        for (int i = 0; i < 8; ++i) {
+          const int m = m0 + c0 + i;
+          if (m >= p.M) break;
+#pragma unroll
+          for (int j = 0; j < RMAX; ++j)
+            if (j < r.cnt) prefetch_l1(p.q + (i64)m * p.ldq + r.ecr[j]);
+        }
+      }
+    }
+  }
+
   // One thread per weight row n (TMEM lane) and column group; walks its share of the TA activation rows in chunks
   // of 8 accumulator columns.
   static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
-                                             bool has_k, const Params& p) {
-    const int n = n0 + quarter * 32 + lane;
-    const bool nok = n < p.N;
-    const int d = nok ? (int)p.d[n] : 0;
-    const i64 gd = nok ? p.g[n] - (i64)d + FR : 0;
-    const int cnt = (nok && p.cnt) ? p.cnt[n] : 0;
-    // The residual list of weight row n (a handful of entries in a few per cent of the rows) is read once per thread;
-    // per output only the gathers from q remain, independent of each other. A warp without any residual row (and
-    // every warp of a linear without residual) skips the whole term.
-    constexpr int RMAX = 4;
-    int ecr[RMAX];
-    i64 evr[RMAX];
-#pragma unroll
-    for (int j = 0; j < RMAX; ++j) {
-      ecr[j] = 0;
-      evr[j] = 0;
-      if (j < cnt) {
-        ecr[j] = p.ec[(i64)n * p.R + j];
-        evr[j] = p.ev[(i64)n * p.R + j];
-      }
-    }
-    const int wcnt = __reduce_max_sync(0xffffffffu, cnt);              // longest list in the warp (uniform)
-    const bool warp_res = wcnt > 0;
+                                             bool has_k, const Params& p, const Row& r) {
+    const int n = r.n;
+    const bool warp_res = r.wcnt > 0;
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
@@ -68,7 +102,7 @@ struct ExactEpilogue {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int m = m0 + c0 + i;
-        if (m < p.M && nok) {
+        if (m < p.M && r.nok) {
           i64 T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +
                   shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
           if (!has_k) T = 0;
@@ -76,12 +110,12 @@ struct ExactEpilogue {
           if (warp_res) {
 #pragma unroll
             for (int j = 0; j < RMAX; ++j)
-              if (j < wcnt && j < cnt) B += (i64)p.q[(i64)m * p.ldq + ecr[j]] * evr[j];
-            for (int j = RMAX; j < cnt; ++j)
+              if (j < r.wcnt && j < r.cnt) B += (i64)p.q[(i64)m * p.ldq + r.ecr[j]] * r.evr[j];
+            for (int j = RMAX; j < r.cnt; ++j)
               B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
           }
           bool bad;
-          const i64 yv = round_shift_hl(T, B, d, p.sh[m] + gd, bad);
+          const i64 yv = round_shift_hl(T, B, r.d, p.sh[m] + r.gd, bad);
           any_bad |= bad;
           p.y[(i64)m * p.N + n] = yv;
         }
@@ -106,6 +140,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 exact_linear_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                                const ExactEpiParams ep, int K, int n_tiles, int m_tiles) {
   limb_gemm_persistent<3, 3, TA, ExactEpilogue<TA>>(&tmap_w, &tmap_a, n_tiles, m_tiles, (K + BKB - 1) / BKB, ep);
+}
+
+// CTA-pair form (tcgen05 .cta_group::2, see limb_gemm_pair.cuh): a cluster of two CTAs per 256 weight rows, one pair
+// per TPC walks the tile list. tmap_b is the activation map with boxes of TA / 2 rows of one limb plane.
+template <int TA>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+exact_linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_b,
+                         const ExactEpiParams ep, int K, int n_tiles2, int m_tiles) {
+  limb_gemm_pair_persistent<3, 3, TA, ExactEpilogue<TA>>(&tmap_w, &tmap_b, n_tiles2, m_tiles, (K + BKB - 1) / BKB, ep);
 }
 
 // q int32 [M, K] (row stride ldq) -> limb planes int8 [3, M, K] (signed base-256 digits, intops.py:62-70).

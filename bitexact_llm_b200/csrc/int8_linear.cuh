@@ -41,11 +41,40 @@ struct Int8EpiParams {
 template <int TA, bool POST>
 struct Int8Epilogue {
   using Params = Int8EpiParams;
+
+  // The thread's weight row and its channel multiplier, loaded before the accumulators are waited for.
+  struct Row {
+    int n;
+    bool nok;
+    i64 mc;
+  };
+
+  static __device__ __forceinline__ Row load_row(int quarter, int lane, int n0, const Params& p) {
+    Row r;
+    r.n = n0 + quarter * 32 + lane;
+    r.nok = r.n < p.N;
+    r.mc = (POST && r.nok) ? p.mul[r.n] : 0;
+    return r;
+  }
+
+  // Row scales of the tile's activation rows into L1 while the MMAs still run.
+  static __device__ __forceinline__ void prefetch(const Row&, int group, int lane, int m0, const Params& p) {
+    if (!POST) return;
+#pragma unroll 1
+    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
+      if (m0 + c0 >= p.M) break;
+      if (lane < 8 && m0 + c0 + lane < p.M) {
+        prefetch_l1(p.mant + m0 + c0 + lane);
+        prefetch_l1(p.e + m0 + c0 + lane);
+      }
+    }
+  }
+
   static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
-                                             bool has_k, const Params& p) {
-    const int n = n0 + quarter * 32 + lane;
-    const bool nok = n < p.N;
-    const i64 mc = (POST && nok) ? p.mul[n] : 0;
+                                             bool has_k, const Params& p, const Row& r) {
+    const int n = r.n;
+    const bool nok = r.nok;
+    const i64 mc = r.mc;
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
@@ -83,6 +112,15 @@ int8_linear_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int mt = blockIdx.x % m_tiles;
   const int nt = blockIdx.x / m_tiles;
   limb_gemm_tile<1, 2, TA, Int8Epilogue<TA, POST>>(&tmap_w, &tmap_a, nt * WROWS, mt * TA, 0, (K + BKB - 1) / BKB, ep);
+}
+
+// Persistent form (one CTA per SM walks the tile list, two accumulator buffers: the post epilogue of tile i overlaps
+// the MMAs of tile i + 1). 2 * 2 TA <= 512 TMEM columns holds for every TA up to 128.
+template <int TA, bool POST>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+int8_linear_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                              const Int8EpiParams ep, int K, int n_tiles, int m_tiles) {
+  limb_gemm_persistent<1, 2, TA, Int8Epilogue<TA, POST>>(&tmap_w, &tmap_a, n_tiles, m_tiles, (K + BKB - 1) / BKB, ep);
 }
 
 }  // namespace bx

@@ -156,14 +156,16 @@ __device__ __forceinline__ void limb_gemm_tile(const CUtensorMap* tmap_w, const 
       }
     }
   } else {
-    // ---- epilogue warps ----
+    // ---- epilogue warps: row constants and L1 prefetches first, they overlap the main loop ----
+    const typename Epi::Row row = Epi::load_row(warp & 3, lane, n0, ep);
+    Epi::prefetch(row, (warp - 2) >> 2, lane, m0, ep);
     bool ok = true;
     if (nkb > 0) ok = mbar_wait(&sh->acc_full, 0);
     ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sh->abort_flag) == 0);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
-      Epi::run(tmem, warp & 3, (warp - 2) >> 2, lane, n0, m0, nkb > 0, ep);
+      Epi::run(tmem, warp & 3, (warp - 2) >> 2, lane, n0, m0, nkb > 0, ep, row);
     } else if (lane == 0) {
       atomicAdd(&g_wait_timeouts, 1);
     }
@@ -308,13 +310,16 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
     bool ok = true;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
       const int buf = tcount & 1, use = tcount >> 1;
+      const int n0 = (tile / m_tiles) * WROWS, m0 = (tile % m_tiles) * TA;
+      // row constants and L1 prefetches before the wait: they overlap the MMAs of this tile
+      const typename Epi::Row row = Epi::load_row(warp & 3, lane, n0, ep);
+      Epi::prefetch(row, (warp - 2) >> 2, lane, m0, ep);
       if (ok) ok = mbar_wait(&sh->acc_full[buf], use & 1);
       ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sh->abort_flag) == 0);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      Epi::run(tmem + buf * Cfg::COLS, warp & 3, (warp - 2) >> 2, lane, (tile / m_tiles) * WROWS, (tile % m_tiles) * TA,
-               nkb > 0, ep);
+      Epi::run(tmem + buf * Cfg::COLS, warp & 3, (warp - 2) >> 2, lane, n0, m0, nkb > 0, ep, row);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);

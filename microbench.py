@@ -90,7 +90,7 @@ def gemmr(args):
     out = []
     for M in [int(v) for v in args.m.split(",")]:
         for name, (N, K) in FUSED.items():
-            if name == "lm":
+            if name == "lm" and args.shapes != "all":
                 continue
             w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
             d0 = decompose(w.to(dev))

@@ -32,8 +32,8 @@ def test_golden_linear_with_residual_and_extreme_shifts():
     z = np.load(os.path.join(GOLD, "exact_ops.npz"))
     dec = {k: z["lin_" + k] for k in ("limbs", "g", "d", "rr", "rc", "rv")}
     fl = _lin(dec)
-    # negative: the persistent kernel; 200 + rows: split-K over a cluster of CTAs
-    for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48, 216, 232, 264):
+    # negative: the persistent kernel; 200 + rows: split-K over a cluster of CTAs; 400 + rows: CTA pairs (cta_group::2)
+    for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48, 216, 232, 264, 416, 432, 448, 516, 532, 548, 564, 580):
         y, flag = _run(fl, z["lin_q"], z["lin_sh"], True, tile)
         assert np.array_equal(y, z["lin_y"]), tile
         assert flag == bool(z["lin_flag"])
@@ -62,7 +62,7 @@ def test_seeded_shapes_against_oracle(M, N, K):
     sh = rng.randint(-45, -8, M).astype(np.int64)
     want, wflag = ox.linear(q, sh, dec, checked=True)
     fl = _lin(dec)
-    for tile in (None, 16, 80, -48, 216, 232, 264) if M > 16 else (None, 64, -16, 216, 264):
+    for tile in (None, 16, 80, -48, 216, 232, 264, 416, 432, 448) if M > 16 else (None, 64, -16, 216, 264, 416, 448, 516, 548, 580):
         y, flag = _run(fl, q, sh, True, tile)
         assert np.array_equal(y, want), (tile, int((y != want).sum()))
         assert flag == wflag
@@ -81,7 +81,7 @@ def test_persistent_kernel_many_tiles_per_cta():
     sh = rng.randint(-45, -8, M).astype(np.int64)
     want, wflag = ox.linear(q, sh, dec, checked=True)
     fl = _lin(dec)
-    for tile in (-16, -32, -48, None):
+    for tile in (-16, -32, -48, None, 416, 432, 448, 532, 548, 564, 580):
         y, flag = _run(fl, q, sh, True, tile)
         assert np.array_equal(y, want), (tile, int((y != want).sum()))
         assert flag == wflag

@@ -38,7 +38,7 @@ def exact_1b():
     from bitexact_llm_b200.vllm_plugin.exact_run import ExactEngine
     cfg = dict(consts.LLAMA_1B)
     cfg["num_hidden_layers"] = 1
-    c = consts.build(cfg, consts.random_state_dict(cfg, seed=0, device="cuda"), n_pos=CTX + 64)
+    c = consts.build(cfg, consts.random_state_dict(cfg, seed=0, device="cuda"), n_pos=CTX + 512)
     eng = ExactEngine(c, "cuda")
     m = OracleModel(_np(c))
     sample = step_sample.make_sample(cfg, ROWS, CTX, seed=0)
