@@ -16,6 +16,7 @@
 #include "int8_stages.cuh"
 #include "elementwise.cuh"
 #include "paged_attention.cuh"
+#include "prefill_attention.cuh"
 #include "sampler.cuh"
 #include "logp.cuh"
 #include "decompose.cuh"
@@ -863,6 +864,55 @@ int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache
   if (!ptab) return BX_EARG;
   return run_attention(q, nullptr, qpos, cache, nb, sc_nb, sc_h, sc_bs, bs, bt, bt_is_int64, sbt, nblk, rmap, nullptr,
                        0, ptab, num, den, R, HKV, M, HD, cluster_size, variant, nullptr, 0, stream);
+}
+
+int bx_prefill_attention(const int32_t* q, const int64_t* sh, const int64_t* pos, const int32_t* tiles, int n_tiles,
+                         const int8_t* cache, int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs,
+                         const void* bt, int bt_is_int64, int64_t sbt, int nblk, const int64_t* lut, int64_t l2e,
+                         const int32_t* ptab, int64_t* num, int64_t* den, int HKV, int G, int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!q || !pos || !tiles || !cache || !bt || !num || !den || n_tiles < 0) return BX_EARG;
+  if (!ptab && (!sh || !lut)) return BX_EARG;
+  if (HD != ATT_HD || HKV <= 0 || HKV > 65535 || G < 1 || G > PF_ROWS || nblk <= 0 || nb <= 0) return BX_EARG;
+  if (bs < 8 || bs > PF_KEYS || PF_KEYS % bs || (int64_t)nblk * bs >= 43690) return BX_EARG;
+  if (sc_bs % 16 || sc_h % 16 || sc_nb % 16 || sc_bs < 384 || !aligned16(cache) || !aligned16(q)) return BX_EARG;
+  if (n_tiles == 0) return BX_OK;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return BX_ELAUNCH;
+  CUtensorMap tm;
+  cuuint64_t dims[4] = {512, (cuuint64_t)bs, (cuuint64_t)HKV, (cuuint64_t)nb};
+  cuuint64_t strides[3] = {(cuuint64_t)sc_bs, (cuuint64_t)sc_h, (cuuint64_t)sc_nb};
+  cuuint32_t box[4] = {128, (cuuint32_t)bs, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (fn(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<int8_t*>(cache), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return BX_ELAUNCH;
+  const int smem = 2 * PF_STAGE + PF_QTILE + PF_PTILE + (int)sizeof(PrefillSmall) + 1024;
+  static PerDevice configured;
+  if (once_per_device(configured, [smem] {
+        return cudaFuncSetAttribute(prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  PrefillParams p{};
+  p.q = q;
+  p.sh = (const i64*)sh;
+  p.pos = (const i64*)pos;
+  p.tiles = tiles;
+  p.bt = bt;
+  p.bt64 = bt_is_int64;
+  p.sbt = sbt;
+  p.nblk = nblk;
+  p.bs = bs;
+  p.w.lut = (const i64*)lut;
+  p.w.l2e = (i64)l2e;
+  p.w.ptab = ptab;
+  p.num = (i64*)num;
+  p.den = (i64*)den;
+  p.HKV = HKV;
+  p.G = G;
+  prefill_attention_kernel<<<dim3((unsigned)n_tiles, (unsigned)HKV), PF_THREADS, smem, (cudaStream_t)stream>>>(tm, p);
+  return launched(1);
 }
 
 int bx_int8_norm(int mode, const void* xin, const int64_t* yin, const int64_t* ids, const int64_t* gamma,

@@ -50,14 +50,20 @@ class Session:
         self.lens[seq] = n
 
     @torch.no_grad()
-    def prefill(self, prompts, lens=None, chunk_rows=4096):
+    def prefill(self, prompts, lens=None, chunk_rows=4096, tiles=True):
         """prompts: int64 [B, P] right-padded, lens [B] the true lengths (default: all P). Token rows are processed
-        in position chunks so that every row's keys are in the cache before it attends. Returns the final residual
-        row of each sequence [B, D]."""
+        in position chunks so that every row's keys are in the cache before it attends; with `tiles` the attention
+        of a chunk runs on the prefill tile kernel (runs of 32 / G consecutive tokens share their K / V staging),
+        else every token is a row of the decode kernel. Same integers either way. Returns the final residual row of
+        each sequence [B, D]."""
+        from .vllm_plugin import tri_prefill
         B, P = prompts.shape
         dev = self.eng.dev
         prompts = prompts.to(dev)
+        lens_host = [P] * B if lens is None else [int(v) for v in lens.tolist()]
         lens = torch.full((B,), P, dtype=torch.long, device=dev) if lens is None else lens.to(dev).long()
+        G = self.eng.H // self.eng.HKV
+        use_tiles = tiles and self.eng.HD == 64 and tri_prefill.BM % G == 0 and self.bs in (8, 16, 32, 64, 128)
         step = max(1, chunk_rows // B)
         last = torch.zeros(B, self.eng.D, dtype=torch.long, device=dev)
         for p0 in range(0, P, step):
@@ -68,7 +74,16 @@ class Session:
                 break
             pos = grid[live]                                                      # sequence-major rows
             seq = self.rows[:, None].expand(-1, p1 - p0)[live]
-            x = self.eng.forward(self.kvs, prompts[:, p0:p1][live], pos, self._slots(seq, pos), self.bt, seq)
+            tt = None
+            if use_tiles:                                                       # sequence-major rows: runs per sequence
+                pre, row0 = [], 0
+                for b in range(B):
+                    n = max(0, min(p1, lens_host[b]) - p0)
+                    if n:
+                        pre.append((b, row0, n, p0 + n))
+                    row0 += n
+                tt = tri_prefill.tile_table(pre, G).to(dev)
+            x = self.eng.forward(self.kvs, prompts[:, p0:p1][live], pos, self._slots(seq, pos), self.bt, seq, tiles=tt)
             fin = pos == lens[seq] - 1
             last[seq[fin]] = x[fin]
         self.lens += lens

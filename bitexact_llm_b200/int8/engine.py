@@ -6,7 +6,7 @@ qkv, attention, attn_out, linear, add_norm, linear, silu_quant, linear, add_norm
 import torch
 
 from .. import _native as nv
-from ..vllm_plugin import tri_fuse, tri_paged
+from ..vllm_plugin import tri_fuse, tri_paged, tri_prefill
 from .gemm_skinny import linear_post
 
 
@@ -47,7 +47,7 @@ class IntEngine:
                 return linear_post(pre[0], lin[0], lin[1], lin[2], pre[1], pre[2], self.fl, True)
         return linear_post(pre[0], lin[0], lin[1], lin[2], pre[1], pre[2], self.fl, True)
 
-    def forward(self, kvs, ids, pos, slot, bt, rmap):
+    def forward(self, kvs, ids, pos, slot, bt, rmap, tiles=None):
         """Same contract as ExactEngine.forward; returns the residual stream int64 [N, D] at 16 bits."""
         fz = tri_fuse
         N, G = ids.shape[0], self.H // self.HKV
@@ -58,7 +58,12 @@ class IntEngine:
         for i in range(self.L):
             ly = self.layers[i]
             q = fz.qkv(self, self._lin(pre, ly["wqkv"]), None, None, None, pos, slot, kvs[i])
-            num, den = tri_paged.attend(q, qpos, kvs[i], bt, self.ptab, rmap=rmap)
+            if tiles is not None:
+                num = torch.zeros(N, self.HKV, G, self.HD, dtype=torch.long, device=self.dev)
+                den = torch.ones(N, self.HKV, G, 1, dtype=torch.long, device=self.dev)    # padding rows: 0 / 1
+                tri_prefill.attend(q, pos, kvs[i], bt, self.ptab, tiles, num, den)
+            else:
+                num, den = tri_paged.attend(q, qpos, kvs[i], bt, self.ptab, rmap=rmap)
             x, *pre = fz.add_norm(self, self._lin(fz.attn_out(self, num, den), ly["wo"]), None, None, None, x, ly["gm"])
             a8, mant, e, _ = fz.silu_quant(self, self._lin(pre, ly["wgu"]), None, None, None, self.silu_t, scr=self.scr[i])
             nxt = self.layers[i + 1]["ga"] if i + 1 < self.L else None

@@ -9,7 +9,7 @@ import torch
 
 from .. import _native as nv
 from ..exact.model import Lin
-from . import exact_fuse, tri_exact_attn
+from . import exact_fuse, tri_exact_attn, tri_prefill
 from .exact_gemm import FusedLin
 
 L2E28_HD = {64: 387270501, 128: 273841598}        # src/bitexact/exact/ops.py:19-20
@@ -55,9 +55,11 @@ class ExactEngine:
         if bool(self.fl.item()):
             raise OverflowError("integer bound violated (exact mode)")
 
-    def forward(self, kvs, ids, pos, slot, bt, rmap):
+    def forward(self, kvs, ids, pos, slot, bt, rmap, tiles=None):
         """ids, pos, slot [N]: the step's tokens (slot < 0: padding, written to the null block 0); kvs: list of the
         per-layer caches int8 [nb, HKV, bs, 8 HD]; bt [*, nblk] block table, rmap [N] the table row of each token.
+        tiles (int32 [T, 3] on the device: block-table row, first token row, tokens; `tri_prefill.tile_table`):
+        prompt processing, runs of consecutive tokens of one request attend through the tile kernel (same integers).
         Returns the residual stream int64 [N, D] at 24 bits."""
         fl, fz = self.fl, exact_fuse
         N, G = ids.shape[0], self.H // self.HKV
@@ -68,8 +70,12 @@ class ExactEngine:
         for i in range(self.L):
             ly = self.layers[i]
             qq, shq = fz.qkv(self, ly["wqkv"](q, sh, fl, False), pos, slot, kvs[i], fl)
-            num, den = tri_exact_attn.attend(qq.view(N, self.HKV, G, self.HD), shq.view(N, self.HKV, G), qpos, kvs[i],
-                                             bt, rmap, self.exp2, self.l2e)
+            if tiles is not None:
+                num, den = tri_prefill.attend_exact(qq.view(N, self.HKV, G, self.HD), shq.view(N, self.HKV, G), pos,
+                                                    kvs[i], bt, tiles, self.exp2, self.l2e)
+            else:
+                num, den = tri_exact_attn.attend(qq.view(N, self.HKV, G, self.HD), shq.view(N, self.HKV, G), qpos,
+                                                 kvs[i], bt, rmap, self.exp2, self.l2e)
             qo, sho = fz.attn_out(self, num, den)
             x, q, sh = fz.add_norm(self, ly["wo"](qo, sho, fl, True), x, ly["gm"], fl)
             q, sh = fz.silu_quant(self, ly["wgu"](q, sh, fl, False), self.exp2, fl)

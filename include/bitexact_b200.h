@@ -212,6 +212,26 @@ int bx_int8_attention_ws(const int32_t* q, const int64_t* qpos, const int8_t* ca
                          const int64_t* rmap, const int32_t* ptab, int64_t* num, int64_t* den, int R, int HKV, int M,
                          int HD, int cluster_size, int variant, void* scratch, size_t scratch_bytes, void* stream);
 
+/* ---- prefill attention (both weight rules) -------------------------------------------------------------------------
+ * Attention of whole TILES of prompt tokens: a tile is up to 32 / G consecutive tokens of one request; one CTA per
+ * (tile, KV head) stages every K / V row once for the tile's 32 query rows (token x G query heads), runs both integer
+ * sweeps and has the limb products (scores and p.V) on tcgen05 with TMEM accumulators.
+ *   q      int32 [N, HKV, G, 64] token-major (|q| <= 2^22 exact mode; within three limbs int8 mode), 16-byte aligned
+ *   sh     int64 [N, HKV, G] row exponents (exact mode; NULL with ptab)
+ *   pos    int64 [N] position of each token: key s is visible iff s <= pos
+ *   tiles  int32 [n_tiles, 3] = (block-table row, first token, tokens <= 32 / G), on the device
+ *   cache, bt, nblk, bs as bx_exact_attention (bs one of 8, 16, 32, 64, 128); lut / l2e: exact weight rule;
+ *   ptab: int8-mode weight table (then lut may be NULL)
+ *   num int64 [N, HKV, G, 64], den int64 [N, HKV, G]: the rows of the tiles' tokens are written, others untouched.
+ * Same integers as the per-row kernels on each token. Replaces tri_prefill.attend + tile_table
+ * (src/bitexact/vllm_plugin/tri_prefill.py:32-108, int8 weight rule); exact mode has no multi-token kernel in the
+ * reference (its plugin runs prompt tokens as rows, src/bitexact/vllm_plugin/exact_run.py:3-7): there the unfused
+ * bmm + softmax_w + bmm of src/bitexact/exact/model.py:114-119 is the rule. */
+int bx_prefill_attention(const int32_t* q, const int64_t* sh, const int64_t* pos, const int32_t* tiles, int n_tiles,
+                         const int8_t* cache, int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs,
+                         const void* bt, int bt_is_int64, int64_t sbt, int nblk, const int64_t* lut, int64_t l2e,
+                         const int32_t* ptab, int64_t* num, int64_t* den, int HKV, int G, int HD, void* stream);
+
 /* ---- int8-mode attention and element-wise stages -------------------------------------------------------
  * Fixed points of int8 mode: residual stream / linear outputs / logits 16 bits, gamma 12, cos / sin 16, q / k / v 14,
  * attention weights 20. A linear's input is always (a8, mant, e): activation limb planes int8 [2, M, K] (limb i of
