@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-int8-extra", action="store_true", help="skip the int8-mode pass reported under `extra`")
+    ap.add_argument("--no-column-sharded", action="store_true",
+                    help="N > 1: skip the int8-mode column-sharded pass reported under `extra.column_sharded`")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="launch kernel by kernel instead of replaying a CUDA graph")
     return ap.parse_args()
 
@@ -486,6 +488,13 @@ def run_b200(args, rank, world):
         dec = hs = None
         int8_extra = int8_pass(args, cfg, dev, peak_mean)
 
+    # ---- N > 1: the column-sharded configuration, the one place where the data path crosses NVLink ----
+    sharded_extra = None
+    if world > 1 and not args.no_column_sharded:
+        dec = hs = run = ses = eng = None                      # free the exact-mode engine and its cache
+        torch.cuda.empty_cache()
+        sharded_extra = column_sharded_pass(args, cfg, dev, rank, world)
+
     times = torch.tensor(region_ms + e2e_ms, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -551,9 +560,114 @@ def run_b200(args, rank, world):
     }
     if int8_extra:
         line["extra"]["int8_mode"] = int8_extra
+    if sharded_extra:
+        line["extra"]["column_sharded"] = sharded_extra
     if cpu_times:
         line["cpu_baseline"], _ = cpu_summary(cpu_times, args.layers, host_cores())
     print(json.dumps(line), flush=True)
+
+
+class CollectiveTimer:
+    """CUDA-event pairs around every collective of `bitexact_llm_b200.parallel` while `on`."""
+
+    def __init__(self):
+        self.on, self.spans = False, []
+
+    @contextlib.contextmanager
+    def span(self, name, nbytes):
+        import torch
+        if not self.on:
+            yield
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        yield
+        e1.record()
+        self.spans.append((name, nbytes, e0, e1))
+
+    def summary(self, steps):
+        out = {}
+        for name, nbytes, e0, e1 in self.spans:
+            d = out.setdefault(name, {"calls_per_step": 0.0, "ms_per_step": 0.0, "bytes_per_step": 0.0})
+            d["calls_per_step"] += 1.0 / steps
+            d["ms_per_step"] += e0.elapsed_time(e1) / steps
+            d["bytes_per_step"] += nbytes / steps
+        return out
+
+
+def column_sharded_pass(args, cfg, dev, rank, world):
+    """BASELINE config 5: int8 mode, 64 sequences per GPU (512 on 8) with prompt lengths U[16, 4096], sequences
+    sharded over the ranks, MLP and LM head + sampler sharded by output column (NCCL all-gathers of the int8 limb
+    planes and the int64 outputs, integer all-reduce MAX of the SiLU row maxima, all-gather of the (max, index)
+    pairs). Returns the decode rate over all ranks and the per-step time of every collective."""
+    import torch
+    import torch.distributed as dist
+
+    from bitexact_llm_b200 import parallel as par
+    from bitexact_llm_b200.decode import Session
+    from bitexact_llm_b200.exact import consts
+    from bitexact_llm_b200.int8 import consts as consts8
+    K, W = args.steps, args.warmup
+    per = 64
+    span = 3 * K + 2 * W + 8
+    sd = consts.random_state_dict(cfg, seed=0, device=dev)
+    c = consts8.build(cfg, sd, n_pos=4096 + span + 64)
+    del sd
+    eng = par.ColumnShardedIntEngine(c, dev)
+    del c
+    g = torch.Generator().manual_seed(5000 + rank)
+    lens = torch.randint(16, 4097, (per,), generator=g)
+    P = int(lens.max())
+    prompts = torch.randint(0, cfg["vocab_size"], (per, P), generator=g)
+    ses = Session(eng, per, 4096 + span, perm_seed=rank)
+    eng.sharded = False
+    h = ses.prefill(prompts, lens, chunk_rows=8192)
+    eng.sharded = True
+    rows_all = torch.zeros(per * world, 4, dtype=torch.long, device=dev)
+    rows_all[:, 0] = torch.arange(per * world, device=dev)
+    rows_all[:, 2], rows_all[:, 3] = 7, 10
+    state = {"h": h}
+
+    def step():
+        tok = eng.sample(state["h"], rows_all)
+        rows_all[:, 1] += 1
+        state["h"] = ses.step(tok)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step()
+    regions = []
+    for _ in range(2):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            step()
+        e1.record()
+        barrier()
+        regions.append(e0.elapsed_time(e1))
+    timer = CollectiveTimer()
+    par.TIMER = timer
+    timer.on = True
+    for _ in range(K):
+        step()
+    barrier()
+    timer.on = False
+    par.TIMER = None
+    eng.check()
+    t = torch.tensor([min(regions)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    coll = timer.summary(K)
+    return {"workload": "BASELINE config 5: int8 mode, 64 sequences per GPU, prompt lengths U[16, 4096] (seeded), "
+                        "sequence-sharded attention, MLP and LM head + sampler sharded by output column",
+            "value": world * per * K / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms / K,
+            "launch": "kernel by kernel (NCCL collectives between the kernels)",
+            "collectives": coll, "collective_ms_per_step": sum(d["ms_per_step"] for d in coll.values()),
+            "mean_context": float(lens.float().mean()) + W + K}
 
 
 def int8_pass(args, cfg, dev, peak):

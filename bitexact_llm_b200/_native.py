@@ -50,6 +50,8 @@ _SIGNATURES = {
     "bx_int8_attn_out": (I, [P, P, P, P, P, I, I, I, P]),
     "bx_int8_silu_quant": (I, [P, P, P, P, P, P, I, I, P]),
     "bx_int8_flag_end": (I, [P, P, I, P]),
+    "bx_int8_silu_prod": (I, [P, P, P, P, P, I, I, P]),
+    "bx_int8_quant_rows": (I, [P, P, P, P, P, I, I, P]),
     "bx_int8_post": (I, [P, P, L, P, P, P, P, I, I, I, P]),
     "bx_pcg_raw": (I, [P, P, I, I, P]),
     "bx_exact_silu_prod": (I, [P, P, P, P, P, I, I, P]),

@@ -966,6 +966,28 @@ int bx_int8_silu_quant(const int64_t* y, const int64_t* lut, int8_t* a8, int64_t
   return launched(1);
 }
 
+int bx_int8_silu_prod(const int64_t* y, const int64_t* lut, int64_t* h, int64_t* rowmax, int64_t* scr, int N, int FFl,
+                      void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!y || !lut || !h || !rowmax || N < 0 || FFl <= 0 || FFl > SILU_THREADS * 28) return BX_EARG;
+  if (N == 0) return BX_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int ept = (FFl + SILU_THREADS - 1) / SILU_THREADS;
+  if (ept <= 4) i8::int8_silu_prod_kernel<4><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, (i64*)h, (i64*)rowmax, (i64*)scr, N, FFl);
+  else if (ept <= 16) i8::int8_silu_prod_kernel<16><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, (i64*)h, (i64*)rowmax, (i64*)scr, N, FFl);
+  else i8::int8_silu_prod_kernel<28><<<N, SILU_THREADS, 0, st>>>((const i64*)y, (const i64*)lut, (i64*)h, (i64*)rowmax, (i64*)scr, N, FFl);
+  return launched(1);
+}
+
+int bx_int8_quant_rows(const int64_t* h, const int64_t* rowmax, int8_t* a8, int64_t* mant, int64_t* e, int N, int K,
+                       void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!h || !rowmax || !a8 || N < 0 || K <= 0 || (mant && !e)) return BX_EARG;
+  if (N == 0) return BX_OK;
+  i8::int8_quant_rows_kernel<<<N, 256, 0, (cudaStream_t)stream>>>((const i64*)h, (const i64*)rowmax, a8, (i64*)mant, (i64*)e, N, K);
+  return launched(1);
+}
+
 int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e, int64_t* y,
                  int32_t* flag, int M, int N, int checked, void* stream) {
   if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;

@@ -274,6 +274,55 @@ __global__ void int8_post_kernel(const int32_t* __restrict__ c, const i64* __res
   if (checked && bad) *flag = 1;
 }
 
+// The same in two steps, for a gate / up projection sharded by output column over several GPUs: step 1 on the
+// rank's columns writes h and the row maxima of |h| (and the |silu(g)|, |u| maxima for the bound flag); the caller
+// takes the integer maximum of the row maxima over the ranks; step 2 quantises the rank's columns with the scale of
+// the FULL row. Same integers as int8_silu_kernel on the full row.
+template <int EPT>
+__global__ void __launch_bounds__(SILU_THREADS)
+int8_silu_prod_kernel(const i64* __restrict__ y, const i64* __restrict__ lut, i64* __restrict__ h,
+                      i64* __restrict__ rowmax, i64* __restrict__ scr, int M, int FF) {
+  __shared__ i64 red[33];
+  const int64_t row = blockIdx.x;
+  const i64* yr = y + row * (2 * (int64_t)FF);
+  i64 hmax = 0, smax = 0, umax = 0;
+#pragma unroll
+  for (int k = 0; k < EPT; ++k) {
+    const int c = threadIdx.x + k * SILU_THREADS;
+    if (c < FF) {
+      const i64 sg = silu_tab(yr[c], lut), u = yr[FF + c];
+      const i64 hv = rshs<FR>((i64)((u64)sg * (u64)u));
+      h[row * FF + c] = hv;
+      hmax = imax(hmax, iabs(hv));
+      smax = imax(smax, iabs(sg));
+      umax = imax(umax, iabs(u));
+    }
+  }
+  hmax = block_reduce<true>(hmax, red);
+  smax = block_reduce<true>(smax, red);
+  umax = block_reduce<true>(umax, red);
+  if (threadIdx.x == 0) {
+    rowmax[row] = hmax;
+    if (scr) {
+      atomicMax(reinterpret_cast<long long*>(scr), (long long)smax);
+      atomicMax(reinterpret_cast<long long*>(scr + 1), (long long)umax);
+    }
+  }
+}
+
+// pre_plain of the rows of h [M, K] given the maxima of the full rows: limb planes a8 [2][M][K], mant, e.
+__global__ void __launch_bounds__(256)
+int8_quant_rows_kernel(const i64* __restrict__ h, const i64* __restrict__ rowmax, int8_t* __restrict__ a8,
+                       i64* __restrict__ mant, i64* __restrict__ eo, int M, int K) {
+  const int64_t row = blockIdx.x;
+  i64 sh, as_;
+  quant_scale(rowmax[row], sh, as_);
+  const u64 inv = ~0ull / (u64)(2 * as_);
+  const int64_t plane = (int64_t)M * K;
+  for (int c = threadIdx.x; c < K; c += blockDim.x) store_limbs2(a8, plane, row * K + c, quant2(h[row * K + c], sh, as_, inv));
+  if (threadIdx.x == 0 && mant) norm24(as_, sh - FR, mant[row], eo[row]);
+}
+
 // flag |= any layer's max|silu(g)| * max|u| >= 2^62 (int64 product, wrapping like the reference's), then reset
 // (tri_fuse._flag_kernel, src/bitexact/vllm_plugin/tri_fuse.py:248-265).
 __global__ void int8_flag_end_kernel(i64* scr, int32_t* flag, int L) {

@@ -13,8 +13,18 @@ The reference is single-GPU (README "TP = 1, PP = 1"); these helpers are the new
 The collective wrappers take any process group (NCCL on GPUs; the unit tests run them on CPU tensors over gloo).
 """
 
+import contextlib
+
 import torch
 import torch.distributed as dist
+
+# Optional timing of the collectives: set TIMER to an object with a context-manager method
+# `span(name, payload_bytes)` (bench.py does, to report the per-step time of each exchange); None = no timing.
+TIMER = None
+
+
+def _span(name, nbytes):
+    return TIMER.span(name, nbytes) if TIMER is not None else contextlib.nullcontext()
 
 
 def shard_bounds(n, world, rank):
@@ -49,7 +59,8 @@ def gather_columns(y_local, group=None):
     y_local = y_local.contiguous()
     M, nl = y_local.shape
     out = torch.empty((world * M, nl), dtype=y_local.dtype, device=y_local.device)      # rank-major blocks of rows
-    dist.all_gather_into_tensor(out, y_local, group=group)
+    with _span("all_gather_columns", out.numel() * out.element_size()):
+        dist.all_gather_into_tensor(out, y_local, group=group)
     return out.view(world, M, nl).permute(1, 0, 2).reshape(M, world * nl)
 
 
@@ -61,8 +72,37 @@ def gather_rows(x_local, group=None):
     x_local = x_local.contiguous()
     out = torch.empty((world * x_local.shape[0],) + tuple(x_local.shape[1:]), dtype=x_local.dtype,
                       device=x_local.device)
-    dist.all_gather_into_tensor(out, x_local, group=group)
+    with _span("all_gather_rows", out.numel() * out.element_size()):
+        dist.all_gather_into_tensor(out, x_local, group=group)
     return out
+
+
+def gather_planes(a8, group=None):
+    """Limb planes [P, m_local, K] of every rank's rows -> [P, world * m_local, K] (rows in rank order)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return a8
+    P, m, K = a8.shape
+    return gather_rows(a8.contiguous().view(P * m, K), group).view(world, P, m, K).permute(1, 0, 2, 3).reshape(
+        P, world * m, K).contiguous()
+
+
+def gather_scaled_rows(a8, mant, e, group=None):
+    """The input of an int8-mode linear for ALL ranks' rows from each rank's own: a8 int8 [2, n, K] limb planes, mant
+    and e int64 [n] -> ([2, world n, K], [world n], [world n]) in rank order, with ONE all-gather: every row travels
+    as limb 0 | limb 1 | mant | e (2 K + 16 bytes), because at decode sizes an exchange costs its launch, not its
+    bytes."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return a8, mant, e
+    P, n, K = a8.shape
+    row = torch.cat([a8.permute(1, 0, 2).reshape(n, P * K).view(torch.uint8), mant.contiguous().view(torch.uint8).view(n, 8),
+                     e.contiguous().view(torch.uint8).view(n, 8)], 1)
+    out = gather_rows(row, group)
+    N = world * n
+    planes = out[:, :P * K].view(torch.int8).view(N, P, K).permute(1, 0, 2).contiguous()
+    tail = out[:, P * K:].contiguous().view(torch.int64).view(N, 2)
+    return planes, tail[:, 0].contiguous(), tail[:, 1].contiguous()
 
 
 def combine_argmax(best, idx, group=None):
@@ -73,7 +113,8 @@ def combine_argmax(best, idx, group=None):
         return idx
     pair = torch.stack([best, idx], 1).contiguous()                       # [M, 2] int64
     allp = torch.empty((world * pair.shape[0], 2), dtype=pair.dtype, device=pair.device)
-    dist.all_gather_into_tensor(allp, pair, group=group)
+    with _span("all_gather_argmax_pairs", allp.numel() * 8):
+        dist.all_gather_into_tensor(allp, pair, group=group)
     allp = allp.view(world, pair.shape[0], 2)
     b, i = allp[..., 0], allp[..., 1]                                     # [world, M]
     top = b.amax(0, keepdim=True)
@@ -84,7 +125,8 @@ def combine_argmax(best, idx, group=None):
 def allreduce_max(x, group=None):
     """Integer maximum over the ranks, in place (exact: no arithmetic, only comparisons)."""
     if dist.get_world_size(group) > 1:
-        dist.all_reduce(x, op=dist.ReduceOp.MAX, group=group)
+        with _span("all_reduce_max", x.numel() * x.element_size()):
+            dist.all_reduce(x, op=dist.ReduceOp.MAX, group=group)
     return x
 
 
@@ -242,3 +284,128 @@ class ShardedHeadInt8:
                                  best.data_ptr(), idx.data_ptr(), M, Vl, self.v0, 16, nv.stream())
         nv.check(rc, "bx_sample_shard")
         return combine_argmax(best, idx, self.group)
+
+
+class ShardedMLPInt8:
+    """Column-sharded MLP of one int8-mode layer: rank r holds intermediate columns [f0, f1) of gate and up (int8
+    weight rows and their channel multipliers) and output columns [d0, d1) of down. As in exact mode, the SiLU
+    product is quantised per FULL row: the shards' row maxima of |h| meet in an integer all-reduce MAX between
+    `bx_int8_silu_prod` and `bx_int8_quant_rows` (the reference's one-kernel form: `tri_mlp.silu_quant`,
+    src/bitexact/vllm_plugin/tri_mlp.py:153-183 = int8/segs.py:111-118), then two all-gathers rebuild the rows: the
+    int8 limb planes of the quantised shard, and the int64 down outputs. Nothing is summed across ranks."""
+
+    def __init__(self, c, layer, FF, device, group=None, nl=2):
+        self.group, self.FF = group, FF
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.f0, self.f1 = column_bounds(FF, self.world, self.rank, 16)
+        w, m = c[f"{layer}.wgu"], c[f"{layer}.wgu.m"]
+        rows = torch.cat([torch.arange(self.f0, self.f1), torch.arange(FF + self.f0, FF + self.f1)])
+        self.wgu = w[rows.to(w.device)].to(device).contiguous()
+        self.mgu = m[rows.to(m.device)].to(device).contiguous()
+        self.fm_gu = int(c[f"{layer}.wgu.fm"]) + 8 * (nl - 1) - 24
+        wd = c[f"{layer}.wd"]
+        self.d0, self.d1 = column_bounds(wd.shape[0], self.world, self.rank)
+        self.wd = wd[self.d0:self.d1].to(device).contiguous()
+        self.md = c[f"{layer}.wd.m"][self.d0:self.d1].to(device).contiguous()
+        self.fm_d = int(c[f"{layer}.wd.fm"]) + 8 * (nl - 1) - 24
+
+    def __call__(self, a8, mant, e, silu_t, flag, scr=None):
+        """(a8 int8 [2 M, D] limb planes, mant, e [M]): the normalised input of ALL rows, identical on every rank ->
+        the down projection's output y int64 [M, D] at 16 bits, identical on every rank. scr int64 [2]: receives the
+        rank's maxima of |silu(gate)| and |up| (the caller takes their maximum over the ranks before `flag_end`)."""
+        from . import _native as nv
+        from .int8.gemm_skinny import linear_post
+        lib, dev = nv.lib(), a8.device
+        M = mant.shape[0]
+        FFl = self.f1 - self.f0
+        y = linear_post(a8, self.wgu, self.mgu, self.fm_gu, mant, e, flag, True)          # [M, 2 FFl]
+        h = torch.empty(M, FFl, dtype=torch.long, device=dev)
+        rmax = torch.empty(M, dtype=torch.long, device=dev)
+        nv.check(lib.bx_int8_silu_prod(y.data_ptr(), silu_t.data_ptr(), h.data_ptr(), rmax.data_ptr(), nv.ptr(scr), M,
+                                       FFl, nv.stream()), "bx_int8_silu_prod")
+        allreduce_max(rmax, self.group)
+        al = torch.empty(2, M, FFl, dtype=torch.int8, device=dev)
+        mant2 = torch.empty(M, dtype=torch.long, device=dev)
+        e2 = torch.empty(M, dtype=torch.long, device=dev)
+        nv.check(lib.bx_int8_quant_rows(h.data_ptr(), rmax.data_ptr(), al.data_ptr(), mant2.data_ptr(), e2.data_ptr(), M,
+                                        FFl, nv.stream()), "bx_int8_quant_rows")
+        af = gather_columns(al.view(2 * M, FFl), self.group).contiguous()                   # [2 M, FF]: all of K
+        return gather_columns(linear_post(af, self.wd, self.md, self.fm_d, mant2, e2, flag, True), self.group)
+
+
+class ColumnShardedIntEngine:
+    """int8 mode over `world` GPUs with BOTH shardings of the 8-GPU configuration: every rank owns a block of the
+    sequences (its KV cache, attention, the attention-side linears and every row-local stage), while the MLP and the
+    LM head + sampler run on ALL ranks' rows with the weights split by output column. Per layer: one all-gather of the
+    normalised rows (int8 limb planes + row scales), the exchanges of `ShardedMLPInt8`, and each rank keeps its own
+    rows of the result; per step one more row gather in front of the column-sharded head. Every rank must hold the
+    same number of rows. Same integers as `IntEngine` on one GPU."""
+
+    def __init__(self, c, dev, group=None):
+        from .int8.engine import IntEngine
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.base = IntEngine(c, dev)
+        b = self.base
+        FF = c["0.wgu"].shape[0] // 2
+        self.mlps = [ShardedMLPInt8(c, i, FF, dev, group) for i in range(b.L)]
+        self.head = ShardedHeadInt8(c, dev, group)
+        self.sharded = True          # False: every call runs on this rank alone (prompt processing: the ranks' row
+        #                              counts differ from chunk to chunk, and the column exchange needs equal blocks)
+        for a in ("dev", "D", "H", "HKV", "HD", "L", "FR", "ln", "fl", "emb", "V"):
+            setattr(self, a, getattr(b, a))
+
+    def check(self):
+        self.base.check()
+
+    def _rows(self, x):
+        n = x.shape[0] // self.world
+        return x[self.rank * n:(self.rank + 1) * n]
+
+    def forward(self, kvs, ids, pos, slot, bt, rmap, tiles=None):
+        """IntEngine.forward on this rank's rows, the MLP of every layer column-sharded over all ranks' rows
+        (with `sharded` off, or for prompt tiles: the plain single-GPU forward with this rank's full weights)."""
+        from .vllm_plugin import tri_fuse as fz
+        from .vllm_plugin import tri_paged
+        b = self.base
+        if not self.sharded or tiles is not None:
+            return b.forward(kvs, ids, pos, slot, bt, rmap, tiles=tiles)
+        N, G = ids.shape[0], b.H // b.HKV
+        pos = pos.long()
+        slot = torch.where(slot < 0, torch.zeros_like(slot), slot).long()
+        qpos = pos.view(-1, 1).expand(-1, G).contiguous()
+        x, *pre = fz.embed_norm(b, ids, b.layers[0]["ga"])
+        for i in range(b.L):
+            ly = b.layers[i]
+            q = fz.qkv(b, b._lin(pre, ly["wqkv"]), None, None, None, pos, slot, kvs[i])
+            num, den = tri_paged.attend(q, qpos, kvs[i], bt, b.ptab, rmap=rmap)
+            x, a8, mant, e = fz.add_norm(b, b._lin(fz.attn_out(b, num, den), ly["wo"]), None, None, None, x, ly["gm"])
+            A, Ma, Ea = gather_scaled_rows(a8.view(2, N, b.D), mant, e, self.group)
+            y = self.mlps[i](A.view(2 * N * self.world, b.D), Ma, Ea, b.silu_t, b.fl, b.scr[i])
+            nxt = b.layers[i + 1]["ga"] if i + 1 < b.L else None
+            x, *pre = fz.add_norm(b, self._rows(y).contiguous(), None, None, None, x, nxt)
+        allreduce_max(b.scr, self.group)                     # the product-bound maxima of every rank's columns
+        fz.flag_end(b, b.scr)
+        return x
+
+    def sample(self, h, rows_all):
+        """Final residual rows of this rank [n, D] and the sampler rows (seed, t, tn, td) of ALL ranks' rows
+        [world n, 4] -> the tokens of this rank's rows (LM head and sampler column-sharded over all rows)."""
+        from .vllm_plugin import tri_fuse as fz
+        b = self.base
+        a8, mant, e = fz.pre_norm(b, h, b.gf)
+        n = h.shape[0]
+        A, Ma, Ea = gather_scaled_rows(a8.view(2, n, b.D), mant, e, self.group)
+        tok = self.head.sample(A.view(2 * n * self.world, b.D), Ma, Ea, b.fl, rows_all, b.ln)
+        return self._rows(tok)
+
+    def logits(self, h):
+        """Full logits rows of this rank's rows (gathers the vocabulary shards: test / hashing mode)."""
+        from .vllm_plugin import tri_fuse as fz
+        b = self.base
+        if not self.sharded:
+            return b.logits(h)
+        a8, mant, e = fz.pre_norm(b, h, b.gf)
+        n = h.shape[0]
+        A, Ma, Ea = gather_scaled_rows(a8.view(2, n, b.D), mant, e, self.group)
+        return self._rows(self.head.full_logits(A.view(2 * n * self.world, b.D), Ma, Ea, b.fl))

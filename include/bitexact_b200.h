@@ -277,6 +277,18 @@ int bx_int8_silu_quant(const int64_t* y, const int64_t* lut, int8_t* a8, int64_t
                        int N, int FF, void* stream);
 int bx_int8_flag_end(int64_t* scr, int32_t* flag, int L, void* stream);
 
+/* h = rsh(silu_table(gate) * up, 16) and pre_plain(h) in two steps, for a gate / up projection sharded by output column
+ * over several GPUs (the reference is single-GPU; same integers as tri_mlp.silu_quant,
+ * src/bitexact/vllm_plugin/tri_mlp.py:153-183, on the full row). bx_int8_silu_prod: y int64 [N, 2 FFl] (the rank's gate
+ * columns, then its up columns) -> h int64 [N, FFl] and rowmax int64 [N] = max |h| over the rank's columns; scr as in
+ * bx_int8_silu_quant. The caller takes the integer maximum of rowmax (and of scr) over the ranks.
+ * bx_int8_quant_rows: pre_plain of the rows of h [N, K] with the maxima of the full rows: limb planes a8 [2][N][K] and
+ * (mant, e) int64 [N] (may be NULL: every rank computes the same values). */
+int bx_int8_silu_prod(const int64_t* y, const int64_t* lut, int64_t* h, int64_t* rowmax, int64_t* scr, int N, int FFl,
+                      void* stream);
+int bx_int8_quant_rows(const int64_t* h, const int64_t* rowmax, int8_t* a8, int64_t* mant, int64_t* e, int N, int K,
+                       void* stream);
+
 /* segs.post on a raw bx_int8_mm output (src/bitexact/int8/segs.py:62-67): c int32 [>= 2 M, N] -> y int64 [M, N].
  * For callers that keep the reference's two-step int_mm + post form; bx_int8_linear_post does both in one kernel. */
 int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e, int64_t* y,

@@ -4,6 +4,8 @@
     python microbench.py gemmr [--m 256] [--iters 10]
     python microbench.py attn [--batch 256] [--ctx 4128] [--iters 10]
     python microbench.py stages [--batch 256] [--iters 10]
+    python microbench.py prefill [--batch 4] [--ctx 2048] [--iters 10]
+    python microbench.py prompt [--batch 4] [--ctx 2048] [--chunk 4096] [--iters 3]
 
 gemm: the exact-mode fused linear on the projection shapes of one Llama-3.2-1B layer and the LM head
       (int8-equivalent ops = 2 * 9 * M * N * K; algorithmic bytes = 3 N K + 4 M K + 8 M N).
@@ -180,6 +182,93 @@ def attn(args):
     return rec
 
 
+def prefill(args):
+    """Prefill attention of whole prompts, Llama-3.2-1B geometry (8 KV heads x 4 query heads, head_dim 64, 16-token
+    pages): --batch prompts of --ctx tokens each through the tile kernel and, for comparison, through the per-row
+    decode kernel (every token a row). Algorithmic int8 ops = 2 products x 2 * 9 * (S^2 / 2) * H * HD per prompt."""
+    from bitexact_llm_b200.exact.consts import exp2_table
+    from bitexact_llm_b200.vllm_plugin import tri_exact_attn, tri_prefill
+    dev = "cuda"
+    R, S, HKV, G, HD, bs = args.batch, args.ctx, 8, 4, 64, 16
+    gen = torch.Generator(device=dev).manual_seed(0)
+    nblk = (S + bs - 1) // bs
+    nb = 1 + R * nblk
+    cache = torch.randint(-128, 128, (nb, HKV, bs, 8 * HD), dtype=torch.int8, device=dev, generator=gen)
+    bt = (1 + torch.randperm(nb - 1, device=dev, generator=gen)).view(R, nblk).to(torch.int32)
+    N = R * S
+    q = torch.randint(-(1 << 22), (1 << 22) + 1, (N, HKV, G, HD), dtype=torch.int32, device=dev, generator=gen)
+    sh = torch.randint(-30, -20, (N, HKV, G), device=dev, generator=gen)
+    pos = torch.arange(S, device=dev).repeat(R)
+    req = torch.arange(R, device=dev).repeat_interleave(S)
+    tiles = tri_prefill.tile_table([(r, r * S, S, S) for r in range(R)], G).to(dev)
+    lut = exp2_table(dev)
+    num = torch.zeros(N, HKV, G, HD, dtype=torch.long, device=dev)
+    den = torch.ones(N, HKV, G, 1, dtype=torch.long, device=dev)
+    qpos = pos[:, None].expand(N, G).contiguous()
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.iters
+
+    ms_tile = timed(lambda: tri_prefill.attend_exact(q, sh, pos, cache, bt, tiles, lut, 387270501, num, den))
+    n2, d2 = tri_exact_attn.attend(q, sh, qpos, cache, bt, req, lut, 387270501)
+    if not (torch.equal(num, n2) and torch.equal(den, d2)):
+        raise SystemExit("tile kernel differs from the per-row kernel")
+    ms_row = timed(lambda: tri_exact_attn.attend(q, sh, qpos, cache, bt, req, lut, 387270501))
+    ops = R * 2.0 * 18.0 * (S * (S + 1) / 2.0) * HKV * G * HD
+    rec = {"kernel": "prefill_attention", "prompts": R, "S": S, "tiles": int(tiles.shape[0]), "us": ms_tile * 1e3,
+           "int8_tops": ops / ms_tile / 1e9, "tokens_per_s_one_layer": N / ms_tile * 1e3,
+           "per_row_kernel_us": ms_row * 1e3, "speedup_vs_rows": ms_row / ms_tile}
+    print(json.dumps(rec), flush=True)
+    return rec
+
+
+def prompt(args):
+    """Prompt processing of the whole model (random-init Llama-3.2-1B, exact mode): --batch prompts of --ctx tokens
+    through `Session.prefill`, with the tile kernel and with every token as a row of the decode kernel."""
+    from bitexact_llm_b200.decode import Session
+    from bitexact_llm_b200.exact import consts
+    from bitexact_llm_b200.vllm_plugin.exact_run import ExactEngine
+    dev = torch.device("cuda")
+    cfg = dict(consts.LLAMA_1B)
+    c = consts.build(cfg, consts.random_state_dict(cfg, seed=0, device=dev), n_pos=args.ctx + 64)
+    eng = ExactEngine(c, dev)
+    del c
+    g = torch.Generator().manual_seed(1)
+    prompts = torch.randint(0, cfg["vocab_size"], (args.batch, args.ctx), generator=g)
+    out = {}
+    for tiles in (True, False):
+        times, last = [], None
+        for _ in range(1 + args.iters):
+            ses = Session(eng, args.batch, args.ctx + 16)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            last = ses.prefill(prompts, chunk_rows=args.chunk, tiles=tiles)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            del ses
+        out[tiles] = (min(times[1:]), last)
+    eng.check()
+    if not torch.equal(out[True][1], out[False][1]):
+        raise SystemExit("prefill with tiles differs from prefill by rows")
+    toks = args.batch * args.ctx
+    rec = {"what": "prompt processing, 16 layers", "prompts": args.batch, "S": args.ctx, "chunk_rows": args.chunk,
+           "ms_tiles": out[True][0], "tok_per_s_tiles": toks / out[True][0] * 1e3, "ms_rows": out[False][0],
+           "tok_per_s_rows": toks / out[False][0] * 1e3}
+    print(json.dumps(rec), flush=True)
+    return rec
+
+
 def _graph_time(run, nsets, iters, reps=4):
     """Mean device time of one call: `reps` rounds over `nsets` input sets captured in one CUDA graph (no host gaps;
     the sets together exceed L2, so every call reads its inputs from HBM)."""
@@ -254,7 +343,7 @@ def stages(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemmr", "attn", "stages"])
+    ap.add_argument("what", choices=["gemm", "gemmr", "attn", "stages", "prefill", "prompt"])
     ap.add_argument("--m", default="1,16,256,4096")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -265,8 +354,9 @@ def main():
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-scratch", action="store_true", help="attn: no scratch buffer (long contexts: cluster kernels)")
     ap.add_argument("--fixed", action="store_true", help="attn: every request has exactly --ctx keys")
+    ap.add_argument("--chunk", type=int, default=4096, help="prompt: token rows per forward call")
     args = ap.parse_args()
-    {"gemm": gemm, "gemmr": gemmr, "attn": attn, "stages": stages}[args.what](args)
+    {"gemm": gemm, "gemmr": gemmr, "attn": attn, "stages": stages, "prefill": prefill, "prompt": prompt}[args.what](args)
     if nv.device_status() != 0:
         raise SystemExit("device-side wait timed out")
 

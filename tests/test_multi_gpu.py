@@ -108,3 +108,83 @@ def test_ranks_nccl():
     for p in procs:
         p.join(timeout=600)
     assert all(p.exitcode == 0 for p in procs) and dict(ret) == {r: True for r in range(world)}
+
+
+# ---- BASELINE config 5: int8 mode, sequences sharded over the ranks, MLP and LM head + sampler sharded by column ----
+
+def _config5_worker(rank, world, port, order, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import hashlib
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        from bitexact_llm_b200 import parallel as par
+        from bitexact_llm_b200.decode import Session
+        from bitexact_llm_b200.exact import consts
+        from bitexact_llm_b200.int8 import consts as consts8
+        dev = torch.device("cuda", rank)
+        cfg = dict(consts.LLAMA_1B)
+        cfg["num_hidden_layers"] = 1
+        c = consts8.build(cfg, consts.random_state_dict(cfg, seed=3, device=dev), n_pos=4200)
+        eng = par.ColumnShardedIntEngine(c, dev)
+        per = len(order) // world
+        mine = order[rank * per:(rank + 1) * per]
+        # sequence s: its own seeded prompt (length U[16, 4096] for a few, short for the rest) and sampler key s
+        rng = [np.random.RandomState(1000 + s) for s in mine]
+        lens = [int(r.randint(16, 4097)) if s % 8 == 0 else int(r.randint(16, 200)) for r, s in zip(rng, mine)]
+        P = max(lens)
+        ids = torch.zeros(per, P, dtype=torch.long)
+        for b, (r, n) in enumerate(zip(rng, lens)):
+            ids[b, :n] = torch.from_numpy(r.randint(0, cfg["vocab_size"], n))
+        ses = Session(eng, per, 4200)
+        eng.sharded = False                                     # prompts: every rank on its own
+        h = ses.prefill(ids, torch.tensor(lens), chunk_rows=2048)
+        eng.sharded = True
+        rows_all = torch.zeros(len(order), 4, dtype=torch.long, device=dev)
+        rows_all[:, 0] = torch.tensor(order, device=dev)
+        rows_all[:, 2], rows_all[:, 3] = 7, 10
+        out = {s: [] for s in mine}
+        for t in range(3):
+            lg = eng.logits(h)                                  # test mode: the gathered rows, for the hashes
+            tok = eng.sample(h, rows_all)
+            for b, s in enumerate(mine):
+                out[s].append((hashlib.sha256(lg[b].cpu().numpy().tobytes()).hexdigest(), int(tok[b])))
+            rows_all[:, 1] += 1
+            h = ses.step(tok)
+        eng.check()
+        ret[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def _config5_run(world, order, port):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_config5_worker, args=(r, world, port, order, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=900)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    merged = {}
+    for r in range(world):
+        merged.update(ret[r])
+    return merged
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_config5_int8_column_sharded_decode_is_identical_at_every_gpu_count_and_order():
+    """One int8-mode decoder layer + LM head at Llama-3.2-1B geometry, 16 sequences with mixed prompt lengths (two of
+    them drawn from U[16, 4096]): per-step logits hashes and T = 0.7 tokens of every sequence are the same on 1 GPU
+    and on 2 / 4 / 8 GPUs with the MLP and the LM head + sampler sharded by column, and under a permuted batch."""
+    order = list(range(16))
+    port = 29900 + os.getpid() % 1000
+    want = _config5_run(1, order, port)
+    worlds = [w for w in (2, 4, 8) if w <= torch.cuda.device_count()]
+    for i, w in enumerate(worlds):
+        assert _config5_run(w, order, port + 1 + i) == want, w
+    perm = [int(v) for v in np.random.RandomState(5).permutation(16)]
+    assert _config5_run(worlds[-1], perm, port + 9) == want

@@ -73,6 +73,14 @@ def _worker(rank, world, port, ret):
         rows = par.gather_rows(torch.arange(lo, lo + 5))                   # equal-size blocks gather in rank order
         ok = ok and rows.tolist() == [*range(0, 5), *range(par.shard_bounds(11, world, 1)[0],
                                                             par.shard_bounds(11, world, 1)[0] + 5)]
+        # packed row exchange of an int8-mode linear input: planes + row scales in one all-gather
+        a8 = torch.from_numpy(rng.randint(-128, 128, (2, 3, 8)).astype(np.int8)) + rank
+        mant = torch.arange(3) + 100 * rank + (1 << 40)
+        ee = -torch.arange(3) - 7 * rank
+        A, Mg, Eg = par.gather_scaled_rows(a8, mant, ee)
+        want_a = torch.cat([a8 - rank + r for r in range(world)], 1)
+        ok = ok and torch.equal(A, want_a) and Mg.tolist() == [v + 100 * r + (1 << 40) for r in range(world) for v in range(3)]
+        ok = ok and Eg.tolist() == [-v - 7 * r for r in range(world) for v in range(3)]
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
