@@ -54,6 +54,15 @@ _SIGNATURES = {
     "bx_int8_quant_rows": (I, [P, P, P, P, P, I, I, P]),
     "bx_int8_post": (I, [P, P, L, P, P, P, P, I, I, I, P]),
     "bx_pcg_raw": (I, [P, P, I, I, P]),
+    "bx_pcg_seed_state": (I, [P, P, I, P]),
+    "bx_pcg_raw_from_state": (I, [P, P, I, I, P]),
+    "bx_exact_rms": (I, [P, P, P, P, I, I, P]),
+    "bx_exact_ndiv": (I, [P, P, P, P, P, P, I, I, P]),
+    "bx_rowmax_abs": (I, [P, P, I, I, P]),
+    "bx_exact_rope": (I, [P, P, P, P, P, P, P, I, I, I, I, P]),
+    "bx_softmax_w": (I, [P, P, P, P, P, L, P, P, P, I, I, P]),
+    "bx_exact_attn_div": (I, [P, P, P, I, I, P]),
+    "bx_int8_post_acc": (I, [P, P, L, P, P, P, P, I, I, I, P]),
     "bx_exact_silu_prod": (I, [P, P, P, P, P, I, I, P]),
     "bx_exact_quant_rows": (I, [P, P, I, P, L, P, P, L, I, I, P]),
     "bx_bmm": (I, [P, I, P, I, P, I, I, I, I, L, L, L, L, L, L, P]),

@@ -21,6 +21,7 @@
 #include "logp.cuh"
 #include "decompose.cuh"
 #include "unfused.cuh"
+#include "unfused_stages.cuh"
 #include "peak_probe.cuh"
 
 namespace {
@@ -1176,6 +1177,100 @@ int bx_exact_quant_rows(const int64_t* P, const int64_t* rowmax, int fbits, int3
   if (N == 0) return BX_OK;
   quant_rows_kernel<<<N, 256, 0, (cudaStream_t)stream>>>((const i64*)P, (const i64*)rowmax, fbits, q, ldq, (i64*)sh, a8,
                                                          plane, K);
+  return launched(1);
+}
+
+// ---- stages of the reference's standalone engine, one kernel each (unfused_stages.cuh) ----
+int bx_exact_rms(const int64_t* x, int64_t* r, int64_t* er, int64_t* amax, int M, int D, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!x || !r || !er || M < 0 || D < 1 || D > 4096 || (D & (D - 1))) return BX_EARG;
+  if (M == 0) return BX_OK;
+  int lg = 0;
+  while ((1 << lg) < D) ++lg;
+  rms_kernel<<<M, US_THREADS, 0, (cudaStream_t)stream>>>((const i64*)x, (i64*)r, (i64*)er, (i64*)amax, D, lg);
+  return launched(1);
+}
+
+int bx_exact_ndiv(const int64_t* x, const int64_t* gm, const int64_t* ge, const int64_t* r, const int64_t* er,
+                  int64_t* P, int M, int D, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!x || !gm || !ge || !r || !er || !P || M < 0 || D < 1) return BX_EARG;
+  if (M == 0) return BX_OK;
+  ndiv_kernel<<<M, US_THREADS, 0, (cudaStream_t)stream>>>((const i64*)x, (const i64*)gm, (const i64*)ge, (const i64*)r,
+                                                        (const i64*)er, (i64*)P, D);
+  return launched(1);
+}
+
+int bx_rowmax_abs(const int64_t* P, int64_t* rowmax, int M, int K, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!P || !rowmax || M < 0 || K < 1) return BX_EARG;
+  if (M == 0) return BX_OK;
+  rowmax_abs_kernel<<<M, US_THREADS, 0, (cudaStream_t)stream>>>((const i64*)P, (i64*)rowmax, K);
+  return launched(1);
+}
+
+int bx_exact_rope(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos, int64_t* Pq, int64_t* k,
+                  int64_t* v, int N, int H, int HKV, int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!y || !cos || !sin || !pos || !Pq || !k || !v || N < 0 || H <= 0 || HKV <= 0 || HD <= 0 || HD % 2) return BX_EARG;
+  if (N == 0) return BX_OK;
+  rope_kernel<<<N, US_THREADS, 0, (cudaStream_t)stream>>>((const i64*)y, (const i64*)cos, (const i64*)sin,
+                                                        (const i64*)pos, (i64*)Pq, (i64*)k, (i64*)v, H, HKV, HD);
+  return launched(1);
+}
+
+int bx_softmax_w(const int64_t* raw, const uint8_t* ok, const int64_t* qpos, const int64_t* sh, const int64_t* lut,
+                 int64_t l2e, const int32_t* ptab, int32_t* p, int64_t* den, int R, int S, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!raw || !p || !den || R < 0 || S < 1 || (!ok && !qpos)) return BX_EARG;
+  if (!ptab && (!sh || !lut)) return BX_EARG;
+  if (R == 0) return BX_OK;
+  AttnParams w{};
+  w.lut = (const i64*)lut;
+  w.l2e = (i64)l2e;
+  w.ptab = ptab;
+  softmax_w_kernel<<<R, US_THREADS, 0, (cudaStream_t)stream>>>((const i64*)raw, ok, (const i64*)qpos,
+                                                             ptab ? nullptr : (const i64*)sh, w, p, (i64*)den, S);
+  return launched(1);
+}
+
+int bx_exact_attn_div(const int64_t* num, const int64_t* den, int64_t* o, int Z, int HD, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!num || !den || !o || Z < 0 || HD < 1) return BX_EARG;
+  if (Z == 0) return BX_OK;
+  attn_div_kernel<<<Z, US_THREADS, 0, (cudaStream_t)stream>>>((const i64*)num, (const i64*)den, (i64*)o, HD);
+  return launched(1);
+}
+
+int bx_int8_post_acc(const int64_t* acc, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e,
+                     int64_t* y, int32_t* flag, int M, int N, int checked, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!acc || !mul || !mant || !e || !y || !flag || M < 0 || N <= 0) return BX_EARG;
+  if (M == 0) return BX_OK;
+  const int64_t total = (int64_t)M * N;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  i8::int8_post_acc_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const i64*)acc, (const i64*)mul, (i64)fmsh,
+                                                                   (const i64*)mant, (const i64*)e, (i64*)y, flag, M, N,
+                                                                   checked);
+  return launched(1);
+}
+
+int bx_pcg_seed_state(const int64_t* keys, int64_t* st, int n, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!keys || !st || n < 0) return BX_EARG;
+  if (n == 0) return BX_OK;
+  pcg_seed_state_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const i64*)keys, (i64*)st, n);
+  return launched(1);
+}
+
+int bx_pcg_raw_from_state(const int64_t* st, int64_t* out, int n, int V, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (!st || !out || n < 0 || V <= 0) return BX_EARG;
+  if (n == 0) return BX_OK;
+  const int run = 16;
+  const int blocks = (V + run * SAMPLE_THREADS - 1) / (run * SAMPLE_THREADS);
+  pcg_raw_state_kernel<<<dim3(blocks, n), SAMPLE_THREADS, 0, (cudaStream_t)stream>>>((const i64*)st, (i64*)out, V, run);
   return launched(1);
 }
 

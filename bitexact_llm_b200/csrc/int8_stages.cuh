@@ -274,6 +274,21 @@ __global__ void int8_post_kernel(const int32_t* __restrict__ c, const i64* __res
   if (checked && bad) *flag = 1;
 }
 
+// segs.post on the joined accumulator acc = c0 + (c1 << 8) as int64 [M, N] (the form the reference's `post` takes).
+__global__ void int8_post_acc_kernel(const i64* __restrict__ acc, const i64* __restrict__ mul, i64 fmsh,
+                                     const i64* __restrict__ mant, const i64* __restrict__ e, i64* __restrict__ y,
+                                     int32_t* flag, int M, int N, int checked) {
+  const int64_t total = (int64_t)M * N;
+  bool bad = false;
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = t / N, n = t % N;
+    const i64 tv = rsh_t((i64)((u64)acc[t] * (u64)mul[n]), fmsh);
+    bad |= iabs(tv) >= (1ll << 38);
+    y[t] = rsh_t((i64)((u64)tv * (u64)mant[m]), 8 - e[m]);
+  }
+  if (checked && bad) *flag = 1;
+}
+
 // The same in two steps, for a gate / up projection sharded by output column over several GPUs: step 1 on the
 // rank's columns writes h and the row maxima of |h| (and the |silu(g)|, |u| maxima for the bound flag); the caller
 // takes the integer maximum of the row maxima over the ranks; step 2 quantises the rank's columns with the scale of

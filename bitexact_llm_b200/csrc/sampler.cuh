@@ -170,6 +170,35 @@ pcg_raw_kernel(const i64* __restrict__ keys, i64* __restrict__ out, int V, int r
   for (int64_t e = e0; e < e1; ++e) out[row * V + e] = (i64)pcg_next(st, inc);
 }
 
+// The generator state after numpy's seeding, as gpu_pcg.seed_state lays it out: st int64 [n, 4] = state hi, state lo,
+// increment hi, increment lo.
+__global__ void pcg_seed_state_kernel(const i64* __restrict__ keys, i64* __restrict__ st, int n) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  u128 state, inc;
+  pcg_seed((u64)keys[2 * r], (u64)keys[2 * r + 1], state, inc);
+  st[4 * r] = (i64)state.hi;
+  st[4 * r + 1] = (i64)state.lo;
+  st[4 * r + 2] = (i64)inc.hi;
+  st[4 * r + 3] = (i64)inc.lo;
+}
+
+// Raw words from given generator states (gpu_pcg.raw_from_state): st int64 [n, 4] -> out int64 [n, V].
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+pcg_raw_state_kernel(const i64* __restrict__ stv, i64* __restrict__ out, int V, int run) {
+  const int64_t row = blockIdx.y;
+  const int64_t e0 = ((int64_t)blockIdx.x * SAMPLE_THREADS + threadIdx.x) * run;
+  if (e0 >= V) return;
+  u128 st, inc;
+  st.hi = (u64)stv[4 * row];
+  st.lo = (u64)stv[4 * row + 1];
+  inc.hi = (u64)stv[4 * row + 2];
+  inc.lo = (u64)stv[4 * row + 3];
+  st = pcg_advance(st, inc, (u64)e0);
+  const int64_t e1 = e0 + run < V ? e0 + run : V;
+  for (int64_t e = e0; e < e1; ++e) out[row * V + e] = (i64)pcg_next(st, inc);
+}
+
 // Chunked sampling pass. rows: int64 [M, 4] = seed, t, tn, td (tn == 0: greedy). Each CTA handles vocabulary
 // entries [chunk * ch, chunk * ch + ch) of one row and writes its (max value, first index) pair.
 // Thread t takes entries c0 + t, c0 + t + 256, ...: a warp reads 32 consecutive logits, and the generator of the

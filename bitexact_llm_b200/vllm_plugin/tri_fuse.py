@@ -101,6 +101,22 @@ def silu_quant(m, c, lin, mant, e, lut, scr=None):
     return q, mant2, e2, ((scr[0] * scr[1] >= 1 << 62) if own else None)
 
 
-def flag_end(m, scr):
-    """Multiply the per-layer maxima collected in scr [L, 2] into the bound flag and clear them."""
+def scratch(m):
+    """The model's per-layer maxima buffer int64 [L, 2] (created on first use, like the reference's `m._scr`)."""
+    if getattr(m, "scr", None) is None:
+        m.scr = torch.zeros(m.L, 2, dtype=torch.long, device=m.dev)
+    return m.scr
+
+
+def mlp_mid(m, ly, c, mant, e, layer):
+    """`tri_mlp.silu_quant` on the raw gate / up GEMM output c of layer `layer`, the product-bound maxima into the
+    model's scratch row -> (limbs, mant, e) (src/bitexact/vllm_plugin/tri_fuse.py:243-245). ly["wgu"] = (w, m, fmsh)."""
+    from . import tri_mlp
+    return tri_mlp.silu_quant(c, ly["wgu"][1], ly["wgu"][2], mant, e, m.silu_t, False, scr=scratch(m)[layer])[:3]
+
+
+def flag_end(m, scr=None):
+    """Multiply the per-layer maxima collected in the model's scratch (or the given scr [L, 2]) into the bound flag
+    m.fl and clear them (src/bitexact/vllm_plugin/tri_fuse.py:248-265: `flag_end(m)`)."""
+    scr = scratch(m) if scr is None else scr
     nv.check(nv.lib().bx_int8_flag_end(scr.data_ptr(), m.fl.data_ptr(), scr.shape[0], nv.stream()), "bx_int8_flag_end")

@@ -309,6 +309,38 @@ int bx_exact_epilogue(const int64_t* T, const int64_t* B, const int32_t* q, int6
                       const int32_t* ec, const int64_t* ev, int R, const int64_t* d, const int64_t* g,
                       const int64_t* sh, int64_t* y, int32_t* flag, int M, int N, int checked, void* stream);
 
+/* ---- stages of the standalone exact engine, one kernel each ------------------------------------------------------
+ * The serving path fuses these into bx_exact_norm / bx_exact_qkv / bx_exact_attention / bx_exact_attn_out; the
+ * separate forms keep code written against bitexact.exact.segs and bitexact.exact.ops running stage by stage.
+ *   bx_exact_rms       ops.rms (src/bitexact/exact/ops.py:92-105): x int64 [M, D] (D a power of two <= 4096) ->
+ *                      r, er int64 [M] with sqrt(mean(x^2) + 1e-5) = r 2^er; amax (may be NULL) = max |x| per row.
+ *   bx_exact_ndiv      segs.ndiv (src/bitexact/exact/segs.py:49-51): P = div_round(x gm, ge - 24 - er + 40, r).
+ *   bx_rowmax_abs      max |P| per row: with bx_exact_quant_rows it is ops.quant (exact/ops.py:82-89).
+ *   bx_exact_rope      segs.rope_y (exact/segs.py:78-87) without the quantisation: y int64 [N, (H + 2 HKV) HD] ->
+ *                      Pq int64 [N, H, HD] at 54 bits, k [N, HKV, HD] at 17 bits, v [N, HKV, HD] at 19 bits.
+ *   bx_softmax_w       ops.softmax_w (exact/ops.py:133-143) on dense scores raw int64 [R, S]: key s of row r takes
+ *                      part iff ok[r, s] != 0 (ok uint8 [R, S]) or, with ok NULL, s <= qpos[r]; sh int64 [R] row
+ *                      exponents, lut / l2e as bx_exact_attention; with ptab the int8-mode rule
+ *                      (int8/segs.py:91-99). p int32 [R, S] (0 where masked), den int64 [R].
+ *   bx_exact_attn_div  segs.attn_div (exact/segs.py:108-113): o[z, :] = div_round(num[z, :], 5, den[z]), num int64 [Z, HD].
+ *   bx_int8_post_acc   segs.post (int8/segs.py:62-67) on the joined accumulator acc int64 [M, N].
+ *   bx_pcg_seed_state / bx_pcg_raw_from_state   gpu_pcg.seed_state / raw_from_state
+ *                      (src/bitexact/vllm_plugin/gpu_pcg.py:44-52, 94-104): keys int64 [n, 2] -> st int64 [n, 4]
+ *                      (state hi, lo, increment hi, lo after numpy's seeding); st -> raw words int64 [n, V]. */
+int bx_exact_rms(const int64_t* x, int64_t* r, int64_t* er, int64_t* amax, int M, int D, void* stream);
+int bx_exact_ndiv(const int64_t* x, const int64_t* gm, const int64_t* ge, const int64_t* r, const int64_t* er,
+                  int64_t* P, int M, int D, void* stream);
+int bx_rowmax_abs(const int64_t* P, int64_t* rowmax, int M, int K, void* stream);
+int bx_exact_rope(const int64_t* y, const int64_t* cos, const int64_t* sin, const int64_t* pos, int64_t* Pq, int64_t* k,
+                  int64_t* v, int N, int H, int HKV, int HD, void* stream);
+int bx_softmax_w(const int64_t* raw, const uint8_t* ok, const int64_t* qpos, const int64_t* sh, const int64_t* lut,
+                 int64_t l2e, const int32_t* ptab, int32_t* p, int64_t* den, int R, int S, void* stream);
+int bx_exact_attn_div(const int64_t* num, const int64_t* den, int64_t* o, int Z, int HD, void* stream);
+int bx_int8_post_acc(const int64_t* acc, const int64_t* mul, int64_t fmsh, const int64_t* mant, const int64_t* e,
+                     int64_t* y, int32_t* flag, int M, int N, int checked, void* stream);
+int bx_pcg_seed_state(const int64_t* keys, int64_t* st, int n, void* stream);
+int bx_pcg_raw_from_state(const int64_t* st, int64_t* out, int n, int V, void* stream);
+
 /* ---- integer sampler ------------------------------------------------------------------------------------
  * Raw PCG64 words of numpy's default_rng([20261022, seed, t]): keys int64 [n, 2] -> out int64 [n, V].
  * Replaces gpu_pcg.raw_rows (src/bitexact/vllm_plugin/gpu_pcg.py:94-108; CPU: src/bitexact/sampling.py:27-37). */

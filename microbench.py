@@ -6,6 +6,7 @@
     python microbench.py stages [--batch 256] [--iters 10]
     python microbench.py prefill [--batch 4] [--ctx 2048] [--iters 10]
     python microbench.py prompt [--batch 4] [--ctx 2048] [--chunk 4096] [--iters 3]
+    python microbench.py bmm [--ctx 2048] [--iters 5]
 
 gemm: the exact-mode fused linear on the projection shapes of one Llama-3.2-1B layer and the LM head
       (int8-equivalent ops = 2 * 9 * M * N * K; algorithmic bytes = 3 N K + 4 M K + 8 M N).
@@ -231,6 +232,34 @@ def prefill(args):
     return rec
 
 
+def bmm_bench(args):
+    """`bmm` (the exact batched product of the reference's standalone engine) on the shapes of a --ctx-token prompt of
+    one sequence: q.K (Z = 8 KV heads, M = 4 T, K = 64, N = S) and p.V (K = S, N = 64). The kernel is a CUDA-core
+    int64 tile: a compatibility path, the serving path never calls it."""
+    from bitexact_llm_b200.bmm import bmm
+    dev = "cuda"
+    S = args.ctx
+    g = torch.Generator(device=dev).manual_seed(0)
+    q = torch.randint(-(1 << 22), 1 << 22, (8, 4 * S, 64), dtype=torch.int32, device=dev, generator=g)
+    k = torch.randint(-(1 << 22), 1 << 22, (8, 64, S), dtype=torch.int64, device=dev, generator=g)
+    p = torch.randint(0, 1 << 22, (8, 4 * S, S), dtype=torch.int32, device=dev, generator=g)
+    v = torch.randint(-(1 << 22), 1 << 22, (8, S, 64), dtype=torch.int64, device=dev, generator=g)
+    for name, a, b in (("q.K", q, k), ("p.V", p, v)):
+        for _ in range(2):
+            bmm(a, b)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.iters):
+            bmm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.iters
+        macs = 8.0 * a.shape[1] * a.shape[2] * b.shape[2]
+        print(json.dumps({"kernel": "bmm", "product": name, "S": S, "us": ms * 1e3, "int64_gmac_per_s": macs / ms / 1e6,
+                          "int8_equivalent_tops": 18.0 * macs / ms / 1e9}), flush=True)
+
+
 def prompt(args):
     """Prompt processing of the whole model (random-init Llama-3.2-1B, exact mode): --batch prompts of --ctx tokens
     through `Session.prefill`, with the tile kernel and with every token as a row of the decode kernel."""
@@ -343,7 +372,7 @@ def stages(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemmr", "attn", "stages", "prefill", "prompt"])
+    ap.add_argument("what", choices=["gemm", "gemmr", "attn", "stages", "prefill", "prompt", "bmm"])
     ap.add_argument("--m", default="1,16,256,4096")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -356,7 +385,7 @@ def main():
     ap.add_argument("--fixed", action="store_true", help="attn: every request has exactly --ctx keys")
     ap.add_argument("--chunk", type=int, default=4096, help="prompt: token rows per forward call")
     args = ap.parse_args()
-    {"gemm": gemm, "gemmr": gemmr, "attn": attn, "stages": stages, "prefill": prefill, "prompt": prompt}[args.what](args)
+    {"gemm": gemm, "gemmr": gemmr, "attn": attn, "stages": stages, "prefill": prefill, "prompt": prompt, "bmm": bmm_bench}[args.what](args)
     if nv.device_status() != 0:
         raise SystemExit("device-side wait timed out")
 
