@@ -44,7 +44,7 @@ _SIGNATURES = {
     "bx_int8_attention_ws": (I, [P, P, P, L, L, L, L, I, P, I, L, I, P, P, P, P, I, I, I, I, I, I, P, Z, P]),
     "bx_exact_attention": (I, [P, P, P, P, L, L, L, L, I, P, I, L, I, P, P, L, P, P, I, I, I, I, I, I, P]),
     "bx_int8_attention": (I, [P, P, P, L, L, L, L, I, P, I, L, I, P, P, P, P, I, I, I, I, I, I, P]),
-    "bx_prefill_attention": (I, [P, P, P, P, I, P, L, L, L, L, I, P, I, L, I, P, L, P, P, P, I, I, I, P]),
+    "bx_prefill_attention": (I, [P, P, P, P, I, P, L, L, L, L, I, P, I, L, I, P, L, P, P, P, I, I, I, I, P]),
     "bx_int8_norm": (I, [I, P, P, P, P, P, P, P, P, P, I, I, I, P]),
     "bx_int8_qkv": (I, [P, P, P, P, P, P, L, L, L, I, P, P, P, I, I, I, I, P]),
     "bx_int8_attn_out": (I, [P, P, P, P, P, I, I, I, P]),

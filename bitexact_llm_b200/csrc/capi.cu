@@ -870,11 +870,14 @@ int bx_int8_attention(const int32_t* q, const int64_t* qpos, const int8_t* cache
 int bx_prefill_attention(const int32_t* q, const int64_t* sh, const int64_t* pos, const int32_t* tiles, int n_tiles,
                          const int8_t* cache, int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs,
                          const void* bt, int bt_is_int64, int64_t sbt, int nblk, const int64_t* lut, int64_t l2e,
-                         const int32_t* ptab, int64_t* num, int64_t* den, int HKV, int G, int HD, void* stream) {
+                         const int32_t* ptab, int64_t* num, int64_t* den, int HKV, int G, int HD, int tile_rows,
+                         void* stream) {
   if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
   if (!q || !pos || !tiles || !cache || !bt || !num || !den || n_tiles < 0) return BX_EARG;
   if (!ptab && (!sh || !lut)) return BX_EARG;
-  if (HD != ATT_HD || HKV <= 0 || HKV > 65535 || G < 1 || G > PF_ROWS || nblk <= 0 || nb <= 0) return BX_EARG;
+  if (tile_rows == 0) tile_rows = 32;
+  if (tile_rows != 16 && tile_rows != 32) return BX_EARG;
+  if (HD != ATT_HD || HKV <= 0 || HKV > 65535 || G < 1 || G > tile_rows || nblk <= 0 || nb <= 0) return BX_EARG;
   if (bs < 8 || bs > PF_KEYS || PF_KEYS % bs || (int64_t)nblk * bs >= 43690) return BX_EARG;
   if (sc_bs % 16 || sc_h % 16 || sc_nb % 16 || sc_bs < 384 || !aligned16(cache) || !aligned16(q)) return BX_EARG;
   if (n_tiles == 0) return BX_OK;
@@ -889,10 +892,15 @@ int bx_prefill_attention(const int32_t* q, const int64_t* sh, const int64_t* pos
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return BX_ELAUNCH;
-  const int smem = 2 * PF_STAGE + PF_QTILE + PF_PTILE + (int)sizeof(PrefillSmall) + 1024;
+  const int smem32 = 2 * PF_STAGE + PfCfg<32>::QTILE + PfCfg<32>::PTILE + (int)sizeof(PrefillSmall) + 1024;
+  const int smem16 = 2 * PF_STAGE + PfCfg<16>::QTILE + PfCfg<16>::PTILE + (int)sizeof(PrefillSmall) + 1024;
   static PerDevice configured;
-  if (once_per_device(configured, [smem] {
-        return cudaFuncSetAttribute(prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (once_per_device(configured, [smem32, smem16] {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             smem32);
+        return e != cudaSuccess ? e
+                                : cudaFuncSetAttribute(prefill_attention_kernel<16>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem16);
       }) != BX_OK)
     return BX_ELAUNCH;
   PrefillParams p{};
@@ -912,7 +920,11 @@ int bx_prefill_attention(const int32_t* q, const int64_t* sh, const int64_t* pos
   p.den = (i64*)den;
   p.HKV = HKV;
   p.G = G;
-  prefill_attention_kernel<<<dim3((unsigned)n_tiles, (unsigned)HKV), PF_THREADS, smem, (cudaStream_t)stream>>>(tm, p);
+  const dim3 grid((unsigned)n_tiles, (unsigned)HKV);
+  if (tile_rows == 32)
+    prefill_attention_kernel<32><<<grid, PfCfg<32>::THREADS, smem32, (cudaStream_t)stream>>>(tm, p);
+  else
+    prefill_attention_kernel<16><<<grid, PfCfg<16>::THREADS, smem16, (cudaStream_t)stream>>>(tm, p);
   return launched(1);
 }
 

@@ -26,16 +26,24 @@
 
 namespace bx {
 
-constexpr int PF_ROWS = 32;                     // query rows per tile
+constexpr int PF_MAXROWS = 32;                  // query rows per tile: 32 (one CTA per SM) or 16 (two CTAs per SM)
 constexpr int PF_KEYS = 128;                    // keys per block
-constexpr int PF_THREADS = 512;
 constexpr int PF_BOX = PF_KEYS * 128;           // one third of the cache rows of a block: 16 KB
 constexpr int PF_STAGE = 3 * PF_BOX;
-constexpr int PF_QTILE = 4 * 12 * 128;          // query limbs [96 rows x 64 dims] as 8 x 16-byte core matrices: 6 KB
-constexpr int PF_PTILE = 8 * 12 * 128;          // weight limbs [96 rows x 128 keys]: 12 KB
-constexpr int PF_LBO = 12 * 128;                // bytes between the 16-byte K chunks of those tiles
-constexpr int PF_S_COLS = 5 * PF_ROWS;          // score accumulators
-constexpr int PF_D1 = PF_S_COLS, PF_D2 = 256;   // p.V accumulators (96 columns each)
+
+// Sizes that follow from the tile height ROWS (3 ROWS limb rows in the query and weight tiles).
+template <int ROWS>
+struct PfCfg {
+  static_assert(ROWS == 16 || ROWS == 32, "tile height");
+  static constexpr int THREADS = 16 * ROWS;               // 4 lane quarters x ROWS / 8 row groups, one warp each
+  static constexpr int RG = 3 * ROWS / 8;                 // 8-row groups of the limb tiles
+  static constexpr int LBO = RG * 128;                    // bytes between the 16-byte K chunks of those tiles
+  static constexpr int QTILE = 4 * LBO;                   // query limbs [3 ROWS x 64 dims] as 8 x 16-byte core matrices
+  static constexpr int PTILE = 8 * LBO;                   // weight limbs [3 ROWS x 128 keys]
+  static constexpr int S_COLS = 5 * ROWS;                 // score accumulators
+  static constexpr int D1 = S_COLS, D2 = D1 + 3 * ROWS;   // p.V accumulators (3 ROWS columns each)
+  static constexpr int TMEM = ROWS == 32 ? 512 : 256;
+};
 
 struct PrefillParams {
   const int32_t* q;     // [N, HKV, G, 64]
@@ -58,17 +66,19 @@ struct PrefillSmall {
   uint64_t pv_done;
   uint32_t tmem_base;
   uint32_t fail;
-  i64 red[4][PF_ROWS];
-  i64 rowmax[PF_ROWS];
+  i64 red[4][PF_MAXROWS];
 };
 
-__global__ void __launch_bounds__(PF_THREADS, 1)
+template <int ROWS>
+__global__ void __launch_bounds__(PfCfg<ROWS>::THREADS, ROWS == 32 ? 1 : 2)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams p) {
+  using C = PfCfg<ROWS>;
+  constexpr int PF_ROWS = ROWS, PF_THREADS = C::THREADS, PF_LBO = C::LBO, PF_D1 = C::D1, PF_D2 = C::D2;
   extern __shared__ uint8_t pf_smem[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pf_smem) + 1023) & ~uintptr_t(1023));
   uint8_t* qtile = ring + 2 * PF_STAGE;
-  uint8_t* ptile = qtile + PF_QTILE;
-  PrefillSmall* sm = reinterpret_cast<PrefillSmall*>(ptile + PF_PTILE);
+  uint8_t* ptile = qtile + C::QTILE;
+  PrefillSmall* sm = reinterpret_cast<PrefillSmall*>(ptile + C::PTILE);
   i64* comb = reinterpret_cast<i64*>(ring);            // after the last MMA: [32 rows][64 dims]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -89,7 +99,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmap, const Prefill
     tma_prefetch_desc(&tmap);
   }
   if (warp == 0) {
-    tmem_alloc(&sm->tmem_base, 512);
+    tmem_alloc(&sm->tmem_base, C::TMEM);
     tmem_relinquish();
   }
   // ---- the three query limb tiles: row (i, r) of the B operand, 16-byte K chunks PF_LBO apart ----
@@ -191,7 +201,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmap, const Prefill
         const uint64_t k2 = umma_desc_sw128(sbase + PF_BOX + ks * 32);
         if (ks == 0) {
           // every column block written once without accumulation
-          const uint64_t q_two = q_all, q_last = umma_desc_kmajor_plain(qk + 8 * 128, PF_LBO, 128);
+          const uint64_t q_two = q_all, q_last = umma_desc_kmajor_plain(qk + (2 * PF_ROWS / 8) * 128, PF_LBO, 128);
           umma_i8(tmem, k0, q_all, ID_ALL, 0);
           umma_i8(tmem + 3 * PF_ROWS, k1, q_last, ID_ONE, 0);
           umma_i8(tmem + 1 * PF_ROWS, k1, q_two, ID_TWO, 1);
@@ -246,7 +256,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmap, const Prefill
         den[j] += pv;
         int rem = (int)pv;
 #pragma unroll
-        for (int i = 0; i < 3; ++i) pcol[i * 4 * 128 + j * 16] = (uint8_t)split8(rem);
+        for (int i = 0; i < 3; ++i) pcol[i * (PF_ROWS / 8) * 128 + j * 16] = (uint8_t)split8(rem);
       }
       fence_proxy_async_smem();
     }
@@ -343,7 +353,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tmap, const Prefill
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, C::TMEM);
   }
 }
 

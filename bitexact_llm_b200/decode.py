@@ -85,7 +85,7 @@ class Session:
                     if n:
                         pre.append((b, row0, n, p0 + n))
                     row0 += n
-                tt = tri_prefill.tile_table(pre, G).to(dev)
+                tt = tri_prefill.tile_table(pre, G, tri_prefill.ROWS).to(dev)
             x = self.eng.forward(self.kvs, prompts[:, p0:p1][live], pos, self._slots(seq, pos), self.bt, seq, tiles=tt)
             fin = pos == lens[seq] - 1
             last[seq[fin]] = x[fin]

@@ -213,13 +213,14 @@ int bx_int8_attention_ws(const int32_t* q, const int64_t* qpos, const int8_t* ca
                          int HD, int cluster_size, int variant, void* scratch, size_t scratch_bytes, void* stream);
 
 /* ---- prefill attention (both weight rules) -------------------------------------------------------------------------
- * Attention of whole TILES of prompt tokens: a tile is up to 32 / G consecutive tokens of one request; one CTA per
- * (tile, KV head) stages every K / V row once for the tile's 32 query rows (token x G query heads), runs both integer
- * sweeps and has the limb products (scores and p.V) on tcgen05 with TMEM accumulators.
+ * Attention of whole TILES of prompt tokens: a tile is up to tile_rows / G consecutive tokens of one request; one CTA
+ * per (tile, KV head) stages every K / V row once for the tile's query rows (token x G query heads), runs both integer
+ * sweeps and has the limb products (scores and p.V) on tcgen05 with TMEM accumulators. tile_rows: 32 (one CTA of
+ * 512 threads per SM; 0 selects it) or 16 (two CTAs of 256 threads per SM). No effect on results.
  *   q      int32 [N, HKV, G, 64] token-major (|q| <= 2^22 exact mode; within three limbs int8 mode), 16-byte aligned
  *   sh     int64 [N, HKV, G] row exponents (exact mode; NULL with ptab)
  *   pos    int64 [N] position of each token: key s is visible iff s <= pos
- *   tiles  int32 [n_tiles, 3] = (block-table row, first token, tokens <= 32 / G), on the device
+ *   tiles  int32 [n_tiles, 3] = (block-table row, first token, tokens <= tile_rows / G), on the device
  *   cache, bt, nblk, bs as bx_exact_attention (bs one of 8, 16, 32, 64, 128); lut / l2e: exact weight rule;
  *   ptab: int8-mode weight table (then lut may be NULL)
  *   num int64 [N, HKV, G, 64], den int64 [N, HKV, G]: the rows of the tiles' tokens are written, others untouched.
@@ -230,7 +231,8 @@ int bx_int8_attention_ws(const int32_t* q, const int64_t* qpos, const int8_t* ca
 int bx_prefill_attention(const int32_t* q, const int64_t* sh, const int64_t* pos, const int32_t* tiles, int n_tiles,
                          const int8_t* cache, int64_t nb, int64_t sc_nb, int64_t sc_h, int64_t sc_bs, int bs,
                          const void* bt, int bt_is_int64, int64_t sbt, int nblk, const int64_t* lut, int64_t l2e,
-                         const int32_t* ptab, int64_t* num, int64_t* den, int HKV, int G, int HD, void* stream);
+                         const int32_t* ptab, int64_t* num, int64_t* den, int HKV, int G, int HD, int tile_rows,
+                         void* stream);
 
 /* ---- int8-mode attention and element-wise stages -------------------------------------------------------
  * Fixed points of int8 mode: residual stream / linear outputs / logits 16 bits, gamma 12, cos / sin 16, q / k / v 14,

@@ -219,13 +219,15 @@ def prefill(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / args.iters
 
-    ms_tile = timed(lambda: tri_prefill.attend_exact(q, sh, pos, cache, bt, tiles, lut, 387270501, num, den))
+    rows = args.tile or tri_prefill.ROWS
+    tiles = tri_prefill.tile_table([(r, r * S, S, S) for r in range(R)], G, rows).to(dev)
+    ms_tile = timed(lambda: tri_prefill.attend_exact(q, sh, pos, cache, bt, tiles, lut, 387270501, num, den, rows))
     n2, d2 = tri_exact_attn.attend(q, sh, qpos, cache, bt, req, lut, 387270501)
     if not (torch.equal(num, n2) and torch.equal(den, d2)):
         raise SystemExit("tile kernel differs from the per-row kernel")
     ms_row = timed(lambda: tri_exact_attn.attend(q, sh, qpos, cache, bt, req, lut, 387270501))
     ops = R * 2.0 * 18.0 * (S * (S + 1) / 2.0) * HKV * G * HD
-    rec = {"kernel": "prefill_attention", "prompts": R, "S": S, "tiles": int(tiles.shape[0]), "us": ms_tile * 1e3,
+    rec = {"kernel": "prefill_attention", "tile_rows": rows, "prompts": R, "S": S, "tiles": int(tiles.shape[0]), "us": ms_tile * 1e3,
            "int8_tops": ops / ms_tile / 1e9, "tokens_per_s_one_layer": N / ms_tile * 1e3,
            "per_row_kernel_us": ms_row * 1e3, "speedup_vs_rows": ms_row / ms_tile}
     print(json.dumps(rec), flush=True)

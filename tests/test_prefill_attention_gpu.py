@@ -82,6 +82,9 @@ def test_tiles_equal_the_oracle_and_the_row_kernel(mode, S, HKV, G, bs):
     tl = T(tiles)
     if mode == "exact":
         num, den = tri_prefill.attend_exact(T(q, torch.int32), T(sh), T(pos), T(planes), T(bt), tl, T(lut_np), ox.L2E28)
+        n32, d32 = tri_prefill.attend_exact(T(q, torch.int32), T(sh), T(pos), T(planes), T(bt), tl, T(lut_np), ox.L2E28,
+                                            rows=32)                      # the 32-row tile height: same integers
+        assert torch.equal(n32, num) and torch.equal(d32, den)
     else:
         num = torch.zeros(N, HKV, G, HD, dtype=torch.long, device="cuda")
         den = torch.ones(N, HKV, G, 1, dtype=torch.long, device="cuda")
