@@ -95,6 +95,8 @@ def gemmr(args):
         for name, (N, K) in FUSED.items():
             if name == "lm" and args.shapes != "all":
                 continue
+            if args.proj and name != args.proj:
+                continue
             w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
             d0 = decompose(w.to(dev))
             nsets = max(2, (200 << 20) // (3 * N * K) + 1)
@@ -108,6 +110,13 @@ def gemmr(args):
             exact_fuse.attach_planes(q, planes)
             sh = torch.full((M,), -14, dtype=torch.long, device=dev)
             fl = torch.zeros(1, dtype=torch.int32, device=dev)
+            if args.eager:                      # plain launches, one per weight set (for a profiler capture)
+                for i in range(nsets):
+                    sets[i](q, sh, fl, False)
+                torch.cuda.synchronize()
+                print(json.dumps({"kernel": "exact_linear", "proj": name, "M": M, "eager_launches": nsets}), flush=True)
+                del sets
+                continue
             for tag in ("residual", "none"):
                 saved = [f.cnt for f in sets]
                 if tag == "none":
@@ -385,6 +394,8 @@ def main():
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-scratch", action="store_true", help="attn: no scratch buffer (long contexts: cluster kernels)")
     ap.add_argument("--fixed", action="store_true", help="attn: every request has exactly --ctx keys")
+    ap.add_argument("--proj", default="", help="gemmr: only this projection (wqkv, wo, wgu, wd, lm)")
+    ap.add_argument("--eager", action="store_true", help="gemmr: one plain launch per weight set, no timing")
     ap.add_argument("--chunk", type=int, default=4096, help="prompt: token rows per forward call")
     args = ap.parse_args()
     {"gemm": gemm, "gemmr": gemmr, "attn": attn, "stages": stages, "prefill": prefill, "prompt": prompt, "bmm": bmm_bench}[args.what](args)
