@@ -182,9 +182,26 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
+
+template <int W>
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[W]) {
+  static_assert(W == 4 || W == 8, "4 or 8 columns");
+  if constexpr (W == 8) tmem_ld8(taddr, r); else tmem_ld4(taddr, r);
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// 32 lanes x 8 consecutive 32-bit columns <- one value (used to clear accumulator columns).
+// 32 lanes x 4 / 8 consecutive 32-bit columns <- one value (used to clear accumulator columns).
+__device__ __forceinline__ void tmem_st4_fill(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ void tmem_st8_fill(uint32_t taddr, uint32_t v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
                : "memory");

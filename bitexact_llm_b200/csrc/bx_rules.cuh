@@ -101,6 +101,35 @@ __device__ __forceinline__ int split8(int& r) {
   return lo;
 }
 
+// Per-tile scalars held across the lanes of a warp: slot s of lane l holds the value of tile row (or column)
+// 32 s + l. A warp loads them once per tile, before it waits for the accumulators, and hands a value round by
+// shuffle when an output needs it: no global load remains between the accumulator read-out and the stores.
+template <int NS>
+__device__ __forceinline__ i64 lane_slot(const i64 (&v)[NS], int idx) {
+  i64 x = v[0];
+#pragma unroll
+  for (int s = 1; s < NS; ++s)
+    if ((idx >> 5) == s) x = v[s];
+  return x;
+}
+template <int NS>
+__device__ __forceinline__ int lane_slot(const int (&v)[NS], int idx) {
+  int x = v[0];
+#pragma unroll
+  for (int s = 1; s < NS; ++s)
+    if ((idx >> 5) == s) x = v[s];
+  return x;
+}
+
+// a0 + a1 2^8 + a2 2^16 + a3 2^24 + a4 2^32 of five signed 32-bit accumulators, as three widening multiply-adds.
+__device__ __forceinline__ i64 join5(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4) {
+  i64 t = (i64)(int32_t)a0;
+  asm("mad.wide.s32 %0, %1, 256, %0;" : "+l"(t) : "r"(a1));
+  asm("mad.wide.s32 %0, %1, 65536, %0;" : "+l"(t) : "r"(a2));
+  asm("mad.wide.s32 %0, %1, 16777216, %0;" : "+l"(t) : "r"(a3));
+  return t + (i64)((u64)a4 << 32);
+}
+
 // round((T * 2^d + B) * 2^p) by the two-word rule (exact/ops.py:60-79), and whether bits were lost or the
 // result left (-2^62, 2^62) (exact/wmm.py:143-149). 0 <= d <= 30.
 __device__ __forceinline__ i64 round_shift_hl(i64 T, i64 B, int d, i64 p, bool& bad) {
@@ -133,17 +162,23 @@ __device__ __forceinline__ i64 round_shift_hl(i64 T, i64 B, int d, i64 p, bool& 
   return y;
 }
 
-// round_shift_hl with a short cut for the common case. For a weight row on its own grid (d = 0) without residual
-// entries (B = 0) and a shift of 1 .. 31 bits (p = -k), H 2^32 + L = T and the two-word rule
-// (H << (32 - k)) + ((L + 2^(k-1)) >> k) is (T + 2^(k-1)) >> k, because H 2^32 is a multiple of 2^k. With
-// |T| < 2^61 (|q| <= 2^22, |W| < 2^23, K < 43690) no bit can be lost and |y| < 2^62: the flag stays clear. Same
-// integers as round_shift_hl, a fifth of its instructions.
-__device__ __forceinline__ i64 exact_round(i64 T, i64 B, int d, i64 p, bool plain_row, bool& bad) {
-  if (plain_row && p < 0 && p > -32) {
-    const int k = (int)(-p);
+// round_shift_hl for a whole warp (all 32 lanes call it together; lanes with on = false take no part in the result).
+// When every lane that is on shifts right by k = -p = 1 .. 31 bits with k >= d, |T| < 2^61 and |B| < 2^60, the short
+// form is taken: nothing wraps, H 2^32 + L is V = T 2^d + B exactly, and the two-word result
+// (H << (32 - k)) + ((L + 2^(k-1)) >> k) is floor((V + 2^(k-1)) / 2^k). With X = B + 2^(k-1) = Xh 2^d + Xl
+// (0 <= Xl < 2^d) that is floor((T + Xh + Xl / 2^d) / 2^(k-d)) = (T + Xh) >> (k - d): the fraction Xl / 2^d < 1
+// cannot carry into the floor. |H| < 2^(29+d) + 2^28 < 2^(31+k) and |y| < 2^62, so the flag stays clear. Same
+// integers as round_shift_hl at a fifth of its instructions; any other case takes round_shift_hl itself.
+__device__ __forceinline__ i64 round_rule_warp(i64 T, i64 B, int d, i64 p, bool on, bool& bad) {
+  const bool in = p < 0 && p > -32 && -p >= (i64)d &&
+                  (((u64)(T + (1ll << 61)) >> 62) | ((u64)(B + (1ll << 60)) >> 61)) == 0;
+  if (__all_sync(0xffffffffu, !on || in)) {
+    const int k = on ? (int)(-p) : 31;
     bad = false;
-    return (T + (1ll << (k - 1))) >> k;
+    return (T + ((B + (1ll << (k - 1))) >> d)) >> (k - d);
   }
+  bad = false;
+  if (!on) return 0;
   return round_shift_hl(T, B, d, p, bad);
 }
 

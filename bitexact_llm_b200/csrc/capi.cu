@@ -255,6 +255,27 @@ int launch_exact_rows(const CUtensorMap& ma, const CUtensorMap& mw, const ExactE
   return launched(1);
 }
 
+template <int TN, int NBUF>
+int launch_exact_rows_one(const CUtensorMap& mact, const CUtensorMap& mwt, const ExactEpiParams& ep, int K,
+                          cudaStream_t st) {
+  using Cfg = GemmCfg<3, 3, TN>;
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(exact_linear_rows_one_kernel<TN, NBUF>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int sms = device_sms();
+  if (sms <= 0) return BX_ELAUNCH;
+  const int row_blocks = (ep.M + WROWS - 1) / WROWS;
+  const int w_tiles = (ep.N + TN - 1) / TN;
+  const long total = (long)row_blocks * w_tiles;
+  const int grid = (int)(total < sms ? total : sms);
+  exact_linear_rows_one_kernel<TN, NBUF><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mact, mwt, ep, K, row_blocks,
+                                                                                     w_tiles);
+  return launched(1);
+}
+
 template <int TA, bool POST>
 int launch_int8(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParams& ep, int K, cudaStream_t st) {
   using Cfg = GemmCfg<1, 2, TA>;
@@ -439,6 +460,10 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
     }
     if (ta <= 48 && n_tiles * ((M + ta - 1) / ta) > 2 * 148) persistent = true;
     if (ta == 64 && K <= 4096 && n_tiles * ((M + 47) / 48) > 2 * 148) { ta = 48; persistent = true; }
+    // Long tile lists of batches that fill blocks of 128 rows at least as well as tiles of 48: the activation rows
+    // go to the MMA M side (no ragged sixth tile at 256 rows, warp-uniform residual lists). Measured at M = 256:
+    // gate / up 80 -> 70 us, LM head 519 -> 468 us.
+    if (persistent && ta == 48 && M > WROWS && ((M + WROWS - 1) / WROWS) * WROWS <= ((M + 47) / 48) * 48) ta = 648;
   }
   // Split-K over a cluster of CTAs (200 + activation rows per tile asks for it; automatic for small batches whose
   // tile list covers less than half of the SMs): as many K slices as keep the CTA count within the 148 SMs.
@@ -467,6 +492,21 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
       case 48: return launch_exact_rows<48, true>(ma, mw, ep, K, st);
       case 64: return launch_exact_rows<64, false>(ma, mw, ep, K, st);
       default: return launch_exact_rows<80, false>(ma, mw, ep, K, st);
+    }
+  }
+  if (ta == 616 || ta == 632 || ta == 648 || ta == 664 || ta == 680) {
+    // 600 + weight rows per tile: activation rows on the MMA M side, one CTA (16 .. 48: two accumulator buffers)
+    ta -= 600;
+    CUtensorMap mact, mwt;
+    if (!make_map(&mact, scratch, (uint64_t)K, (uint64_t)M, 3, WROWS)) return BX_ELAUNCH;
+    if (!make_map(&mwt, limbs, (uint64_t)K, (uint64_t)N, 3, (uint32_t)ta)) return BX_ELAUNCH;
+    ExactEpiParams ep{q, ldq, sh, d, g, cnt, ec, ev, R, y, flag, M, N, checked};
+    switch (ta) {
+      case 16: return launch_exact_rows_one<16, 2>(mact, mwt, ep, K, st);
+      case 32: return launch_exact_rows_one<32, 2>(mact, mwt, ep, K, st);
+      case 48: return launch_exact_rows_one<48, 2>(mact, mwt, ep, K, st);
+      case 64: return launch_exact_rows_one<64, 1>(mact, mwt, ep, K, st);
+      default: return launch_exact_rows_one<80, 1>(mact, mwt, ep, K, st);
     }
   }
   int split = 0;

@@ -37,16 +37,23 @@ struct ExactEpilogue {
   // What a thread needs about its weight row n (TMEM lane): loaded BEFORE the accumulators are waited for, so the
   // loads (two dependent levels: the count, then the list) overlap the main loop instead of heading every tile's
   // epilogue. The residual list of row n (a handful of entries in a few per cent of the rows) is read once.
+  static constexpr int NS = (TA + 31) / 32;
   struct Row {
     int n, d, cnt, wcnt;
     bool nok;
     i64 gd;
     int ecr[RMAX];
     i64 evr[RMAX];
+    i64 shv[NS];             // row exponents of the tile's activation rows, lane-held (lane_slot)
   };
 
-  static __device__ __forceinline__ Row load_row(int quarter, int lane, int n0, const Params& p) {
+  static __device__ __forceinline__ Row load_row(int quarter, int group, int lane, int n0, int m0, const Params& p) {
     Row r;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int c = s * 32 + lane;
+      r.shv[s] = (c < TA && m0 + c < p.M) ? p.sh[m0 + c] : 0;
+    }
     r.n = n0 + quarter * 32 + lane;
     r.nok = r.n < p.N;
     r.d = r.nok ? (int)p.d[r.n] : 0;
@@ -65,15 +72,14 @@ struct ExactEpilogue {
     return r;
   }
 
-  // Pulls what the epilogue of tile rows m0 .. will read per output into L1 while the tile's MMAs still run: the
-  // row exponents (one lane per row) and, for a thread whose weight row has a residual list, its gathers from q.
+  // Pulls the gathers from q of a thread whose weight row has a residual list into L1 while the tile's MMAs still
+  // run.
   static __device__ __forceinline__ void prefetch(const Row& r, int group, int lane, int m0, const Params& p) {
 #pragma unroll 1
-    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
+    for (int c0 = group * CW; c0 < TA; c0 += CW * EPI_GROUPS) {
       if (m0 + c0 >= p.M) break;
-      if (lane < 8 && m0 + c0 + lane < p.M) prefetch_l1(p.sh + m0 + c0 + lane);
       if (r.cnt > 0) {
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < CW; ++i) {
           const int m = m0 + c0 + i;
           if (m >= p.M) break;
 #pragma unroll
@@ -84,8 +90,12 @@ struct ExactEpilogue {
     }
   }
 
+  // Accumulator columns per chunk: 8 when the TA columns split evenly over the EPI_GROUPS warps of a lane quarter in
+  // chunks of 8, else 4 (TA = 48: three chunks of 4 for every warp instead of two chunks of 8 for half of them).
+  static constexpr int CW = (TA % (8 * EPI_GROUPS) == 0) ? 8 : 4;
+
   // One thread per weight row n (TMEM lane) and column group; walks its share of the TA activation rows in chunks
-  // of 8 accumulator columns.
+  // of CW accumulator columns.
   static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
                                              bool has_k, const Params& p, const Row& r) {
     const int n = r.n;
@@ -93,32 +103,31 @@ struct ExactEpilogue {
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
-    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
+    for (int c0 = group * CW; c0 < TA; c0 += CW * EPI_GROUPS) {
       if (m0 + c0 >= p.M) break;                     // warp-uniform
-      uint32_t acc[5][8];
+      const i64 sh_slot = lane_slot<NS>(r.shv, c0);      // lane (c0 & 31) + i holds the exponent of row c0 + i
+      uint32_t acc[5][CW];
 #pragma unroll
-      for (int b = 0; b < 5; ++b) tmem_ld8(tbase + b * TA + c0, acc[b]);
+      for (int b = 0; b < 5; ++b) tmem_ldn<CW>(tbase + b * TA + c0, acc[b]);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < CW; ++i) {
         const int m = m0 + c0 + i;
-        if (m < p.M && r.nok) {
-          i64 T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +
-                  shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
-          if (!has_k) T = 0;
-          i64 B = 0;
-          if (warp_res) {
+        const bool on = m < p.M && r.nok;
+        const i64 pv = __shfl_sync(0xffffffffu, sh_slot, (c0 & 31) + i) + r.gd;
+        const i64 T = has_k ? join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]) : 0;
+        i64 B = 0;
+        if (warp_res && on) {
 #pragma unroll
-            for (int j = 0; j < RMAX; ++j)
-              if (j < r.wcnt && j < r.cnt) B += (i64)p.q[(i64)m * p.ldq + r.ecr[j]] * r.evr[j];
-            for (int j = RMAX; j < r.cnt; ++j)
-              B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
-          }
-          bool bad;
-          const i64 yv = round_shift_hl(T, B, r.d, p.sh[m] + r.gd, bad);
-          any_bad |= bad;
-          p.y[(i64)m * p.N + n] = yv;
+          for (int j = 0; j < RMAX; ++j)
+            if (j < r.wcnt && j < r.cnt) B += (i64)p.q[(i64)m * p.ldq + r.ecr[j]] * r.evr[j];
+          for (int j = RMAX; j < r.cnt; ++j)
+            B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
         }
+        bool bad;
+        const i64 yv = round_rule_warp(T, B, r.d, pv, on, bad);
+        any_bad |= bad;
+        if (on) p.y[(i64)m * p.N + n] = yv;
       }
     }
     if (p.checked && any_bad) *p.flag = 1;

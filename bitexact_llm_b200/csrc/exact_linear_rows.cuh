@@ -43,66 +43,169 @@ struct RowsCfg {
 
 template <int TN>
 struct RowsEpilogue {
-  // Thread = activation row m0 + 32 quarter + lane; its group walks the tile's weight rows in chunks of 8.
+  // Thread = activation row m0 + 32 quarter + lane; its group walks the tile's weight rows in chunks of CW = 4
+  // (every tile size divides evenly among the EPI_GROUPS warps of a lane quarter; chunks of 8 spill registers).
+  static constexpr int CW = 4;
+  static constexpr int NS = (TN + 31) / 32;
+
+  // Loaded before the accumulators are waited for: the thread's row exponent and, lane-held (lane_slot), the
+  // constants of the tile's TN weight rows. No global load is left between the accumulator read-out and the stores,
+  // except the gathers of the few weight rows with a residual list.
+  struct Row {
+    int m;
+    bool mok;
+    i64 shm;
+    int d[NS], cnt[NS];
+    i64 gd[NS];
+  };
+
+  static __device__ __forceinline__ Row load_row(int quarter, int lane, int n0, int m0, const ExactEpiParams& p) {
+    Row r;
+    r.m = m0 + quarter * 32 + lane;
+    r.mok = r.m < p.M;
+    r.shm = r.mok ? p.sh[r.m] : 0;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int c = s * 32 + lane, n = n0 + c;
+      const bool nok = c < TN && n < p.N;
+      r.d[s] = nok ? (int)__ldg(p.d + n) : 0;
+      r.gd[s] = nok ? __ldg(p.g + n) - (i64)r.d[s] + FR : 0;
+      r.cnt[s] = (nok && p.cnt) ? __ldg(p.cnt + n) : 0;
+    }
+    return r;
+  }
+
+  // One output chunk: constants by shuffle, residual, rounding, store. T: the joined accumulators of the chunk.
+  static __device__ __forceinline__ void finish_chunk(const i64 (&T)[CW], int c0, int n0, const ExactEpiParams& p,
+                                                      const Row& r, const int32_t* qrow, i64* yrow, bool vec,
+                                                      bool& any_bad) {
+    const int d_slot = lane_slot<NS>(r.d, c0), cnt_slot = lane_slot<NS>(r.cnt, c0);
+    const i64 gd_slot = lane_slot<NS>(r.gd, c0);
+    i64 out[CW];
+#pragma unroll
+    for (int i = 0; i < CW; ++i) {
+      const int n = n0 + c0 + i, src = (c0 & 31) + i;
+      const int dv = __shfl_sync(0xffffffffu, d_slot, src), cntv = __shfl_sync(0xffffffffu, cnt_slot, src);
+      const i64 gdv = __shfl_sync(0xffffffffu, gd_slot, src);
+      const bool on = n < p.N && r.mok;
+      i64 B = 0;
+      if (on)
+        for (int j = 0; j < cntv; ++j)
+          B += (i64)qrow[__ldg(p.ec + (i64)n * p.R + j)] * __ldg(p.ev + (i64)n * p.R + j);
+      bool bad;
+      out[i] = round_rule_warp(T[i], B, dv, r.shm + gdv, on, bad);
+      any_bad |= bad;
+    }
+    if (r.mok) {
+      if (vec && n0 + c0 + CW <= p.N) {
+        longlong2* dst = reinterpret_cast<longlong2*>(yrow + n0 + c0);
+#pragma unroll
+        for (int i = 0; i < CW / 2; ++i) dst[i] = make_longlong2(out[2 * i], out[2 * i + 1]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < CW; ++i)
+          if (n0 + c0 + i < p.N) yrow[n0 + c0 + i] = out[i];
+      }
+    }
+  }
+
   static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
-                                             const ExactEpiParams& p) {
-    const int m = m0 + quarter * 32 + lane;
-    const bool mok = m < p.M;
-    const i64 shm = mok ? p.sh[m] : 0;
-    const int32_t* qrow = p.q + (i64)(mok ? m : 0) * p.ldq;
-    i64* yrow = reinterpret_cast<i64*>(p.y) + (i64)(mok ? m : 0) * p.N;
+                                             const ExactEpiParams& p, const Row& r) {
+    const int32_t* qrow = p.q + (i64)(r.mok ? r.m : 0) * p.ldq;
+    i64* yrow = reinterpret_cast<i64*>(p.y) + (i64)(r.mok ? r.m : 0) * p.N;
     const bool vec = (p.N & 1) == 0;
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
-    for (int c0 = group * 8; c0 < TN; c0 += 8 * EPI_GROUPS) {
+    for (int c0 = group * CW; c0 < TN; c0 += CW * EPI_GROUPS) {
       if (n0 + c0 >= p.N) break;                     // warp-uniform
-      uint32_t acc[5][8];
+      uint32_t acc[5][CW];
 #pragma unroll
-      for (int b = 0; b < 5; ++b) tmem_ld8(tbase + b * TN + c0, acc[b]);
-      // constants of the chunk's 8 weight rows: warp-uniform loads, in flight while the accumulators are read out
-      int dv[8], cntv[8];
-      i64 gdv[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int n = n0 + c0 + i;
-        const bool nok = n < p.N;
-        dv[i] = nok ? (int)__ldg(p.d + n) : 0;
-        gdv[i] = nok ? __ldg(p.g + n) - (i64)dv[i] + FR : 0;
-        cntv[i] = (nok && p.cnt) ? __ldg(p.cnt + n) : 0;
-      }
+      for (int b = 0; b < 5; ++b) tmem_ldn<CW>(tbase + b * TN + c0, acc[b]);
       tmem_ld_wait();
-      i64 out[8];
+      i64 T[CW];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int n = n0 + c0 + i;
-        out[i] = 0;
-        if (n < p.N && mok) {
-          const i64 T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +
-                        shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
-          i64 B = 0;
-          for (int j = 0; j < cntv[i]; ++j)
-            B += (i64)qrow[__ldg(p.ec + (i64)n * p.R + j)] * __ldg(p.ev + (i64)n * p.R + j);
-          bool bad;
-          out[i] = exact_round(T, B, dv[i], shm + gdv[i], cntv[i] == 0 && dv[i] == 0, bad);
-          any_bad |= bad;
-        }
+      for (int i = 0; i < CW; ++i) T[i] = join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]);
+      finish_chunk(T, c0, n0, p, r, qrow, yrow, vec, any_bad);
+    }
+    if (p.checked && any_bad) *p.flag = 1;
+  }
+
+  // The two halves of run for a kernel with one accumulator buffer: drain reads the thread's accumulators out and
+  // joins them (the buffer can be handed back right after), finish does the rest from registers.
+  static constexpr int NCH = TN / (CW * EPI_GROUPS);
+  struct Drained {
+    i64 T[NCH][CW];
+  };
+
+  static __device__ __forceinline__ void drain(uint32_t tmem, int quarter, int group, int n0, const ExactEpiParams& p,
+                                               Drained& a) {
+    const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c0 = (k * EPI_GROUPS + group) * CW;
+      if (n0 + c0 < p.N) {                           // warp-uniform
+        uint32_t acc[5][CW];
+#pragma unroll
+        for (int b = 0; b < 5; ++b) tmem_ldn<CW>(tbase + b * TN + c0, acc[b]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < CW; ++i) a.T[k][i] = join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]);
       }
-      if (mok) {
-        if (vec && n0 + c0 + 8 <= p.N) {
-          longlong2* dst = reinterpret_cast<longlong2*>(yrow + n0 + c0);
+    }
+  }
+
+  static __device__ __forceinline__ void finish(const Drained& a, int group, int n0, const ExactEpiParams& p,
+                                                const Row& r) {
+    const int32_t* qrow = p.q + (i64)(r.mok ? r.m : 0) * p.ldq;
+    i64* yrow = reinterpret_cast<i64*>(p.y) + (i64)(r.mok ? r.m : 0) * p.N;
+    const bool vec = (p.N & 1) == 0;
+    bool any_bad = false;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i] = make_longlong2(out[2 * i], out[2 * i + 1]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (n0 + c0 + i < p.N) yrow[n0 + c0 + i] = out[i];
-        }
-      }
+    for (int k = 0; k < NCH; ++k) {
+      const int c0 = (k * EPI_GROUPS + group) * CW;
+      if (n0 + c0 < p.N) finish_chunk(a.T[k], c0, n0, p, r, qrow, yrow, vec, any_bad);
     }
     if (p.checked && any_bad) *p.flag = 1;
   }
 };
+
+// The same layout on ONE CTA: the limb product is symmetric in its operands, so limb_gemm_persistent runs unchanged
+// with the activation planes as its 128-row operand and TN weight rows as its stacked operand; only the epilogue
+// (TMEM lane = activation row) differs. A batch of 256 rows is two row blocks without a ragged tile (six tiles of 48
+// rows cover 288), and the residual lists, which belong to weight rows, are warp-uniform here. TN = 48: two
+// accumulator buffers; TN = 64 / 80: one buffer (320 / 400 columns), wider MMAs, the epilogue not overlapped.
+template <int TN>
+struct RowsEpilogueOne {
+  using Params = ExactEpiParams;
+  using Row = typename RowsEpilogue<TN>::Row;
+  // a0: first activation row of the tile (the 128-row operand), w0: first weight row (the stacked operand)
+  static __device__ __forceinline__ Row load_row(int quarter, int, int lane, int a0, int w0, const Params& p) {
+    return RowsEpilogue<TN>::load_row(quarter, lane, w0, a0, p);
+  }
+  static __device__ __forceinline__ void prefetch(const Row&, int, int, int, const Params&) {}
+  static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int a0, int w0, bool,
+                                             const Params& p, const Row& r) {
+    RowsEpilogue<TN>::run(tmem, quarter, group, lane, w0, a0, p, r);
+  }
+  using Drained = typename RowsEpilogue<TN>::Drained;
+  static __device__ __forceinline__ void drain(uint32_t tmem, int quarter, int group, int, int, int w0, bool,
+                                               const Params& p, Drained& a) {
+    RowsEpilogue<TN>::drain(tmem, quarter, group, w0, p, a);
+  }
+  static __device__ __forceinline__ void finish(const Drained& a, int, int group, int, int, int w0, const Params& p,
+                                                const Row& r) {
+    RowsEpilogue<TN>::finish(a, group, w0, p, r);
+  }
+};
+
+template <int TN, int NBUF>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+exact_linear_rows_one_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_wt,
+                             const ExactEpiParams ep, int K, int row_blocks, int w_tiles) {
+  limb_gemm_persistent<3, 3, TN, RowsEpilogueOne<TN>, NBUF, true>(&tmap_act, &tmap_wt, row_blocks, w_tiles,
+                                                                  (K + BKB - 1) / BKB, ep);
+}
 
 // tmap_a: activation limb planes [3, M, K], boxes of 128 rows x 3 planes; tmap_w: weight limbs [3, N, K], boxes of
 // TN / 2 rows of one plane. Tiles: n_tiles = ceil(N / TN) by m_tiles2 = ceil(M / 256), the batch index fastest.
@@ -259,9 +362,13 @@ exact_linear_rows_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       auto hand_back = [&](int buf) {
         // Blocks 3 and 4 are only ever accumulated into: they start every tile at zero. A warp clears exactly the
         // columns it reads in RowsEpilogue::run, so no warp clears what another still reads.
-        for (int c0 = group * 8; c0 < TN; c0 += 8 * EPI_GROUPS) {
-          tmem_st8_fill(tmem + lane_base + buf * Cfg::COLS + 3 * TN + c0, 0u);
-          tmem_st8_fill(tmem + lane_base + buf * Cfg::COLS + 4 * TN + c0, 0u);
+        constexpr int CW = RowsEpilogue<TN>::CW;
+        for (int c0 = group * CW; c0 < TN; c0 += CW * EPI_GROUPS) {
+#pragma unroll
+          for (int b = 3; b < 5; ++b) {
+            const uint32_t at = tmem + lane_base + buf * Cfg::COLS + b * TN + c0;
+            if constexpr (CW == 8) tmem_st8_fill(at, 0u); else tmem_st4_fill(at, 0u);
+          }
         }
         tmem_st_wait();
         tc_fence_before();
@@ -274,13 +381,14 @@ exact_linear_rows_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       bool ok = true;
       for (int tile = pair; tile < total; tile += npairs, ++tcount) {
         const int buf = DBL ? (tcount & 1) : 0, use = DBL ? (tcount >> 1) : tcount;
+        const int w0 = (tile / m_tiles2) * TN, a0 = ((tile % m_tiles2) * 2 + (int)rank) * WROWS;
+        const typename RowsEpilogue<TN>::Row row = RowsEpilogue<TN>::load_row(quarter, lane, w0, a0, ep);
         if (ok) ok = mbar_wait(&sh->acc_full[buf], use & 1);
         ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sh->abort_flag) == 0);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        RowsEpilogue<TN>::run(tmem + buf * Cfg::COLS, quarter, group, lane, (tile / m_tiles2) * TN,
-                              ((tile % m_tiles2) * 2 + (int)rank) * WROWS, ep);
+        RowsEpilogue<TN>::run(tmem + buf * Cfg::COLS, quarter, group, lane, w0, a0, ep, row);
         hand_back(buf);
       }
       if (!ok && lane == 0) atomicAdd(&g_wait_timeouts, 1);

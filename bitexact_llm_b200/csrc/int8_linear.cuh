@@ -43,32 +43,30 @@ struct Int8Epilogue {
   using Params = Int8EpiParams;
 
   // The thread's weight row and its channel multiplier, loaded before the accumulators are waited for.
+  static constexpr int NS = (TA + 31) / 32;
   struct Row {
     int n;
     bool nok;
     i64 mc;
+    i64 mant[NS], e[NS];     // row scales of the tile's activation rows, lane-held (lane_slot)
   };
 
-  static __device__ __forceinline__ Row load_row(int quarter, int lane, int n0, const Params& p) {
+  static __device__ __forceinline__ Row load_row(int quarter, int group, int lane, int n0, int m0, const Params& p) {
     Row r;
     r.n = n0 + quarter * 32 + lane;
     r.nok = r.n < p.N;
     r.mc = (POST && r.nok) ? p.mul[r.n] : 0;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int c = s * 32 + lane;
+      const bool on = POST && c < TA && m0 + c < p.M;
+      r.mant[s] = on ? p.mant[m0 + c] : 0;
+      r.e[s] = on ? p.e[m0 + c] : 0;
+    }
     return r;
   }
 
-  // Row scales of the tile's activation rows into L1 while the MMAs still run.
-  static __device__ __forceinline__ void prefetch(const Row&, int group, int lane, int m0, const Params& p) {
-    if (!POST) return;
-#pragma unroll 1
-    for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
-      if (m0 + c0 >= p.M) break;
-      if (lane < 8 && m0 + c0 + lane < p.M) {
-        prefetch_l1(p.mant + m0 + c0 + lane);
-        prefetch_l1(p.e + m0 + c0 + lane);
-      }
-    }
-  }
+  static __device__ __forceinline__ void prefetch(const Row&, int, int, int, const Params&) {}
 
   static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
                                              bool has_k, const Params& p, const Row& r) {
@@ -83,17 +81,20 @@ struct Int8Epilogue {
       uint32_t a0[8], a1[8];
       tmem_ld8(tbase + c0, a0);
       tmem_ld8(tbase + TA + c0, a1);
+      const i64 mant_slot = POST ? lane_slot<NS>(r.mant, c0) : 0, e_slot = POST ? lane_slot<NS>(r.e, c0) : 0;
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int m = m0 + c0 + i;
+        const i64 mant_m = POST ? __shfl_sync(0xffffffffu, mant_slot, (c0 & 31) + i) : 0;
+        const i64 e_m = POST ? __shfl_sync(0xffffffffu, e_slot, (c0 & 31) + i) : 0;
         if (m < p.M && nok) {
           const int32_t v0 = has_k ? (int32_t)a0[i] : 0, v1 = has_k ? (int32_t)a1[i] : 0;
           if (POST) {
             const i64 acc = (i64)v0 + shl((i64)v1, 8);
             const i64 t = rsh_t((i64)((u64)acc * (u64)mc), p.fmsh);
             any_bad |= iabs(t) >= (1ll << 38);
-            p.y[(i64)m * p.N + n] = rsh_t((i64)((u64)t * (u64)p.mant[m]), 8 - p.e[m]);
+            p.y[(i64)m * p.N + n] = rsh_t((i64)((u64)t * (u64)mant_m), 8 - e_m);
           } else {
             p.c[(i64)m * p.N + n] = v0;
             p.c[((i64)p.M + m) * p.N + n] = v1;

@@ -157,7 +157,7 @@ __device__ __forceinline__ void limb_gemm_tile(const CUtensorMap* tmap_w, const 
     }
   } else {
     // ---- epilogue warps: row constants and L1 prefetches first, they overlap the main loop ----
-    const typename Epi::Row row = Epi::load_row(warp & 3, lane, n0, ep);
+    const typename Epi::Row row = Epi::load_row(warp & 3, (warp - 2) >> 2, lane, n0, m0, ep);
     Epi::prefetch(row, (warp - 2) >> 2, lane, m0, ep);
     bool ok = true;
     if (nkb > 0) ok = mbar_wait(&sh->acc_full, 0);
@@ -193,12 +193,19 @@ struct GemmSharedP {
   uint32_t abort_flag;
 };
 
-template <int NW, int NA, int TA, class Epi>
+// NBUF accumulator buffers in TMEM (2: the epilogue of a tile runs behind the MMAs of the next one; 1: tiles too wide
+// for two buffers, the MMAs of the next tile wait until the epilogue has read the accumulators out, while the TMA
+// warp already fills the ring for it). W_FASTEST: consecutive tiles walk the 128-row operand first.
+template <int NW, int NA, int TA, class Epi, int NBUF = 2, bool W_FASTEST = false>
 __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, const CUtensorMap* tmap_a, int n_tiles,
                                                      int m_tiles, int nkb, const typename Epi::Params& ep) {
   using Cfg = GemmCfg<NW, NA, TA>;
-  static_assert(2 * Cfg::COLS <= 512, "two accumulator buffers must fit in TMEM");
-  constexpr int TCOLS = 2 * Cfg::COLS <= 64 ? 64 : 2 * Cfg::COLS <= 128 ? 128 : 2 * Cfg::COLS <= 256 ? 256 : 512;
+  static_assert(NBUF == 1 || NBUF == 2, "one or two accumulator buffers");
+  static_assert(NBUF * Cfg::COLS <= 512, "the accumulator buffers must fit in TMEM");
+  constexpr int UCOLS = NBUF * Cfg::COLS;
+  constexpr int TCOLS = UCOLS <= 64 ? 64 : UCOLS <= 128 ? 128 : UCOLS <= 256 ? 256 : 512;
+  auto w_origin = [&](int tile) { return (W_FASTEST ? tile % n_tiles : tile / m_tiles) * WROWS; };
+  auto a_origin = [&](int tile) { return (W_FASTEST ? tile / n_tiles : tile % m_tiles) * TA; };
   extern __shared__ uint8_t smem_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmSharedP* sh = reinterpret_cast<GemmSharedP*>(ring + Cfg::STAGES * Cfg::STAGE_BYTES);
@@ -212,7 +219,7 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NBUF; ++b) {
       mbar_init(&sh->acc_full[b], 1);
       mbar_init(&sh->acc_empty[b], 4 * EPI_GROUPS);
     }
@@ -238,7 +245,7 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
       int it = 0;            // global stage counter
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const int n0 = (tile / m_tiles) * WROWS, m0 = (tile % m_tiles) * TA;
+        const int n0 = w_origin(tile), m0 = a_origin(tile);
         for (int i = 0; i < nkb && ok; ++i, ++it) {
           const int s = it % Cfg::STAGES, round = it / Cfg::STAGES;
           if (round > 0) ok = mbar_wait(&sh->empty[s], (round - 1) & 1);
@@ -265,7 +272,7 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
       int it = 0, tcount = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++tcount) {
-        const int buf = tcount & 1, use = tcount >> 1;
+        const int buf = tcount % NBUF, use = tcount / NBUF;
         if (use > 0) ok = mbar_wait(&sh->acc_empty[buf], (use - 1) & 1);   // epilogue has drained this buffer
         if (!ok) break;
         tc_fence_after();
@@ -309,20 +316,31 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
     int tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++tcount) {
-      const int buf = tcount & 1, use = tcount >> 1;
-      const int n0 = (tile / m_tiles) * WROWS, m0 = (tile % m_tiles) * TA;
+      const int buf = tcount % NBUF, use = tcount / NBUF;
+      const int n0 = w_origin(tile), m0 = a_origin(tile);
       // row constants and L1 prefetches before the wait: they overlap the MMAs of this tile
-      const typename Epi::Row row = Epi::load_row(warp & 3, lane, n0, ep);
+      const typename Epi::Row row = Epi::load_row(warp & 3, (warp - 2) >> 2, lane, n0, m0, ep);
       Epi::prefetch(row, (warp - 2) >> 2, lane, m0, ep);
       if (ok) ok = mbar_wait(&sh->acc_full[buf], use & 1);
       ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sh->abort_flag) == 0);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      Epi::run(tmem + buf * Cfg::COLS, warp & 3, (warp - 2) >> 2, lane, n0, m0, nkb > 0, ep, row);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
+      if constexpr (NBUF == 1) {
+        // One buffer: read the accumulators out into registers, hand the buffer back to the MMA warp at once, and do
+        // the arithmetic and the stores behind the MMAs of the next tile.
+        typename Epi::Drained acc;
+        Epi::drain(tmem, warp & 3, (warp - 2) >> 2, lane, n0, m0, nkb > 0, ep, acc);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->acc_empty[0]);
+        Epi::finish(acc, warp & 3, (warp - 2) >> 2, lane, n0, m0, ep, row);
+      } else {
+        Epi::run(tmem + buf * Cfg::COLS, warp & 3, (warp - 2) >> 2, lane, n0, m0, nkb > 0, ep, row);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
+      }
     }
     if (!ok && lane == 0) atomicAdd(&g_wait_timeouts, 1);
   }

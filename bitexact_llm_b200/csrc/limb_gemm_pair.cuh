@@ -212,11 +212,14 @@ __device__ __forceinline__ void limb_gemm_pair_persistent(const CUtensorMap* tma
       const uint32_t acc_empty1 = mapa_shared(smem_u32(&sh->acc_empty[1]), 0);
       auto hand_back = [&](int buf) {
         // Column blocks no accumulate-free MMA writes start the next tile at zero. A warp clears exactly the columns
-        // it reads in Epi::run (activation rows c0 .. c0 + 7 of its group), so no warp clears what another still reads.
+        // it reads in Epi::run (the chunks of Epi::CW activation rows of its group), so no warp clears what another still reads.
         if (Cfg::ZERO_COL0 < Cfg::COLS) {
-          for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS)
+          for (int c0 = group * Epi::CW; c0 < TA; c0 += Epi::CW * EPI_GROUPS)
 #pragma unroll
-            for (int b = NA; b < Cfg::NBLK; ++b) tmem_st8_fill(tmem + lane_base + buf * Cfg::COLS + b * TA + c0, 0u);
+            for (int b = NA; b < Cfg::NBLK; ++b) {
+              const uint32_t at = tmem + lane_base + buf * Cfg::COLS + b * TA + c0;
+              if constexpr (Epi::CW == 8) tmem_st8_fill(at, 0u); else tmem_st4_fill(at, 0u);
+            }
           tmem_st_wait();
         }
         tc_fence_before();
@@ -230,7 +233,7 @@ __device__ __forceinline__ void limb_gemm_pair_persistent(const CUtensorMap* tma
       for (int tile = pair; tile < total; tile += npairs, ++tcount) {
         const int buf = tcount & 1, use = tcount >> 1;
         const int n0 = ((tile / m_tiles) * 2 + (int)rank) * WROWS, m0 = (tile % m_tiles) * TA;
-        const typename Epi::Row row = Epi::load_row(quarter, lane, n0, ep);      // overlaps the tile's MMAs
+        const typename Epi::Row row = Epi::load_row(quarter, group, lane, n0, m0, ep);      // overlaps the tile's MMAs
         Epi::prefetch(row, group, lane, m0, ep);
         if (ok) ok = mbar_wait(&sh->acc_full[buf], use & 1);
         ok = ok && (*reinterpret_cast<volatile uint32_t*>(&sh->abort_flag) == 0);

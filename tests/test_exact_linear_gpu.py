@@ -32,8 +32,10 @@ def test_golden_linear_with_residual_and_extreme_shifts():
     z = np.load(os.path.join(GOLD, "exact_ops.npz"))
     dec = {k: z["lin_" + k] for k in ("limbs", "g", "d", "rr", "rc", "rv")}
     fl = _lin(dec)
-    # negative: the persistent kernel; 200 + rows: split-K over a cluster of CTAs; 400 + rows: CTA pairs (cta_group::2)
-    for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48, 216, 232, 264, 416, 432, 448, 516, 532, 548, 564, 580):
+    # negative: the persistent kernel; 200 + rows: split-K over a cluster of CTAs; 400 + rows: CTA pairs (cta_group::2);
+    # 500 / 600 + weight rows: activation rows on the MMA M side (CTA pairs / one CTA)
+    for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48, 216, 232, 264, 416, 432, 448, 516, 532, 548, 564, 580,
+                 616, 632, 648, 664, 680):
         y, flag = _run(fl, z["lin_q"], z["lin_sh"], True, tile)
         assert np.array_equal(y, z["lin_y"]), tile
         assert flag == bool(z["lin_flag"])
@@ -62,7 +64,8 @@ def test_seeded_shapes_against_oracle(M, N, K):
     sh = rng.randint(-45, -8, M).astype(np.int64)
     want, wflag = ox.linear(q, sh, dec, checked=True)
     fl = _lin(dec)
-    for tile in (None, 16, 80, -48, 216, 232, 264, 416, 432, 448) if M > 16 else (None, 64, -16, 216, 264, 416, 448, 516, 548, 580):
+    for tile in (None, 16, 80, -48, 216, 232, 264, 416, 432, 448, 648, 680) if M > 16 else \
+            (None, 64, -16, 216, 264, 416, 448, 516, 548, 580, 616, 664):
         y, flag = _run(fl, q, sh, True, tile)
         assert np.array_equal(y, want), (tile, int((y != want).sum()))
         assert flag == wflag
@@ -81,10 +84,42 @@ def test_persistent_kernel_many_tiles_per_cta():
     sh = rng.randint(-45, -8, M).astype(np.int64)
     want, wflag = ox.linear(q, sh, dec, checked=True)
     fl = _lin(dec)
-    for tile in (-16, -32, -48, None, 416, 432, 448, 532, 548, 564, 580):
+    for tile in (-16, -32, -48, None, 416, 432, 448, 532, 548, 564, 580, 632, 648, 664, 680):
         y, flag = _run(fl, q, sh, True, tile)
         assert np.array_equal(y, want), (tile, int((y != want).sum()))
         assert flag == wflag
+
+
+def test_rounding_rule_boundaries_of_the_short_form():
+    """The epilogue takes a short form of the rounding rule when a whole warp shifts right by 1 .. 31 bits with
+    k >= d and moderate T, B, and the two-word rule otherwise: shifts on both sides of every boundary (k = d, k = d - 1,
+    k = 0, 1, 31, 32), residual terms below and above 2^60, extreme T; warps with all rows alike and mixed warps."""
+    rng = np.random.RandomState(11)
+    M, N, K = 70, 512, 384
+    W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
+    W[5, :] = 8355711
+    W[6, :] = -8355711
+    q = rng.randint(-(1 << 22), (1 << 22) + 1, (M, K)).astype(np.int64)
+    q[3, :] = 1 << 22
+    q[4, :] = -(1 << 22)
+    limbs = np.stack([l.astype(np.int8) for l in ox.split_limbs(W, 3)[0]])
+    n = np.arange(N)
+    d = np.where(n < 256, n % 31, (n // 32) % 31).astype(np.int64)     # rows 256..: one d per warp
+    for s0, off in ((-10, 0), (-25, 2), (-39, 14), (-41, -6)):
+        e = -((n // 32) % 4) * 3 - off
+        g = (-24 - s0 + e).astype(np.int64)                            # k - d = (s0 - sh) - e
+        sh = (s0 + (np.arange(M) % 7) - 3).astype(np.int64)            # k - d in -3 .. 3 (+ 0, 3, 6, 9 by warp, + off)
+        rr = np.arange(0, N, 9, dtype=np.int64)
+        rv = rng.randint(-(1 << 20), 1 << 20, len(rr)).astype(np.int64)
+        rv[::4] = (1 << 37) + 12345                                    # |B| up to 2^59
+        rv[1::8] = -(1 << 40)                                          # |B| up to 2^62: outside the short form
+        dec = {"limbs": limbs, "g": g, "d": d, "rr": rr, "rc": rng.randint(0, K, len(rr)).astype(np.int64), "rv": rv}
+        want, wflag = ox.linear(q, sh, dec, checked=True)
+        fl = _lin(dec)
+        for tile in (None, 16, 32, 48, 64, 80, -48, 216, 448, 548, 648, 664, 680):
+            y, flag = _run(fl, q, sh, True, tile)
+            assert np.array_equal(y, want), (s0, tile, int((y != want).sum()))
+            assert flag == wflag, (s0, tile)
 
 
 def test_bf16_weights_config_one_shape():
