@@ -460,10 +460,20 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
     }
     if (ta <= 48 && n_tiles * ((M + ta - 1) / ta) > 2 * 148) persistent = true;
     if (ta == 64 && K <= 4096 && n_tiles * ((M + 47) / 48) > 2 * 148) { ta = 48; persistent = true; }
-    // Long tile lists of batches that fill blocks of 128 rows at least as well as tiles of 48: the activation rows
-    // go to the MMA M side (no ragged sixth tile at 256 rows, warp-uniform residual lists). Measured at M = 256:
-    // gate / up 80 -> 70 us, LM head 519 -> 468 us.
-    if (persistent && ta == 48 && M > WROWS && ((M + WROWS - 1) / WROWS) * WROWS <= ((M + 47) / 48) * 48) ta = 648;
+    // Long tile lists of batches that fill blocks of 128 rows about as well as tiles of 48: the activation rows go
+    // to the MMA M side, 64 weight rows per tile (no ragged sixth tile at 256 rows, warp-uniform residual lists,
+    // wider MMAs). Measured, gate / up and LM head: 80 -> 67 us and 519 -> 429 us at M = 256, 46 -> 42 us and
+    // 277 -> 238 us at M = 128, gate / up 878 -> 809 us at M = 4096.
+    if (persistent && ta == 48 && M >= WROWS) {
+      const long ra = ((M + WROWS - 1) / WROWS) * (long)WROWS, rw = ((M + 47) / 48) * 48L;
+      if (10 * ra <= 11 * rw) ta = 664;
+    }
+  }
+  int want_split = 0;                 // 10000 S + 200 + rows: split-K over clusters of exactly S CTAs
+  if (ta >= 10000) {
+    want_split = ta / 10000;
+    ta %= 10000;
+    if (ta < 200 || ta >= 300 || (want_split != 2 && want_split != 4 && want_split != 8)) return BX_EARG;
   }
   // Split-K over a cluster of CTAs (200 + activation rows per tile asks for it; automatic for small batches whose
   // tile list covers less than half of the SMs): as many K slices as keep the CTA count within the 148 SMs.
@@ -512,11 +522,17 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
   int split = 0;
   if (ta >= 200) {
     ta -= 200;
-    split = SPLITK_MAX;
+    split = want_split ? want_split : SPLITK_MAX;
     if (ta != 16 && ta != 32 && ta != 64) return BX_EARG;
   } else if (tile_rows == 0 && !persistent && M <= 128 && (ta == 16 || ta == 32 || ta == 64)) {
     const long tiles = ((N + WROWS - 1) / WROWS) * ((M + ta - 1) / ta);
     if (tiles * 2 <= 148) split = (int)(148 / tiles);
+  } else if (tile_rows == 0 && !persistent && M > 128 && K >= 8192 &&
+             ((N + WROWS - 1) / WROWS) * (long)((M + 63) / 64) * 2 <= 148) {
+    // Long K, few tiles (the down projection at a batch of 256): 64-row tiles with K split over CTA pairs read less
+    // shared memory per product than one wave of 32-row tiles (measured 47 -> 39 us).
+    ta = 64;
+    split = 2;
   }
   if (split > 0) {
     const int nkb = (K + BKB - 1) / BKB;

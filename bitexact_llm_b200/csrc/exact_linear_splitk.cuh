@@ -76,12 +76,16 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   const uint32_t tmem = sh->tmem_base;
   bool acc_ok = false;                                                // epilogue warps: accumulators complete
   // epilogue threads: constants of weight row n (see ExactEpilogue), loaded before the accumulators exist
-  constexpr int RMAX = 4;
+  constexpr int RMAX = 2;
   bool nok = false;
   int d = 0, cnt = 0, wcnt = 0;
   i64 gd = 0;
-  int ecr[RMAX] = {0, 0, 0, 0};
-  i64 evr[RMAX] = {0, 0, 0, 0};
+  int ecr[RMAX] = {0, 0};
+  i64 evr[RMAX] = {0, 0};
+  constexpr int NS = (TA + 31) / 32;
+  i64 shv[NS];                                                        // the tile's row exponents, lane-held
+#pragma unroll
+  for (int s = 0; s < NS; ++s) shv[s] = 0;
 
   if (warp == 0) {
     if (lane == 0 && !dead) {
@@ -164,6 +168,11 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         }
       }
       wcnt = __reduce_max_sync(0xffffffffu, cnt);                      // longest list in the warp (uniform)
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const int c = s * 32 + lane;
+        if (c < TA && m0 + c < ep.M) shv[s] = ep.sh[m0 + c];
+      }
     }
     // ---- epilogue warps: wait for this CTA's accumulators ----
     bool ok = !dead;
@@ -199,10 +208,7 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       for (int i = 0; i < 8; ++i) {
         const int c = c0 + i;
         if (m0 + c >= ep.M) break;
-        i64 T = 0;
-        if (acc_ok)
-          T = (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8) + shl((i64)(int32_t)acc[2][i], 16) +
-              shl((i64)(int32_t)acc[3][i], 24) + shl((i64)(int32_t)acc[4][i], 32);
+        const i64 T = acc_ok ? join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]) : 0;
         i64* dst = cluster.map_shared_rank(partial, c % S);
         dst[((size_t)rank * own + c / S) * WROWS + row] = T;
       }
@@ -217,21 +223,22 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     for (int k = group; k < own; k += EPI_GROUPS) {
       const int c = rank + k * S;
       const int m = m0 + c;
-      if (c >= TA || m >= ep.M || !nok) continue;
+      if (c >= TA || m >= ep.M) break;                                // warp-uniform
       i64 T = 0;
       for (int r = 0; r < S; ++r) T += partial[((size_t)r * own + k) * WROWS + row];
       i64 B = 0;
-      if (wcnt > 0) {
+      if (wcnt > 0 && nok) {
 #pragma unroll
         for (int j = 0; j < RMAX; ++j)
           if (j < wcnt && j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
         for (int j = RMAX; j < cnt; ++j)
           B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)n * ep.R + j]] * ep.ev[(i64)n * ep.R + j];
       }
+      const i64 pv = __shfl_sync(0xffffffffu, lane_slot<NS>(shv, c), c & 31) + gd;
       bool bad;
-      const i64 yv = round_shift_hl(T, B, d, ep.sh[m] + gd, bad);
+      const i64 yv = round_rule_warp(T, B, d, pv, nok, bad);
       any_bad |= bad;
-      ep.y[(i64)m * ep.N + n] = yv;
+      if (nok) ep.y[(i64)m * ep.N + n] = yv;
     }
     if (ep.checked && any_bad) *ep.flag = 1;
   }

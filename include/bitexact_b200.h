@@ -63,7 +63,11 @@ int bx_i8_tensor_peak(int iters, int repeats, double* tops, void* stream);
  *              that tile size on the persistent kernel (one CTA per SM, overlapped epilogue); 216, 232, 264 select
  *              16, 32, 64 rows with the K dimension split over a cluster of up to 8 CTAs (partial sums through
  *              distributed shared memory), the automatic choice for M <= 128 when the tile list covers less than
- *              half of the SMs. No effect on results.
+ *              half of the SMs (10000 S + 2xx: clusters of exactly S = 2, 4 or 8 CTAs); 416, 432, 448: that many
+ *              activation rows on CTA pairs (tcgen05 cta_group::2, 256 weight rows per pair); 516 .. 580 and
+ *              616 .. 680 (steps of 16): the ACTIVATION rows on the MMA M side and that many weight rows per tile,
+ *              on CTA pairs / on one CTA (the automatic choice for long tile lists of batches of 128 rows and
+ *              more: 664). No effect on results.
  */
 size_t bx_exact_linear_scratch_bytes(int M, int K);
 int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,

@@ -133,6 +133,38 @@ def gemmr(args):
     return out
 
 
+def gemm8(args):
+    """int8-mode fused linear (GEMM + post) on the model's projections: CUDA-graph timing over weight sets larger than
+    L2. int8 ops = 2 * 2 * M * N * K (two activation limbs)."""
+    lib, dev = nv.lib(), "cuda"
+    g = torch.Generator().manual_seed(0)
+    out = []
+    for M in [int(v) for v in args.m.split(",")]:
+        for name, (N, K) in FUSED.items():
+            if (name == "lm" and args.shapes != "all") or (args.proj and name != args.proj):
+                continue
+            nsets = max(2, (200 << 20) // (N * K) + 1)
+            ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, generator=g).to(dev) for _ in range(nsets)]
+            a = torch.randint(-128, 128, (2 * M, K), dtype=torch.int8, generator=g).to(dev)
+            mul = torch.randint(1 << 20, 1 << 24, (N,), generator=g).to(dev)
+            mant = torch.randint(1 << 7, 1 << 8, (M,), generator=g).to(dev)
+            e = torch.randint(-12, -4, (M,), generator=g).to(dev)
+            y = torch.empty(M, N, dtype=torch.long, device=dev)
+            fl = torch.zeros(1, dtype=torch.int32, device=dev)
+
+            def run(i):
+                nv.check(lib.bx_int8_linear_post(a.data_ptr(), ws[i].data_ptr(), mul.data_ptr(), 30, mant.data_ptr(),
+                                                 e.data_ptr(), y.data_ptr(), fl.data_ptr(), M, N, K, 0, args.tile,
+                                                 nv.stream()), "bx_int8_linear_post")
+            ms = _graph_time(run, nsets, args.iters)
+            rec = {"kernel": "int8_linear", "proj": name, "M": M, "N": N, "K": K, "residual": "residual",
+                   "us": ms * 1e3, "int8_tops": 4.0 * M * N * K / ms / 1e9}
+            out.append(rec)
+            print(json.dumps(rec), flush=True)
+            del ws
+    return out
+
+
 def attn(args):
     from bitexact_llm_b200.exact.consts import exp2_table
     lib, dev = nv.lib(), "cuda"
@@ -383,7 +415,7 @@ def stages(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemmr", "attn", "stages", "prefill", "prompt", "bmm"])
+    ap.add_argument("what", choices=["gemm", "gemmr", "gemm8", "attn", "stages", "prefill", "prompt", "bmm"])
     ap.add_argument("--m", default="1,16,256,4096")
     ap.add_argument("--tile", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -398,7 +430,7 @@ def main():
     ap.add_argument("--eager", action="store_true", help="gemmr: one plain launch per weight set, no timing")
     ap.add_argument("--chunk", type=int, default=4096, help="prompt: token rows per forward call")
     args = ap.parse_args()
-    {"gemm": gemm, "gemmr": gemmr, "attn": attn, "stages": stages, "prefill": prefill, "prompt": prompt, "bmm": bmm_bench}[args.what](args)
+    {"gemm": gemm, "gemmr": gemmr, "gemm8": gemm8, "attn": attn, "stages": stages, "prefill": prefill, "prompt": prompt, "bmm": bmm_bench}[args.what](args)
     if nv.device_status() != 0:
         raise SystemExit("device-side wait timed out")
 
