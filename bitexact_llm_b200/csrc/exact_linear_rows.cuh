@@ -97,10 +97,8 @@ struct RowsEpilogue {
       any_bad |= bad;
     }
     if (r.mok) {
-      if (vec && n0 + c0 + CW <= p.N) {
-        longlong2* dst = reinterpret_cast<longlong2*>(yrow + n0 + c0);
-#pragma unroll
-        for (int i = 0; i < CW / 2; ++i) dst[i] = make_longlong2(out[2 * i], out[2 * i + 1]);
+      if (vec && n0 + c0 + CW <= p.N) {                 // one full 32-byte sector per thread
+        st_global_v4(yrow + n0 + c0, out[0], out[1], out[2], out[3]);
       } else {
 #pragma unroll
         for (int i = 0; i < CW; ++i)
@@ -113,7 +111,7 @@ struct RowsEpilogue {
                                              const ExactEpiParams& p, const Row& r) {
     const int32_t* qrow = p.q + (i64)(r.mok ? r.m : 0) * p.ldq;
     i64* yrow = reinterpret_cast<i64*>(p.y) + (i64)(r.mok ? r.m : 0) * p.N;
-    const bool vec = (p.N & 1) == 0;
+    const bool vec = (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 31) == 0;
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
@@ -159,7 +157,7 @@ struct RowsEpilogue {
                                                 const Row& r) {
     const int32_t* qrow = p.q + (i64)(r.mok ? r.m : 0) * p.ldq;
     i64* yrow = reinterpret_cast<i64*>(p.y) + (i64)(r.mok ? r.m : 0) * p.N;
-    const bool vec = (p.N & 1) == 0;
+    const bool vec = (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 31) == 0;
     bool any_bad = false;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
