@@ -13,6 +13,7 @@
 #include "exact_linear_splitk.cuh"
 #include "exact_linear_rows.cuh"
 #include "int8_linear.cuh"
+#include "int8_linear_splitk.cuh"
 #include "int8_stages.cuh"
 #include "elementwise.cuh"
 #include "paged_attention.cuh"
@@ -311,6 +312,35 @@ int launch_int8_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const I
   return launched(1);
 }
 
+template <int TA>
+int launch_int8_splitk(const CUtensorMap& mw, const CUtensorMap& ma, const Int8EpiParams& ep, int K, int split,
+                       cudaStream_t st) {
+  using Cfg = GemmCfg<1, 2, TA>;
+  static_assert((TA + SPLITK_MAX - 1) * WROWS * 8 <= Cfg::STAGES * Cfg::STAGE_BYTES, "partial columns fit in the ring");
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(int8_linear_splitk_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int m_tiles = (ep.M + TA - 1) / TA;
+  const int n_tiles = (ep.N + WROWS - 1) / WROWS;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(m_tiles * n_tiles * split), 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, int8_linear_splitk_kernel<TA>, mw, ma, ep, K, m_tiles) != cudaSuccess) return BX_ELAUNCH;
+  return launched(1);
+}
+
 template <bool POST>
 int run_int8(const int8_t* a, const int8_t* w, const Int8EpiParams& ep, int K, int tile_rows, cudaStream_t st) {
   const int M = ep.M, N = ep.N;
@@ -324,15 +354,49 @@ int run_int8(const int8_t* a, const int8_t* w, const Int8EpiParams& ep, int K, i
   } else if (ta == 0) {
     const long n_tiles = (N + WROWS - 1) / WROWS;
     ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : (n_tiles * ((M + 127) / 128) >= 90 ? 128 : 64);
-    // 64-row tiles that would cover less than half of the SMs: 32-row tiles (wo / wd at 256 rows: 12.7 -> 10.6 us,
-    // 28.2 -> 26.3 us)
-    if (ta == 64 && M > 64 && n_tiles * ((M + 63) / 64) * 2 <= 148) ta = 32;
+    // 64-row tiles that would cover less than half of the SMs: with a short K, 32-row tiles (wo at 256 rows:
+    // 12.7 -> 10.6 us); with a long K the 64-row tiles stay and K is split over clusters below
+    if (ta == 64 && M > 64 && K < 4096 && n_tiles * ((M + 63) / 64) * 2 <= 148) ta = 32;
     // more tiles than SMs: one CTA per SM with the epilogue of a tile behind the MMAs of the next
     persistent = n_tiles * ((M + ta - 1) / ta) > 148;
+  }
+  // Split-K over a cluster of CTAs (fused post only): 200 + rows (10000 S + 200 + rows: clusters of exactly S) asks
+  // for it; automatic when the tile list covers less than half of the SMs and K is long enough for two K blocks per
+  // slice, with as many slices (2, 4 or 8) as keep the CTA count within the SMs.
+  int split = 0;
+  if (POST) {
+    int want = 0;
+    if (ta >= 10000) { want = ta / 10000; ta %= 10000; if (want != 2 && want != 4 && want != 8) return BX_EARG; }
+    if (ta >= 200 && ta < 300) {
+      ta -= 200;
+      if (ta != 16 && ta != 32 && ta != 64) return BX_EARG;
+      split = want ? want : SPLITK_MAX;
+    } else if (want) {
+      return BX_EARG;
+    } else if (tile_rows == 0 && !persistent && (ta == 16 || ta == 32 || ta == 64)) {
+      const long tiles = ((N + WROWS - 1) / WROWS) * (long)((M + ta - 1) / ta);
+      if (tiles * 2 <= 148) split = (int)(148 / tiles);
+      if (split > 8) split = 8;
+    }
+    if (split > 0) {
+      const int nkb = (K + BKB - 1) / BKB;
+      if (split > nkb / 2) split = nkb / 2;
+      while (split & (split - 1)) --split;
+      if (tile_rows == 0 && split > 4) split = 4;
+    }
   }
   CUtensorMap mw, ma;
   if (!make_map(&mw, w, (uint64_t)K, (uint64_t)N, 1, WROWS)) return BX_ELAUNCH;
   if (!make_map(&ma, a, (uint64_t)K, (uint64_t)M, 2, (uint32_t)ta)) return BX_ELAUNCH;
+  if constexpr (POST) {
+    if (split >= 2) {
+      switch (ta) {
+        case 16: return launch_int8_splitk<16>(mw, ma, ep, K, split, st);
+        case 32: return launch_int8_splitk<32>(mw, ma, ep, K, split, st);
+        default: return launch_int8_splitk<64>(mw, ma, ep, K, split, st);
+      }
+    }
+  }
   if (persistent) {
     switch (ta) {
       case 16: return launch_int8_persistent<16, POST>(mw, ma, ep, K, st);

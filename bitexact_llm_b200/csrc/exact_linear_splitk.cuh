@@ -28,12 +28,79 @@ __host__ __device__ constexpr int splitk_limit() {
   return SPLITK_MAX;
 }
 
+// The exact-mode policy of limb_splitk: what an epilogue thread knows about its weight row before the accumulators
+// exist, how the column blocks join, and the tail (sparse residual, one rounding, flag) of an owned output.
 template <int TA>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
-                           const ExactEpiParams ep, int K, int m_tiles) {
+struct ExactSplitEpi {
+  using Params = ExactEpiParams;
+  static constexpr int NW = 3, NA = 3, RMAX = 2, NS = (TA + 31) / 32;
+  struct Consts {
+    int n, d, cnt, wcnt;
+    bool nok;
+    i64 gd;
+    int ecr[RMAX];
+    i64 evr[RMAX];
+    i64 shv[NS];                                                      // the tile's row exponents, lane-held
+  };
+
+  static __device__ __forceinline__ Consts load(int n0, int m0, int quarter, int group, int lane, int rank, int S,
+                                                const Params& ep) {
+    Consts c;
+    c.n = n0 + quarter * 32 + lane;
+    c.nok = c.n < ep.N;
+    c.d = c.nok ? (int)ep.d[c.n] : 0;
+    c.gd = c.nok ? ep.g[c.n] - (i64)c.d + FR : 0;
+    c.cnt = (c.nok && ep.cnt) ? ep.cnt[c.n] : 0;
+#pragma unroll
+    for (int j = 0; j < RMAX; ++j) {
+      c.ecr[j] = 0;
+      c.evr[j] = 0;
+      if (j < c.cnt) {
+        c.ecr[j] = ep.ec[(i64)c.n * ep.R + j];
+        c.evr[j] = ep.ev[(i64)c.n * ep.R + j];
+      }
+    }
+    c.wcnt = __reduce_max_sync(0xffffffffu, c.cnt);                    // longest list in the warp (uniform)
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int col = s * 32 + lane;
+      c.shv[s] = (col < TA && m0 + col < ep.M) ? ep.sh[m0 + col] : 0;
+    }
+    return c;
+  }
+
+  static __device__ __forceinline__ i64 join(const uint32_t (&acc)[5][8], int i) {
+    return join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]);
+  }
+
+  // Output (m, c.n) of tile column col from the summed limb sums T. All 32 lanes of a warp call it together.
+  static __device__ __forceinline__ void final(i64 T, int col, int m, const Consts& c, const Params& ep, bool& any_bad) {
+    i64 B = 0;
+    if (c.wcnt > 0 && c.nok) {
+#pragma unroll
+      for (int j = 0; j < RMAX; ++j)
+        if (j < c.wcnt && j < c.cnt) B += (i64)ep.q[(i64)m * ep.ldq + c.ecr[j]] * c.evr[j];
+      for (int j = RMAX; j < c.cnt; ++j)
+        B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)c.n * ep.R + j]] * ep.ev[(i64)c.n * ep.R + j];
+    }
+    const i64 pv = __shfl_sync(0xffffffffu, lane_slot<NS>(c.shv, col), col & 31) + c.gd;
+    bool bad;
+    const i64 yv = round_rule_warp(T, B, c.d, pv, c.nok, bad);
+    any_bad |= bad;
+    if (c.nok) ep.y[(i64)m * ep.N + c.n] = yv;
+  }
+
+  static __device__ __forceinline__ void finish(bool any_bad, const Params& ep) {
+    if (ep.checked && any_bad) *ep.flag = 1;
+  }
+};
+
+template <int TA, class Epi>
+__device__ __forceinline__ void limb_splitk(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
+                                            const typename Epi::Params& ep, int K, int m_tiles) {
   namespace cg = cooperative_groups;
-  using Cfg = GemmCfg<3, 3, TA>;
+  constexpr int NW = Epi::NW, NA = Epi::NA, NBLK = NW + NA - 1;
+  using Cfg = GemmCfg<NW, NA, TA>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmShared* sh = reinterpret_cast<GemmShared*>(ring + Cfg::STAGES * Cfg::STAGE_BYTES);
@@ -75,17 +142,7 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
   bool acc_ok = false;                                                // epilogue warps: accumulators complete
-  // epilogue threads: constants of weight row n (see ExactEpilogue), loaded before the accumulators exist
-  constexpr int RMAX = 2;
-  bool nok = false;
-  int d = 0, cnt = 0, wcnt = 0;
-  i64 gd = 0;
-  int ecr[RMAX] = {0, 0};
-  i64 evr[RMAX] = {0, 0};
-  constexpr int NS = (TA + 31) / 32;
-  i64 shv[NS];                                                        // the tile's row exponents, lane-held
-#pragma unroll
-  for (int s = 0; s < NS; ++s) shv[s] = 0;
+  typename Epi::Consts cst = {};                                     // epilogue threads: loaded before the wait
 
   if (warp == 0) {
     if (lane == 0 && !dead) {
@@ -113,9 +170,9 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   } else if (warp == 1) {
     if (lane == 0 && !dead) {
       // ---- MMA issue (as limb_gemm_tile) ----
-      constexpr uint32_t ID_ALL = umma_idesc_i8(3 * TA);
+      constexpr uint32_t ID_ALL = umma_idesc_i8(NA * TA);
       constexpr uint32_t ID_ONE = umma_idesc_i8(TA);
-      constexpr uint32_t ID_REST = umma_idesc_i8(2 * TA);
+      constexpr uint32_t ID_REST = umma_idesc_i8(NA > 1 ? (NA - 1) * TA : TA);
       bool ok = true;
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % Cfg::STAGES;
@@ -131,14 +188,14 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
           if (i == 0 && ks == 0) {
             umma_i8(tmem, umma_desc_sw128(wbase + koff), adesc, ID_ALL, 0);
 #pragma unroll
-            for (int j = 1; j < 3; ++j) {
+            for (int j = 1; j < NW; ++j) {
               const uint64_t wdesc = umma_desc_sw128(wbase + j * (WROWS * BKB) + koff);
-              umma_i8(tmem + (j + 2) * TA, wdesc, umma_desc_sw128(abase + 2 * TA * BKB + koff), ID_ONE, 0);
-              umma_i8(tmem + j * TA, wdesc, adesc, ID_REST, 1);
+              umma_i8(tmem + (j + NA - 1) * TA, wdesc, umma_desc_sw128(abase + (NA - 1) * TA * BKB + koff), ID_ONE, 0);
+              if (NA > 1) umma_i8(tmem + j * TA, wdesc, adesc, ID_REST, 1);
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 3; ++j)
+            for (int j = 0; j < NW; ++j)
               umma_i8(tmem + j * TA, umma_desc_sw128(wbase + j * (WROWS * BKB) + koff), adesc, ID_ALL, 1);
           }
         }
@@ -152,28 +209,9 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
     }
   } else {
-    // ---- epilogue warps: the per-row constants and the residual list of weight row n do not depend on the
-    //      accumulators; at decode sizes this kernel is a latency chain, so their loads start before the wait ----
-    {
-      const int n = n0 + (warp & 3) * 32 + lane;
-      nok = n < ep.N;
-      d = nok ? (int)ep.d[n] : 0;
-      gd = nok ? ep.g[n] - (i64)d + FR : 0;
-      cnt = (nok && ep.cnt) ? ep.cnt[n] : 0;
-#pragma unroll
-      for (int j = 0; j < RMAX; ++j) {
-        if (j < cnt) {
-          ecr[j] = ep.ec[(i64)n * ep.R + j];
-          evr[j] = ep.ev[(i64)n * ep.R + j];
-        }
-      }
-      wcnt = __reduce_max_sync(0xffffffffu, cnt);                      // longest list in the warp (uniform)
-#pragma unroll
-      for (int s = 0; s < NS; ++s) {
-        const int c = s * 32 + lane;
-        if (c < TA && m0 + c < ep.M) shv[s] = ep.sh[m0 + c];
-      }
-    }
+    // ---- epilogue warps: what does not depend on the accumulators (per-row constants, lists, row scales) is loaded
+    //      first; at decode sizes this kernel is a latency chain ----
+    cst = Epi::load(n0, m0, warp & 3, (warp - 2) >> 2, lane, rank, S, ep);
     // ---- epilogue warps: wait for this CTA's accumulators ----
     bool ok = !dead;
     if (ok && nkb > 0) ok = mbar_wait(&sh->acc_full, 0);
@@ -198,17 +236,17 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 #pragma unroll 1
     for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
       if (m0 + c0 >= ep.M) break;
-      uint32_t acc[5][8];
+      uint32_t acc[NBLK][8];
       if (acc_ok) {
 #pragma unroll
-        for (int b = 0; b < 5; ++b) tmem_ld8(tbase + b * TA + c0, acc[b]);
+        for (int b = 0; b < NBLK; ++b) tmem_ld8(tbase + b * TA + c0, acc[b]);
         tmem_ld_wait();
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int c = c0 + i;
         if (m0 + c >= ep.M) break;
-        const i64 T = acc_ok ? join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]) : 0;
+        const i64 T = acc_ok ? Epi::join(acc, i) : 0;
         i64* dst = cluster.map_shared_rank(partial, c % S);
         dst[((size_t)rank * own + c / S) * WROWS + row] = T;
       }
@@ -217,8 +255,7 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   cluster.sync();                                                     // every partial column is in its owner's ring
 
   if (warp >= 2) {
-    // ---- the columns this CTA owns: sum of the S partials, then the epilogue of exact_linear_kernel ----
-    const int n = n0 + row;
+    // ---- the columns this CTA owns: sum of the S partials, then the usual tail of the epilogue ----
     bool any_bad = false;
     for (int k = group; k < own; k += EPI_GROUPS) {
       const int c = rank + k * S;
@@ -226,21 +263,9 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       if (c >= TA || m >= ep.M) break;                                // warp-uniform
       i64 T = 0;
       for (int r = 0; r < S; ++r) T += partial[((size_t)r * own + k) * WROWS + row];
-      i64 B = 0;
-      if (wcnt > 0 && nok) {
-#pragma unroll
-        for (int j = 0; j < RMAX; ++j)
-          if (j < wcnt && j < cnt) B += (i64)ep.q[(i64)m * ep.ldq + ecr[j]] * evr[j];
-        for (int j = RMAX; j < cnt; ++j)
-          B += (i64)ep.q[(i64)m * ep.ldq + ep.ec[(i64)n * ep.R + j]] * ep.ev[(i64)n * ep.R + j];
-      }
-      const i64 pv = __shfl_sync(0xffffffffu, lane_slot<NS>(shv, c), c & 31) + gd;
-      bool bad;
-      const i64 yv = round_rule_warp(T, B, d, pv, nok, bad);
-      any_bad |= bad;
-      if (nok) ep.y[(i64)m * ep.N + n] = yv;
+      Epi::final(T, c, m, cst, ep, any_bad);
     }
-    if (ep.checked && any_bad) *ep.flag = 1;
+    Epi::finish(any_bad, ep);
   }
 
   tc_fence_before();
@@ -250,6 +275,13 @@ exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);
   }
+}
+
+template <int TA>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                           const ExactEpiParams ep, int K, int m_tiles) {
+  limb_splitk<TA, ExactSplitEpi<TA>>(tmap_w, tmap_a, ep, K, m_tiles);
 }
 
 }  // namespace bx

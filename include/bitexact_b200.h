@@ -117,8 +117,10 @@ int bx_exact_linear_static(const int32_t* q, int64_t ldq, const int64_t* sh, con
  * tri_fuse._y, src/bitexact/vllm_plugin/tri_fuse.py:74-79): acc = c0 + (c1 << 8); t = rsh(acc * mul[n], fmsh);
  * y[m, n] = rsh(t * mant[m], 8 - e[m]) at 16 fractional bits; flag set when `checked` and some |t| >= 2^38.
  * tile_rows: 0 = automatic, else 16, 32, 64 or 128; -16 .. -128 select that tile size on the persistent kernel (one
- * CTA per SM, two accumulator buffers), the automatic choice when there are more tiles than SMs. No effect on
- * results. */
+ * CTA per SM, two accumulator buffers), the automatic choice when there are more tiles than SMs; for
+ * bx_int8_linear_post also 216, 232, 264 (10000 S + 2xx: clusters of exactly S = 2, 4 or 8): that many rows per tile
+ * with the K dimension split over a cluster of CTAs, the automatic choice when the tile list covers less than half
+ * of the SMs. No effect on results. */
 int bx_int8_mm(const int8_t* a, const int8_t* w, int32_t* c, int M, int N, int K, int tile_rows, void* stream);
 int bx_int8_linear_post(const int8_t* a, const int8_t* w, const int64_t* mul, int64_t fmsh, const int64_t* mant,
                         const int64_t* e, int64_t* y, int32_t* flag, int M, int N, int K, int checked, int tile_rows,

@@ -51,7 +51,8 @@ def test_seeded_int8_shapes(M, N, K):
     assert np.array_equal(c[:M] + (c[M:2 * M] << 8), acc)
     lib = nv.lib()
     wd, md, mantd, ed = T(w), T(m), T(mant), T(e)              # keep the device buffers alive across the calls
-    for tile in (0, 16, 32, 64, 128, -16, -32, -64, -128):               # negative: the persistent kernel
+    # negative: the persistent kernel; 200 + rows (10000 S + 200 + rows): K split over clusters of up to 8 (of S) CTAs
+    for tile in (0, 16, 32, 64, 128, -16, -32, -64, -128, 216, 232, 264, 20216, 20264, 40232, 80264):
         flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         y = torch.empty(M, N, dtype=torch.long, device="cuda")
         rc = lib.bx_int8_linear_post(a.data_ptr(), wd.data_ptr(), md.data_ptr(), fmsh, mantd.data_ptr(),
