@@ -32,7 +32,7 @@ template <int TA>
 struct ExactEpilogue {
   using Params = ExactEpiParams;
 
-  static constexpr int RMAX = 4;
+  static constexpr int RMAX = 2;
 
   // What a thread needs about its weight row n (TMEM lane): loaded BEFORE the accumulators are waited for, so the
   // loads (two dependent levels: the count, then the list) overlap the main loop instead of heading every tile's
@@ -94,12 +94,17 @@ struct ExactEpilogue {
   // chunks of 8, else 4 (TA = 48: three chunks of 4 for every warp instead of two chunks of 8 for half of them).
   static constexpr int CW = (TA % (8 * EPI_GROUPS) == 0) ? 8 : 4;
 
+  static constexpr int NCH = (TA + CW * EPI_GROUPS - 1) / (CW * EPI_GROUPS);      // chunks per warp
+
   // One thread per weight row n (TMEM lane) and column group; walks its share of the TA activation rows in chunks
-  // of CW accumulator columns.
+  // of CW accumulator columns. A thread whose weight row has a residual list does not finish its outputs here: each
+  // would wait for its own gather from q, one after the other, with the rest of the warp waiting beside it. It
+  // stores the joined sum T in place of y, and the warp then deals these (row, column) outputs out over its 32
+  // lanes (`deferred`): all their loads are in flight together, one round trip instead of one per column.
   static __device__ __forceinline__ void run(uint32_t tmem, int quarter, int group, int lane, int n0, int m0,
                                              bool has_k, const Params& p, const Row& r) {
     const int n = r.n;
-    const bool warp_res = r.wcnt > 0;
+    const bool listed = r.cnt > 0 && r.nok;
     const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
     bool any_bad = false;
 #pragma unroll 1
@@ -113,24 +118,67 @@ struct ExactEpilogue {
 #pragma unroll
       for (int i = 0; i < CW; ++i) {
         const int m = m0 + c0 + i;
-        const bool on = m < p.M && r.nok;
+        const bool in = m < p.M && r.nok;
         const i64 pv = __shfl_sync(0xffffffffu, sh_slot, (c0 & 31) + i) + r.gd;
         const i64 T = has_k ? join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]) : 0;
-        i64 B = 0;
-        if (warp_res && on) {
-#pragma unroll
-          for (int j = 0; j < RMAX; ++j)
-            if (j < r.wcnt && j < r.cnt) B += (i64)p.q[(i64)m * p.ldq + r.ecr[j]] * r.evr[j];
-          for (int j = RMAX; j < r.cnt; ++j)
-            B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
-        }
         bool bad;
-        const i64 yv = round_rule_warp(T, B, r.d, pv, on, bad);
+        const i64 yv = round_rule_warp(T, 0, r.d, pv, in && !listed, bad);
         any_bad |= bad;
-        if (on) p.y[(i64)m * p.N + n] = yv;
+        if (in) p.y[(i64)m * p.N + n] = listed ? T : yv;
       }
     }
+    if (r.wcnt > 0) deferred(group, lane, m0, p, r, any_bad);         // warp-uniform
     if (p.checked && any_bad) *p.flag = 1;
+  }
+
+  // The outputs of the warp's weight rows with a residual list: item (l, cc) = l-th such row, cc-th column of the
+  // warp, one item per lane and round. The owner's constants come by shuffle, T is read back from y.
+  static __device__ __forceinline__ void deferred(int group, int lane, int m0, const Params& p, const Row& r,
+                                                  bool& any_bad) {
+    constexpr unsigned FULL = 0xffffffffu;
+    const unsigned lmask = __ballot_sync(FULL, r.cnt > 0 && r.nok);
+    if (lmask == 0) return;
+    __threadfence_block();                            // the sums stored above are read by other lanes below
+    __syncwarp();
+    constexpr int NCOL = NCH * CW;
+    const int items = __popc(lmask) * NCOL;
+    for (int it0 = 0; it0 < items; it0 += 32) {
+      const int it = it0 + lane;
+      const bool has = it < items;
+      const int l = has ? it / NCOL : 0, cc = has ? it % NCOL : 0;
+      const int src = __fns(lmask, 0, l + 1);        // lane of the l-th listed row
+      const int c = ((cc / CW) * EPI_GROUPS + group) * CW + cc % CW;
+      const int m = m0 + c;
+      const bool on = has && c < TA && m < p.M;
+      const int n = __shfl_sync(FULL, r.n, src), d = __shfl_sync(FULL, r.d, src), cnt = __shfl_sync(FULL, r.cnt, src);
+      const i64 gd = __shfl_sync(FULL, r.gd, src);
+      i64 shm = 0;
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const i64 v = __shfl_sync(FULL, r.shv[s], c & 31);
+        if ((c >> 5) == s) shm = v;
+      }
+      int ec0[RMAX];
+      i64 ev0[RMAX];
+#pragma unroll
+      for (int j = 0; j < RMAX; ++j) {
+        ec0[j] = __shfl_sync(FULL, r.ecr[j], src);
+        ev0[j] = __shfl_sync(FULL, r.evr[j], src);
+      }
+      i64 T = 0, B = 0;
+      if (on) {
+        T = p.y[(i64)m * p.N + n];
+#pragma unroll
+        for (int j = 0; j < RMAX; ++j)
+          if (j < cnt) B += (i64)p.q[(i64)m * p.ldq + ec0[j]] * ev0[j];
+        for (int j = RMAX; j < cnt; ++j)
+          B += (i64)p.q[(i64)m * p.ldq + p.ec[(i64)n * p.R + j]] * p.ev[(i64)n * p.R + j];
+      }
+      bool bad;
+      const i64 yv = round_rule_warp(T, B, d, shm + gd, on, bad);
+      any_bad |= bad;
+      if (on) p.y[(i64)m * p.N + n] = yv;
+    }
   }
 };
 
