@@ -256,16 +256,14 @@ int launch_exact_rows(const CUtensorMap& ma, const CUtensorMap& mw, const ExactE
   return launched(1);
 }
 
-template <int TN, int NBUF, int SW = 0, int SA = 0>
+template <int TN, int NBUF>
 int launch_exact_rows_one(const CUtensorMap& mact, const CUtensorMap& mwt, const ExactEpiParams& ep, int K,
                           cudaStream_t st) {
   using Cfg = GemmCfg<3, 3, TN>;
-  constexpr int SMEM = SW > 0 ? SW * Cfg::W_BYTES + SA * Cfg::A_BYTES + 1024 + 256 : Cfg::SMEM_BYTES;
-  static_assert(SMEM <= 227 * 1024, "shared memory");
   static PerDevice configured;
   if (once_per_device(configured, [] {
-        return cudaFuncSetAttribute(exact_linear_rows_one_kernel<TN, NBUF, SW, SA>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        return cudaFuncSetAttribute(exact_linear_rows_one_kernel<TN, NBUF>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
       }) != BX_OK)
     return BX_ELAUNCH;
   const int sms = device_sms();
@@ -274,8 +272,8 @@ int launch_exact_rows_one(const CUtensorMap& mact, const CUtensorMap& mwt, const
   const int w_tiles = (ep.N + TN - 1) / TN;
   const long total = (long)row_blocks * w_tiles;
   const int grid = (int)(total < sms ? total : sms);
-  exact_linear_rows_one_kernel<TN, NBUF, SW, SA><<<grid, GEMM_THREADS, SMEM, st>>>(mact, mwt, ep, K, row_blocks,
-                                                                                  w_tiles);
+  exact_linear_rows_one_kernel<TN, NBUF><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mact, mwt, ep, K, row_blocks,
+                                                                                     w_tiles);
   return launched(1);
 }
 
@@ -572,14 +570,6 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
       case 64: return launch_exact_rows<64, false>(ma, mw, ep, K, st);
       default: return launch_exact_rows<80, false>(ma, mw, ep, K, st);
     }
-  }
-  if (ta == 665 || ta == 681) {          // 664 / 680 with split rings: 2 activation slots, 4 weight slots
-    CUtensorMap mact, mwt;
-    if (!make_map(&mact, scratch, (uint64_t)K, (uint64_t)M, 3, WROWS)) return BX_ELAUNCH;
-    if (!make_map(&mwt, limbs, (uint64_t)K, (uint64_t)N, 3, (uint32_t)(ta - 601))) return BX_ELAUNCH;
-    ExactEpiParams ep{q, ldq, sh, d, g, cnt, ec, ev, R, y, flag, M, N, checked};
-    if (ta == 665) return launch_exact_rows_one<64, 1, 2, 4>(mact, mwt, ep, K, st);
-    return launch_exact_rows_one<80, 1, 2, 4>(mact, mwt, ep, K, st);
   }
   if (ta == 616 || ta == 632 || ta == 648 || ta == 664 || ta == 680) {
     // 600 + weight rows per tile: activation rows on the MMA M side, one CTA (16 .. 48: two accumulator buffers)

@@ -197,14 +197,12 @@ struct RowsEpilogueOne {
   }
 };
 
-// SW, SA > 0: split rings (limb_gemm_persistent): SW slots of activation tiles (48 KB, from L2), SA slots of weight
-// tiles (from HBM).
-template <int TN, int NBUF, int SW = 0, int SA = 0>
+template <int TN, int NBUF>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 exact_linear_rows_one_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_wt,
                              const ExactEpiParams ep, int K, int row_blocks, int w_tiles) {
-  limb_gemm_persistent<3, 3, TN, RowsEpilogueOne<TN>, NBUF, true, SW, SA>(&tmap_act, &tmap_wt, row_blocks, w_tiles,
-                                                                          (K + BKB - 1) / BKB, ep);
+  limb_gemm_persistent<3, 3, TN, RowsEpilogueOne<TN>, NBUF, true>(&tmap_act, &tmap_wt, row_blocks, w_tiles,
+                                                                  (K + BKB - 1) / BKB, ep);
 }
 
 // tmap_a: activation limb planes [3, M, K], boxes of 128 rows x 3 planes; tmap_w: weight limbs [3, N, K], boxes of

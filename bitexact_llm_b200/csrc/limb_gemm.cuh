@@ -196,12 +196,7 @@ struct GemmSharedP {
 // NBUF accumulator buffers in TMEM (2: the epilogue of a tile runs behind the MMAs of the next one; 1: tiles too wide
 // for two buffers, the MMAs of the next tile wait until the epilogue has read the accumulators out, while the TMA
 // warp already fills the ring for it). W_FASTEST: consecutive tiles walk the 128-row operand first.
-// SW, SA > 0: two rings instead of one ring of whole stages, SW slots for the 128-row operand and SA slots for the
-// stacked operand (full[0 .. SW) / empty[0 .. SW) and full[4 .. 4 + SA) / empty[4 .. 4 + SA); SW, SA <= 4). A tile
-// shape whose whole stages fit only twice into shared memory can then keep the operand that comes from HBM four
-// K blocks ahead and the one that comes from L2 two. The producer issues the stacked operand of K block
-// j + SA - SW and then the 128-row operand of K block j: both slots are freed by the MMAs of K block j - SW.
-template <int NW, int NA, int TA, class Epi, int NBUF = 2, bool W_FASTEST = false, int SW = 0, int SA = 0>
+template <int NW, int NA, int TA, class Epi, int NBUF = 2, bool W_FASTEST = false>
 __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, const CUtensorMap* tmap_a, int n_tiles,
                                                      int m_tiles, int nkb, const typename Epi::Params& ep) {
   using Cfg = GemmCfg<NW, NA, TA>;
@@ -211,20 +206,16 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
   constexpr int TCOLS = UCOLS <= 64 ? 64 : UCOLS <= 128 ? 128 : UCOLS <= 256 ? 256 : 512;
   auto w_origin = [&](int tile) { return (W_FASTEST ? tile % n_tiles : tile / m_tiles) * WROWS; };
   auto a_origin = [&](int tile) { return (W_FASTEST ? tile / n_tiles : tile % m_tiles) * TA; };
-  constexpr bool SPLIT = SW > 0;
-  static_assert(!SPLIT || (SA >= SW && SW <= 4 && SA <= 4), "split rings: SW <= SA <= 4");
-  constexpr int RING_BYTES = SPLIT ? SW * Cfg::W_BYTES + SA * Cfg::A_BYTES : Cfg::STAGES * Cfg::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ring_a = ring + SW * Cfg::W_BYTES;                 // split rings: the stacked operand's slots
-  GemmSharedP* sh = reinterpret_cast<GemmSharedP*>(ring + RING_BYTES);
+  GemmSharedP* sh = reinterpret_cast<GemmSharedP*>(ring + Cfg::STAGES * Cfg::STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total = n_tiles * m_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 8; ++s) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->empty[s], 1);
     }
@@ -251,40 +242,8 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
   if (warp == 0) {
     if (lane == 0) {
       // ---- TMA producer: one continuous stream of stages over all tiles of this CTA ----
-      bool ok = true;
-      if constexpr (SPLIT) {
-        const int my_tiles = total > (int)blockIdx.x ? (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-        const int all = my_tiles * nkb;                      // K blocks of this CTA, numbered across its tiles
-        int ja = 0, jw = 0;                                  // next K block of the stacked / of the 128-row operand
-        auto load_a = [&](int j) {
-          const int tile = (int)blockIdx.x + (j / nkb) * (int)gridDim.x, s = j % SA;
-          mbar_arrive_expect_tx(&sh->full[4 + s], Cfg::A_BYTES);
-          tma_load_3d(ring_a + s * Cfg::A_BYTES, tmap_a, &sh->full[4 + s], (j % nkb) * BKB, a_origin(tile), 0);
-        };
-        auto load_w = [&](int j) {
-          const int tile = (int)blockIdx.x + (j / nkb) * (int)gridDim.x, s = j % SW;
-          mbar_arrive_expect_tx(&sh->full[s], Cfg::W_BYTES);
-          tma_load_3d(ring + s * Cfg::W_BYTES, tmap_w, &sh->full[s], (j % nkb) * BKB, w_origin(tile), 0);
-        };
-        for (; ja < SA - SW && ja < all; ++ja) load_a(ja);   // the stacked operand runs SA - SW K blocks ahead
-        for (; jw < all && ok; ++jw) {
-          if (ja < all) {
-            if (ja >= SA) ok = mbar_wait(&sh->empty[4 + ja % SA], (ja / SA - 1) & 1);
-            if (!ok) break;
-            load_a(ja++);
-          }
-          if (jw >= SW) ok = mbar_wait(&sh->empty[jw % SW], (jw / SW - 1) & 1);
-          if (!ok) break;
-          load_w(jw);
-        }
-        if (!ok) {
-          atomicAdd(&g_wait_timeouts, 1);
-          sh->abort_flag = 1;
-          for (int j = (ja > SA ? ja - SA : 0); j < ja; ++j) mbar_wait(&sh->full[4 + j % SA], (j / SA) & 1);
-          for (int j = (jw > SW ? jw - SW : 0); j < jw; ++j) mbar_wait(&sh->full[j % SW], (j / SW) & 1);
-        }
-      } else {
       int it = 0;            // global stage counter
+      bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const int n0 = w_origin(tile), m0 = a_origin(tile);
         for (int i = 0; i < nkb && ok; ++i, ++it) {
@@ -303,7 +262,6 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
         for (int i = (it > Cfg::STAGES ? it - Cfg::STAGES : 0); i < it; ++i)
           mbar_wait(&sh->full[i % Cfg::STAGES], (i / Cfg::STAGES) & 1);
       }
-      }
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -320,21 +278,12 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
         tc_fence_after();
         const uint32_t acc = tmem + buf * Cfg::COLS;
         for (int i = 0; i < nkb && ok; ++i, ++it) {
-          const int s = SPLIT ? it % (SPLIT ? SW : 1) : it % Cfg::STAGES;
-          const int sa = SPLIT ? it % (SPLIT ? SA : 1) : 0;
-          uint32_t wbase, abase;
-          if constexpr (SPLIT) {
-            ok = mbar_wait(&sh->full[s], (it / SW) & 1);
-            if (ok) ok = mbar_wait(&sh->full[4 + sa], (it / SA) & 1);
-            wbase = smem_u32(ring + s * Cfg::W_BYTES);
-            abase = smem_u32(ring_a + sa * Cfg::A_BYTES);
-          } else {
-            ok = mbar_wait(&sh->full[s], (it / Cfg::STAGES) & 1);
-            wbase = smem_u32(ring + s * Cfg::STAGE_BYTES);
-            abase = wbase + Cfg::W_BYTES;
-          }
+          const int s = it % Cfg::STAGES;
+          ok = mbar_wait(&sh->full[s], (it / Cfg::STAGES) & 1);
           if (!ok) break;
           tc_fence_after();
+          const uint32_t wbase = smem_u32(ring + s * Cfg::STAGE_BYTES);
+          const uint32_t abase = wbase + Cfg::W_BYTES;
 #pragma unroll
           for (int ks = 0; ks < BKB / UMMA_K; ++ks) {
             const uint32_t koff = ks * UMMA_K;
@@ -354,7 +303,6 @@ __device__ __forceinline__ void limb_gemm_persistent(const CUtensorMap* tmap_w, 
             }
           }
           umma_commit(&sh->empty[s]);
-          if constexpr (SPLIT) umma_commit(&sh->empty[4 + sa]);
         }
         if (ok) umma_commit(&sh->acc_full[buf]);
       }
