@@ -66,6 +66,8 @@ _SIGNATURES = {
     "bx_exact_silu_prod": (I, [P, P, P, P, P, I, I, P]),
     "bx_exact_quant_rows": (I, [P, P, I, P, L, P, P, L, I, I, P]),
     "bx_bmm": (I, [P, I, P, I, P, I, I, I, I, L, L, L, L, L, L, P]),
+    "bx_bmm_limb_scratch_bytes": (Z, [I, I, I, I]),
+    "bx_bmm_limb": (I, [P, I, P, I, P, I, I, I, I, L, L, L, L, L, L, P, I, P]),
     "bx_exact_epilogue": (I, [P, P, P, L, P, P, P, I, P, P, P, P, P, I, I, I, P]),
     "bx_sample_scratch_bytes": (Z, [I, I]),
     "bx_sample": (I, [P, L, P, P, P, P, I, I, I, P]),

@@ -24,6 +24,7 @@
 #include "unfused.cuh"
 #include "unfused_stages.cuh"
 #include "peak_probe.cuh"
+#include "bmm_limb.cuh"
 
 namespace {
 
@@ -339,6 +340,30 @@ int launch_int8_splitk(const CUtensorMap& mw, const CUtensorMap& ma, const Int8E
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, int8_linear_splitk_kernel<TA>, mw, ma, ep, K, m_tiles) != cudaSuccess) return BX_ELAUNCH;
   return launched(1);
+}
+
+template <int TA>
+int launch_bmm_limb(const CUtensorMap& mb, const CUtensorMap& ma, const BmmEpiParams& ep, int Z, int K16, cudaStream_t st) {
+  using Cfg = GemmCfg<3, 3, TA>;
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(bmm_limb_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int m_tiles = (ep.M + TA - 1) / TA, n_tiles = (ep.N + WROWS - 1) / WROWS;
+  const long grid = (long)Z * m_tiles * n_tiles;
+  if (grid > 0x7fffffffL) return BX_EARG;
+  bmm_limb_kernel<TA><<<(unsigned)grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(mb, ma, ep, K16, n_tiles, m_tiles);
+  return launched(1);
+}
+
+template <class TX>
+void launch_bmm_pack(const void* x, int64_t sz, int64_t sr, int64_t sk, int8_t* planes, int Z, int R, int K, int K16,
+                     cudaStream_t st) {
+  const int64_t total = (int64_t)Z * R * (K16 / 16);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  bmm_pack_kernel<TX><<<(unsigned)blocks, 256, 0, st>>>((const TX*)x, sz, sr, sk, planes, Z, R, K, K16);
 }
 
 template <bool POST>
@@ -1426,6 +1451,57 @@ int bx_bmm(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t
   else
     bmm_kernel<int32_t, int32_t><<<grid, 256, 0, st>>>((const int32_t*)a, (const int32_t*)b, (i64*)c, M, N, K, saz, sam, sak, sbz, sbk, sbn);
   return launched(1);
+}
+
+// ---- bmm on the tensor pipe (bmm_limb.cuh) ----
+size_t bx_bmm_limb_scratch_bytes(int Z, int M, int N, int K) {
+  if (Z <= 0 || M < 0 || N < 0 || K < 0) return 0;
+  const size_t K16 = ((size_t)K + 15) / 16 * 16;
+  return 3 * (size_t)Z * ((size_t)M + (size_t)N) * K16 + 16;
+}
+
+int bx_bmm_limb(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t* c, int Z, int M, int N, int K,
+                int64_t saz, int64_t sam, int64_t sak, int64_t sbz, int64_t sbk, int64_t sbn, int8_t* scratch,
+                int tile_rows, void* stream) {
+  if (g_status_seen.load(std::memory_order_relaxed)) return BX_EDEVICE;
+  if (Z < 0 || M < 0 || N < 0 || K < 0 || K >= 43690) return BX_EARG;
+  if (Z == 0 || M == 0 || N == 0) return BX_OK;
+  if (!c) return BX_EARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (K == 0)                                        // an empty sum (the operands may be null pointers)
+    return cudaMemsetAsync(c, 0, sizeof(int64_t) * (size_t)Z * M * N, st) == cudaSuccess ? BX_OK : BX_ELAUNCH;
+  if (!a || !b || !scratch || !aligned16(scratch)) return BX_EARG;
+  const int K16 = (K + 15) / 16 * 16;
+  int8_t* pa = scratch;
+  int8_t* pb = scratch + 3 * (size_t)Z * M * K16;
+  if (a_is_int64) launch_bmm_pack<i64>(a, saz, sam, sak, pa, Z, M, K, K16, st);
+  else launch_bmm_pack<int32_t>(a, saz, sam, sak, pa, Z, M, K, K16, st);
+  if (b_is_int64) launch_bmm_pack<i64>(b, sbz, sbn, sbk, pb, Z, N, K, K16, st);      // rows of b^T: columns of b
+  else launch_bmm_pack<int32_t>(b, sbz, sbn, sbk, pb, Z, N, K, K16, st);
+  int ta = tile_rows;
+  if (ta == 0) {
+    ta = M <= 16 ? 16 : M <= 32 ? 32 : M <= 48 ? 48 : M <= 64 ? 64 : 80;
+    if (M > 80) {
+      long best = -1;
+      const int cand[3] = {80, 64, 48};
+      for (int i = 0; i < 3; ++i) {
+        const long cost = (long)((M + cand[i] - 1) / cand[i]) * (cand[i] + 16);
+        if (best < 0 || cost < best) { best = cost; ta = cand[i]; }
+      }
+    }
+  }
+  CUtensorMap mb, ma;
+  if (!make_map(&mb, pb, (uint64_t)K16, (uint64_t)Z * N, 3, WROWS)) return BX_ELAUNCH;
+  if (!make_map(&ma, pa, (uint64_t)K16, (uint64_t)Z * M, 3, (uint32_t)ta)) return BX_ELAUNCH;
+  BmmEpiParams ep{c, M, N};
+  switch (ta) {
+    case 16: return launch_bmm_limb<16>(mb, ma, ep, Z, K16, st);
+    case 32: return launch_bmm_limb<32>(mb, ma, ep, Z, K16, st);
+    case 48: return launch_bmm_limb<48>(mb, ma, ep, Z, K16, st);
+    case 64: return launch_bmm_limb<64>(mb, ma, ep, Z, K16, st);
+    case 80: return launch_bmm_limb<80>(mb, ma, ep, Z, K16, st);
+    default: return BX_EARG;
+  }
 }
 
 int bx_exact_epilogue(const int64_t* T, const int64_t* B, const int32_t* q, int64_t ldq, const int32_t* cnt,

@@ -313,6 +313,15 @@ int bx_int8_post(const int32_t* c, const int64_t* mul, int64_t fmsh, const int64
  * residual: then y = T. */
 int bx_bmm(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t* c, int Z, int M, int N, int K,
            int64_t saz, int64_t sam, int64_t sak, int64_t sbz, int64_t sbk, int64_t sbn, void* stream);
+/* The same product on the tensor pipe, the way the reference's Triton kernel forms it (src/bitexact/bmm.py:27-75:
+ * up to 3 x 3 int8 limb products into five int32 accumulators, one int64 join at the end): a pass packs both
+ * operands into K-major limb planes (b transposed on the way) in `scratch` (bx_bmm_limb_scratch_bytes bytes, 16-byte
+ * aligned), then one CTA per (batch, 128 columns of b, tile_rows rows of a) runs the tcgen05 limb main loop.
+ * tile_rows: 0 = automatic, else 16, 32, 48, 64 or 80. Same contract and integers as bx_bmm (|x| < 2^23). */
+size_t bx_bmm_limb_scratch_bytes(int Z, int M, int N, int K);
+int bx_bmm_limb(const void* a, int a_is_int64, const void* b, int b_is_int64, int64_t* c, int Z, int M, int N, int K,
+                int64_t saz, int64_t sam, int64_t sak, int64_t sbz, int64_t sbk, int64_t sbn, int8_t* scratch,
+                int tile_rows, void* stream);
 int bx_exact_epilogue(const int64_t* T, const int64_t* B, const int32_t* q, int64_t ldq, const int32_t* cnt,
                       const int32_t* ec, const int64_t* ev, int R, const int64_t* d, const int64_t* g,
                       const int64_t* sh, int64_t* y, int32_t* flag, int M, int N, int checked, void* stream);

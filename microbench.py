@@ -277,8 +277,9 @@ def prefill(args):
 
 def bmm_bench(args):
     """`bmm` (the exact batched product of the reference's standalone engine) on the shapes of a --ctx-token prompt of
-    one sequence: q.K (Z = 8 KV heads, M = 4 T, K = 64, N = S) and p.V (K = S, N = 64). The kernel is a CUDA-core
-    int64 tile: a compatibility path, the serving path never calls it."""
+    one sequence: q.K (Z = 8 KV heads, M = 4 T, K = 64, N = S) and p.V (K = S, N = 64), on the tensor pipe (limb planes
+    packed per call + the tcgen05 limb main loop) and on the CUDA-core int64 tile kernel. The serving path never calls
+    it (its attention kernels form these products themselves)."""
     from bitexact_llm_b200.bmm import bmm
     dev = "cuda"
     S = args.ctx
@@ -288,19 +289,21 @@ def bmm_bench(args):
     p = torch.randint(0, 1 << 22, (8, 4 * S, S), dtype=torch.int32, device=dev, generator=g)
     v = torch.randint(-(1 << 22), 1 << 22, (8, S, 64), dtype=torch.int64, device=dev, generator=g)
     for name, a, b in (("q.K", q, k), ("p.V", p, v)):
+      for path in ("tensor", "cuda"):
         for _ in range(2):
-            bmm(a, b)
+            bmm(a, b, path=path)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
         for _ in range(args.iters):
-            bmm(a, b)
+            bmm(a, b, path=path)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / args.iters
         macs = 8.0 * a.shape[1] * a.shape[2] * b.shape[2]
-        print(json.dumps({"kernel": "bmm", "product": name, "S": S, "us": ms * 1e3, "int64_gmac_per_s": macs / ms / 1e6,
-                          "int8_equivalent_tops": 18.0 * macs / ms / 1e9}), flush=True)
+        print(json.dumps({"kernel": "bmm", "path": path, "product": name, "S": S, "us": ms * 1e3,
+                          "int64_gmac_per_s": macs / ms / 1e6, "int8_equivalent_tops": 18.0 * macs / ms / 1e9}),
+              flush=True)
 
 
 def prompt(args):

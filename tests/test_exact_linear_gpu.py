@@ -174,10 +174,22 @@ def test_unfused_linear_api_and_bmm():
     assert wmm.wmm_triton is wmm.wmm
     rng = np.random.RandomState(5)
     for Z, M, K, N, da, db in [(3, 5, 64, 70, np.int64, np.int64), (16, 16, 64, 300, np.int32, np.int64),
-                               (2, 130, 515, 64, np.int64, np.int32), (1, 1, 1, 1, np.int32, np.int32)]:
+                               (2, 130, 515, 64, np.int64, np.int32), (1, 1, 1, 1, np.int32, np.int32),
+                               (5, 97, 130, 129, np.int32, np.int32), (2, 260, 2048, 40, np.int64, np.int64)]:
         a = rng.randint(-(1 << 22), (1 << 22) + 1, (Z, M, K)).astype(da)
         b = rng.randint(-8355711, 8355712, (Z, N, K)).astype(db)               # stored transposed: strided view
+        a[0, 0, :] = 8355711                                                    # extremes of three limbs
+        b[0, 0, :] = -8355711
         bt = torch.from_numpy(b).cuda().transpose(1, 2)
-        c = bmm(torch.from_numpy(a).cuda(), bt)
         want = np.einsum("zmk,znk->zmn", a.astype(np.int64), b.astype(np.int64))
-        assert np.array_equal(c.cpu().numpy(), want), (Z, M, K, N)
+        ad = torch.from_numpy(a).cuda()
+        for path, tiles in (("cuda", (0,)), ("tensor", (0, 16, 32, 48, 64, 80))):
+            for tile in tiles:
+                c = bmm(ad, bt, path=path, tile_rows=tile)
+                assert np.array_equal(c.cpu().numpy(), want), (Z, M, K, N, path, tile)
+        # b stored [Z, K, N] contiguous (the p.V layout) and a strided view of a
+        bkn = torch.from_numpy(np.ascontiguousarray(b.transpose(0, 2, 1))).cuda()
+        a2 = torch.from_numpy(np.concatenate([a, a], 2)).cuda()[:, :, :K]
+        assert np.array_equal(bmm(a2, bkn).cpu().numpy(), want), (Z, M, K, N, "contiguous b")
+    assert bmm(torch.zeros(2, 3, 0, dtype=torch.long, device="cuda"), torch.zeros(2, 0, 4, dtype=torch.long, device="cuda")) \
+        .abs().sum().item() == 0
