@@ -173,6 +173,36 @@ int launch_exact_splitk(const CUtensorMap& mw, const CUtensorMap& ma, const Exac
   return launched(1);
 }
 
+// Split-K with the activation rows as the 128-row operand (exact_linear_rows_splitk_kernel).
+template <int TA>
+int launch_exact_rows_splitk(const CUtensorMap& mact, const CUtensorMap& mwt, const ExactEpiParams& ep, int K, int split,
+                             cudaStream_t st) {
+  using Cfg = GemmCfg<3, 3, TA>;
+  static PerDevice configured;
+  if (once_per_device(configured, [] {
+        return cudaFuncSetAttribute(exact_linear_rows_splitk_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_BYTES);
+      }) != BX_OK)
+    return BX_ELAUNCH;
+  const int w_tiles = (ep.N + TA - 1) / TA;
+  const int row_blocks = (ep.M + WROWS - 1) / WROWS;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(w_tiles * row_blocks * split), 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, exact_linear_rows_splitk_kernel<TA>, mact, mwt, ep, K, w_tiles) != cudaSuccess)
+    return BX_ELAUNCH;
+  return launched(1);
+}
+
 template <int TA>
 int launch_exact_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const ExactEpiParams& ep, int K,
                             cudaStream_t st) {
@@ -565,7 +595,30 @@ static int exact_linear_core(const int32_t* q, int64_t ldq, const int64_t* sh, c
   if (ta >= 10000) {
     want_split = ta / 10000;
     ta %= 10000;
-    if (ta < 200 || ta >= 300 || (want_split != 2 && want_split != 4 && want_split != 8)) return BX_EARG;
+    if (!((ta >= 200 && ta < 300) || ta == 764) || (want_split != 2 && want_split != 4 && want_split != 8)) return BX_EARG;
+  }
+  // Long K, few tiles, a batch that fills blocks of 128 rows (the down projection at 256 rows): K split over CTA
+  // pairs with the activation rows on the MMA M side, 64 weight rows per tile (764; 10000 S + 764: clusters of S).
+  if (tile_rows == 0 && !persistent && M >= WROWS && K >= 8192 &&
+      10 * (((M + WROWS - 1) / WROWS) * (long)WROWS) <= 11 * (((M + 47) / 48) * 48L) &&
+      ((M + WROWS - 1) / WROWS) * (long)((N + 63) / 64) * 2 <= 148) {
+    const long tiles = ((M + WROWS - 1) / WROWS) * (long)((N + 63) / 64);
+    ta = 764;
+    want_split = tiles * 4 <= 148 ? 4 : 2;           // as many K slices as keep the CTA count within the SMs
+  }
+  if (ta == 764) {
+    int split = want_split ? want_split : 2;
+    const int nkb = (K + BKB - 1) / BKB;
+    if (split > nkb / 2) split = nkb / 2;
+    while (split & (split - 1)) --split;
+    if (split >= 2) {
+      CUtensorMap mact, mwt;
+      if (!make_map(&mact, scratch, (uint64_t)K, (uint64_t)M, 3, WROWS)) return BX_ELAUNCH;
+      if (!make_map(&mwt, limbs, (uint64_t)K, (uint64_t)N, 3, 64)) return BX_ELAUNCH;
+      ExactEpiParams ep{q, ldq, sh, d, g, cnt, ec, ev, R, y, flag, M, N, checked};
+      return launch_exact_rows_splitk<64>(mact, mwt, ep, K, split, st);
+    }
+    ta = 664;                          // K too short to split: the same tile shape on the one-CTA kernel
   }
   // Split-K over a cluster of CTAs (200 + activation rows per tile asks for it; automatic for small batches whose
   // tile list covers less than half of the SMs): as many K slices as keep the CTA count within the 148 SMs.

@@ -72,6 +72,7 @@ struct ExactSplitEpi {
   static __device__ __forceinline__ i64 join(const uint32_t (&acc)[5][8], int i) {
     return join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]);
   }
+  static __device__ __forceinline__ int a_rows(const Params& ep) { return ep.M; }   // rows of the stacked operand
 
   // Output (m, c.n) of tile column col from the summed limb sums T. All 32 lanes of a warp call it together.
   // (Dealing the outputs of rows with a residual list out over the warp, as exact_linear_kernel does, was measured
@@ -237,7 +238,7 @@ __device__ __forceinline__ void limb_splitk(const CUtensorMap& tmap_w, const CUt
     // ---- join this CTA's limb sums and send column c to CTA c mod S, slot [this rank][c / S] ----
 #pragma unroll 1
     for (int c0 = group * 8; c0 < TA; c0 += 8 * EPI_GROUPS) {
-      if (m0 + c0 >= ep.M) break;
+      if (m0 + c0 >= Epi::a_rows(ep)) break;
       uint32_t acc[NBLK][8];
       if (acc_ok) {
 #pragma unroll
@@ -247,7 +248,7 @@ __device__ __forceinline__ void limb_splitk(const CUtensorMap& tmap_w, const CUt
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int c = c0 + i;
-        if (m0 + c >= ep.M) break;
+        if (m0 + c >= Epi::a_rows(ep)) break;
         const i64 T = acc_ok ? Epi::join(acc, i) : 0;
         i64* dst = cluster.map_shared_rank(partial, c % S);
         dst[((size_t)rank * own + c / S) * WROWS + row] = T;
@@ -262,7 +263,7 @@ __device__ __forceinline__ void limb_splitk(const CUtensorMap& tmap_w, const CUt
     for (int k = group; k < own; k += EPI_GROUPS) {
       const int c = rank + k * S;
       const int m = m0 + c;
-      if (c >= TA || m >= ep.M) break;                                // warp-uniform
+      if (c >= TA || m >= Epi::a_rows(ep)) break;                     // warp-uniform
       i64 T = 0;
       for (int r = 0; r < S; ++r) T += partial[((size_t)r * own + k) * WROWS + row];
       Epi::final(T, c, m, cst, ep, any_bad);
@@ -279,11 +280,86 @@ __device__ __forceinline__ void limb_splitk(const CUtensorMap& tmap_w, const CUt
   }
 }
 
+// The exact-mode policy with the ACTIVATION rows as the 128-row operand (TMEM lane = activation row) and TA weight
+// rows as the stacked operand: the residual lists then belong to accumulator columns, a warp takes the list branch
+// together, and only the few listed columns pay for a gather (down projection at 256 rows, weight-major: 40.7 us
+// with the lists against 32.8 us without). In limb_splitk's terms n0 is the first activation row of the tile and
+// the stacked-operand rows (m0 + column) are weight rows.
+template <int TA>
+struct ExactRowsSplitEpi {
+  using Params = ExactEpiParams;
+  static constexpr int NW = 3, NA = 3, NS = (TA + 31) / 32;
+  struct Consts {
+    int m;                                                            // this lane's activation row
+    bool mok;
+    i64 shm;
+    int d[NS], cnt[NS], ec0[NS];                                      // the tile's weight rows, lane-held
+    i64 gd[NS], ev0[NS];                                              // (ec0, ev0: first entry of the row's list)
+  };
+
+  static __device__ __forceinline__ Consts load(int a0, int w0, int quarter, int, int lane, int, int, const Params& ep) {
+    Consts c;
+    c.m = a0 + quarter * 32 + lane;
+    c.mok = c.m < ep.M;
+    c.shm = c.mok ? ep.sh[c.m] : 0;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int col = s * 32 + lane, n = w0 + col;
+      const bool nok = col < TA && n < ep.N;
+      c.d[s] = nok ? (int)__ldg(ep.d + n) : 0;
+      c.gd[s] = nok ? __ldg(ep.g + n) - (i64)c.d[s] + FR : 0;
+      c.cnt[s] = (nok && ep.cnt) ? __ldg(ep.cnt + n) : 0;
+      c.ec0[s] = c.cnt[s] > 0 ? __ldg(ep.ec + (i64)n * ep.R) : 0;
+      c.ev0[s] = c.cnt[s] > 0 ? __ldg(ep.ev + (i64)n * ep.R) : 0;
+    }
+    return c;
+  }
+
+  static __device__ __forceinline__ i64 join(const uint32_t (&acc)[5][8], int i) {
+    return join5(acc[0][i], acc[1][i], acc[2][i], acc[3][i], acc[4][i]);
+  }
+  static __device__ __forceinline__ int a_rows(const Params& ep) { return ep.N; }
+
+  // Output (c.m, n) from the summed limb sums T; n = weight row (warp-uniform), col = its column in the tile.
+  static __device__ __forceinline__ void final(i64 T, int col, int n, const Consts& c, const Params& ep, bool& any_bad) {
+    const int src = col & 31;
+    const int d = __shfl_sync(0xffffffffu, lane_slot<NS>(c.d, col), src);
+    const int cnt = __shfl_sync(0xffffffffu, lane_slot<NS>(c.cnt, col), src);
+    const i64 gd = __shfl_sync(0xffffffffu, lane_slot<NS>(c.gd, col), src);
+    i64 B = 0;
+    if (cnt > 0) {                                                    // warp-uniform
+      const int ec0 = __shfl_sync(0xffffffffu, lane_slot<NS>(c.ec0, col), src);
+      const i64 ev0 = __shfl_sync(0xffffffffu, lane_slot<NS>(c.ev0, col), src);
+      if (c.mok) {
+        B = (i64)ep.q[(i64)c.m * ep.ldq + ec0] * ev0;
+        for (int j = 1; j < cnt; ++j)
+          B += (i64)ep.q[(i64)c.m * ep.ldq + __ldg(ep.ec + (i64)n * ep.R + j)] * __ldg(ep.ev + (i64)n * ep.R + j);
+      }
+    }
+    bool bad;
+    const i64 yv = round_rule_warp(T, B, d, c.shm + gd, c.mok, bad);
+    any_bad |= bad;
+    if (c.mok) ep.y[(i64)c.m * ep.N + n] = yv;
+  }
+
+  static __device__ __forceinline__ void finish(bool any_bad, const Params& ep) {
+    if (ep.checked && any_bad) *ep.flag = 1;
+  }
+};
+
 template <int TA>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 exact_linear_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                            const ExactEpiParams ep, int K, int m_tiles) {
   limb_splitk<TA, ExactSplitEpi<TA>>(tmap_w, tmap_a, ep, K, m_tiles);
+}
+
+// tmap_act: activation limb planes (boxes of 128 rows), tmap_wt: weight limbs (boxes of TA rows); w_tiles = ceil(N / TA).
+template <int TA>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+exact_linear_rows_splitk_kernel(const __grid_constant__ CUtensorMap tmap_act, const __grid_constant__ CUtensorMap tmap_wt,
+                                const ExactEpiParams ep, int K, int w_tiles) {
+  limb_splitk<TA, ExactRowsSplitEpi<TA>>(tmap_act, tmap_wt, ep, K, w_tiles);
 }
 
 }  // namespace bx

@@ -41,6 +41,8 @@ struct Int8SplitEpi {
     return (i64)(int32_t)acc[0][i] + shl((i64)(int32_t)acc[1][i], 8);
   }
 
+  static __device__ __forceinline__ int a_rows(const Params& ep) { return ep.M; }
+
   static __device__ __forceinline__ void final(i64 T, int col, int m, const Consts& c, const Params& ep, bool& any_bad) {
     const i64 mant_m = __shfl_sync(0xffffffffu, lane_slot<NS>(c.mant, col), col & 31);
     const i64 e_m = __shfl_sync(0xffffffffu, lane_slot<NS>(c.e, col), col & 31);

@@ -67,7 +67,9 @@ int bx_i8_tensor_peak(int iters, int repeats, double* tops, void* stream);
  *              activation rows on CTA pairs (tcgen05 cta_group::2, 256 weight rows per pair); 516 .. 580 and
  *              616 .. 680 (steps of 16): the ACTIVATION rows on the MMA M side and that many weight rows per tile,
  *              on CTA pairs / on one CTA (the automatic choice for long tile lists of batches of 128 rows and
- *              more: 664). No effect on results.
+ *              more: 664); 764 (10000 S + 764): 64 weight rows per tile with the activation rows on the M side and
+ *              K split over clusters of S = 2 or 4 CTAs (the automatic choice for short tile lists with K >= 8192
+ *              at 128 rows and more). No effect on results.
  */
 size_t bx_exact_linear_scratch_bytes(int M, int K);
 int bx_exact_linear(const int32_t* q, int64_t ldq, const int64_t* sh, const int8_t* limbs, const int64_t* d,

@@ -35,7 +35,7 @@ def test_golden_linear_with_residual_and_extreme_shifts():
     # negative: the persistent kernel; 200 + rows: split-K over a cluster of CTAs; 400 + rows: CTA pairs (cta_group::2);
     # 500 / 600 + weight rows: activation rows on the MMA M side (CTA pairs / one CTA)
     for tile in (None, 16, 32, 48, 64, 80, -16, -32, -48, 216, 232, 264, 416, 432, 448, 516, 532, 548, 564, 580,
-                 616, 632, 648, 664, 680):
+                 616, 632, 648, 664, 680, 764, 20764, 40764, 20264):
         y, flag = _run(fl, z["lin_q"], z["lin_sh"], True, tile)
         assert np.array_equal(y, z["lin_y"]), tile
         assert flag == bool(z["lin_flag"])
@@ -64,8 +64,8 @@ def test_seeded_shapes_against_oracle(M, N, K):
     sh = rng.randint(-45, -8, M).astype(np.int64)
     want, wflag = ox.linear(q, sh, dec, checked=True)
     fl = _lin(dec)
-    for tile in (None, 16, 80, -48, 216, 232, 264, 416, 432, 448, 648, 680) if M > 16 else \
-            (None, 64, -16, 216, 264, 416, 448, 516, 548, 580, 616, 664):
+    for tile in (None, 16, 80, -48, 216, 232, 264, 416, 432, 448, 648, 680, 764, 40764) if M > 16 else \
+            (None, 64, -16, 216, 264, 416, 448, 516, 548, 580, 616, 664, 764):
         y, flag = _run(fl, q, sh, True, tile)
         assert np.array_equal(y, want), (tile, int((y != want).sum()))
         assert flag == wflag
@@ -116,7 +116,7 @@ def test_rounding_rule_boundaries_of_the_short_form():
         dec = {"limbs": limbs, "g": g, "d": d, "rr": rr, "rc": rng.randint(0, K, len(rr)).astype(np.int64), "rv": rv}
         want, wflag = ox.linear(q, sh, dec, checked=True)
         fl = _lin(dec)
-        for tile in (None, 16, 32, 48, 64, 80, -48, 216, 448, 548, 648, 664, 680):
+        for tile in (None, 16, 32, 48, 64, 80, -48, 216, 448, 548, 648, 664, 680, 764):
             y, flag = _run(fl, q, sh, True, tile)
             assert np.array_equal(y, want), (s0, tile, int((y != want).sum()))
             assert flag == wflag, (s0, tile)
