@@ -122,6 +122,29 @@ def test_rounding_rule_boundaries_of_the_short_form():
             assert flag == wflag, (s0, tile)
 
 
+def test_long_residual_lists_on_every_kernel_family():
+    """Weight rows with 1 .. 6 residual entries (the kernels keep the first one or two in registers and read the rest
+    from the ELL arrays), whole warps of listed rows and warps without any, on every kernel family."""
+    rng = np.random.RandomState(21)
+    M, N, K = 150, 640, 8192
+    W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
+    q = rng.randint(-(1 << 22), (1 << 22) + 1, (M, K)).astype(np.int64)
+    limbs = np.stack([l.astype(np.int8) for l in ox.split_limbs(W, 3)[0]])
+    rows = np.concatenate([np.repeat(np.arange(0, 64), 1 + np.arange(64) % 6),          # two full warps of listed rows
+                           np.repeat(np.arange(200, 640, 37), 5), [639] * 6])
+    rows.sort()
+    dec = {"limbs": limbs, "g": rng.randint(-34, -24, N).astype(np.int64), "d": rng.randint(0, 31, N).astype(np.int64),
+           "rr": rows.astype(np.int64), "rc": rng.randint(0, K, len(rows)).astype(np.int64),
+           "rv": rng.randint(-(1 << 20), 1 << 20, len(rows)).astype(np.int64)}
+    sh = rng.randint(-45, -8, M).astype(np.int64)
+    want, wflag = ox.linear(q, sh, dec, checked=True)
+    fl = _lin(dec)
+    for tile in (None, 32, 48, 80, -48, 232, 20264, 448, 548, 580, 648, 664, 680, 764, 40764):
+        y, flag = _run(fl, q, sh, True, tile)
+        assert np.array_equal(y, want), (tile, int((y != want).sum()))
+        assert flag == wflag
+
+
 def test_bf16_weights_config_one_shape():
     """q_proj shape of Llama-3.2-1B, M = 64, seed-0 N(0, 0.02^2) bf16 weights, uniform |q| <= 2^22."""
     from bitexact_llm_b200.exact.consts import decompose
