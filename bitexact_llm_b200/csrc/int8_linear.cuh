@@ -26,6 +26,24 @@ __device__ __forceinline__ i64 rsh_t(i64 x, i64 s) {
   return shl_t(shr_t(x + half, pos), neg);
 }
 
+// rsh_t for a shift known to lie in 1 .. 62: the same integers without the generality.
+__device__ __forceinline__ i64 rsh_pos(i64 x, int s) { return (x + (1ll << (s - 1))) >> s; }
+
+// segs.post on a joined accumulator: t = rsh(acc * m_c, fmsh), y = rsh(t * mant_r, 8 - e_r); bad when |t| >= 2^38.
+// Both shifts are almost always in 1 .. 62 (fmsh is a constant of the layer, 8 - e_r a property of the activation
+// row, the same for every lane of a warp): that case takes two plain rounding shifts, any other the general rule.
+__device__ __forceinline__ i64 int8_post(i64 acc, i64 mc, i64 fmsh, i64 mant, i64 e, bool& bad) {
+  const i64 s2 = 8 - e;
+  if (fmsh >= 1 && fmsh <= 62 && s2 >= 1 && s2 <= 62) {               // warp-uniform
+    const i64 t = rsh_pos((i64)((u64)acc * (u64)mc), (int)fmsh);
+    bad = iabs(t) >= (1ll << 38);
+    return rsh_pos((i64)((u64)t * (u64)mant), (int)s2);
+  }
+  const i64 t = rsh_t((i64)((u64)acc * (u64)mc), fmsh);
+  bad = iabs(t) >= (1ll << 38);
+  return rsh_t((i64)((u64)t * (u64)mant), s2);
+}
+
 struct Int8EpiParams {
   int32_t* c;            // raw: [R, N] int32, limb i of row m at row i * M + m
   const int64_t* mul;    // post: [N] per-channel multipliers
@@ -91,10 +109,9 @@ struct Int8Epilogue {
         if (m < p.M && nok) {
           const int32_t v0 = has_k ? (int32_t)a0[i] : 0, v1 = has_k ? (int32_t)a1[i] : 0;
           if (POST) {
-            const i64 acc = (i64)v0 + shl((i64)v1, 8);
-            const i64 t = rsh_t((i64)((u64)acc * (u64)mc), p.fmsh);
-            any_bad |= iabs(t) >= (1ll << 38);
-            p.y[(i64)m * p.N + n] = rsh_t((i64)((u64)t * (u64)mant_m), 8 - e_m);
+            bool bad;
+            p.y[(i64)m * p.N + n] = int8_post((i64)v0 + shl((i64)v1, 8), mc, p.fmsh, mant_m, e_m, bad);
+            any_bad |= bad;
           } else {
             p.c[(i64)m * p.N + n] = v0;
             p.c[((i64)p.M + m) * p.N + n] = v1;

@@ -47,9 +47,9 @@ struct Int8SplitEpi {
     const i64 mant_m = __shfl_sync(0xffffffffu, lane_slot<NS>(c.mant, col), col & 31);
     const i64 e_m = __shfl_sync(0xffffffffu, lane_slot<NS>(c.e, col), col & 31);
     if (c.nok) {
-      const i64 t = rsh_t((i64)((u64)T * (u64)c.mc), ep.fmsh);
-      any_bad |= iabs(t) >= (1ll << 38);
-      ep.y[(i64)m * ep.N + c.n] = rsh_t((i64)((u64)t * (u64)mant_m), 8 - e_m);
+      bool bad;
+      ep.y[(i64)m * ep.N + c.n] = int8_post(T, c.mc, ep.fmsh, mant_m, e_m, bad);
+      any_bad |= bad;
     }
   }
 

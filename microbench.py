@@ -156,6 +156,13 @@ def gemm8(args):
                 nv.check(lib.bx_int8_linear_post(a.data_ptr(), ws[i].data_ptr(), mul.data_ptr(), 30, mant.data_ptr(),
                                                  e.data_ptr(), y.data_ptr(), fl.data_ptr(), M, N, K, 0, args.tile,
                                                  nv.stream()), "bx_int8_linear_post")
+            if args.eager:                      # plain launches, one per weight set (for a profiler capture)
+                for i in range(nsets):
+                    run(i)
+                torch.cuda.synchronize()
+                print(json.dumps({"kernel": "int8_linear", "proj": name, "M": M, "eager_launches": nsets}), flush=True)
+                del ws
+                continue
             ms = _graph_time(run, nsets, args.iters)
             rec = {"kernel": "int8_linear", "proj": name, "M": M, "N": N, "K": K, "residual": "residual",
                    "us": ms * 1e3, "int8_tops": 4.0 * M * N * K / ms / 1e9}
@@ -429,8 +436,8 @@ def main():
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--no-scratch", action="store_true", help="attn: no scratch buffer (long contexts: cluster kernels)")
     ap.add_argument("--fixed", action="store_true", help="attn: every request has exactly --ctx keys")
-    ap.add_argument("--proj", default="", help="gemmr: only this projection (wqkv, wo, wgu, wd, lm)")
-    ap.add_argument("--eager", action="store_true", help="gemmr: one plain launch per weight set, no timing")
+    ap.add_argument("--proj", default="", help="gemmr / gemm8: only this projection (wqkv, wo, wgu, wd, lm)")
+    ap.add_argument("--eager", action="store_true", help="gemmr / gemm8: one plain launch per weight set, no timing")
     ap.add_argument("--chunk", type=int, default=4096, help="prompt: token rows per forward call")
     args = ap.parse_args()
     {"gemm": gemm, "gemmr": gemmr, "gemm8": gemm8, "attn": attn, "stages": stages, "prefill": prefill, "prompt": prompt, "bmm": bmm_bench}[args.what](args)

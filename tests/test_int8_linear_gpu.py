@@ -61,3 +61,31 @@ def test_seeded_int8_shapes(M, N, K):
         assert rc == 0 and np.array_equal(y.cpu().numpy(), want), (tile, int((y.cpu().numpy() != want).sum()))
         assert bool(flag.item()) == wflag
     assert nv.device_status() == 0
+
+
+def test_post_shift_regimes():
+    """The fused post epilogue takes two plain rounding shifts when both shifts lie in 1 .. 62 and the general rule
+    otherwise: row exponents and layer shifts on both sides of every boundary (shift 0, negative = left shift, 62, 63,
+    beyond 63), on the tile, persistent and split-K kernels."""
+    from bitexact_llm_b200 import _native as nv
+    rng = np.random.RandomState(8)
+    M, N, K = 96, 256, 512
+    w = rng.randint(-127, 128, (N, K)).astype(np.int8)
+    q = rng.randint(-32512, 32513, (M, K)).astype(np.int64)
+    m = rng.randint(1, 1 << 12, N).astype(np.int64)
+    mant = rng.randint(1 << 3, 1 << 6, M).astype(np.int64)
+    e = np.array([8, 7, 9, 20, -54, -55, -56, -70, -12, 0][:10] * 10)[:M].astype(np.int64)     # shifts 0, 1, -1, -12, 62, 63, 64, 78 ...
+    acc = o8.imm(q, w)
+    a = T(o8.stack_limbs(q, 2))
+    lib = nv.lib()
+    wd, md, mantd, ed = T(w), T(m), T(mant), T(e)
+    for fmsh in (20, 1, 0, -2, 62, 63):
+        want, wflag = o8.post(acc, m, fmsh, mant, e)
+        for tile in (0, 32, -32, 216, 20232):
+            flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+            y = torch.empty(M, N, dtype=torch.long, device="cuda")
+            rc = lib.bx_int8_linear_post(a.data_ptr(), wd.data_ptr(), md.data_ptr(), fmsh, mantd.data_ptr(),
+                                         ed.data_ptr(), y.data_ptr(), flag.data_ptr(), M, N, K, 1, tile, nv.stream())
+            torch.cuda.synchronize()
+            assert rc == 0 and np.array_equal(y.cpu().numpy(), want), (fmsh, tile, int((y.cpu().numpy() != want).sum()))
+            assert bool(flag.item()) == wflag, (fmsh, tile)
