@@ -57,7 +57,7 @@ class IntEngine:
         x, *pre = fz.embed_norm(self, ids, self.layers[0]["ga"])
         for i in range(self.L):
             ly = self.layers[i]
-            q = fz.qkv(self, self._lin(pre, ly["wqkv"]), None, None, None, pos, slot, kvs[i])
+            q = fz.qkv(self, self._lin(pre, ly["wqkv"]), None, None, None, pos, slot, kvs[i], int32=True)
             if tiles is not None:
                 num = torch.zeros(N, self.HKV, G, self.HD, dtype=torch.long, device=self.dev)
                 den = torch.ones(N, self.HKV, G, 1, dtype=torch.long, device=self.dev)    # padding rows: 0 / 1

@@ -377,7 +377,7 @@ class ColumnShardedIntEngine:
         x, *pre = fz.embed_norm(b, ids, b.layers[0]["ga"])
         for i in range(b.L):
             ly = b.layers[i]
-            q = fz.qkv(b, b._lin(pre, ly["wqkv"]), None, None, None, pos, slot, kvs[i])
+            q = fz.qkv(b, b._lin(pre, ly["wqkv"]), None, None, None, pos, slot, kvs[i], int32=True)
             num, den = tri_paged.attend(q, qpos, kvs[i], bt, b.ptab, rmap=rmap)
             x, a8, mant, e = fz.add_norm(b, b._lin(fz.attn_out(b, num, den), ly["wo"]), None, None, None, x, ly["gm"])
             A, Ma, Ea = gather_scaled_rows(a8.view(2, N, b.D), mant, e, self.group)

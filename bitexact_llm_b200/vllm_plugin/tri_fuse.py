@@ -56,16 +56,18 @@ def pre_norm(m, x, gamma):
     return _run(m, x, None, None, gamma, 2, True)[1:]
 
 
-def qkv(m, c, lin, mant, e, pos, slot, cache):
-    """qkv linear output -> q int64 [N, HKV, G, HD]; K / V of the tokens are stored at slot in cache."""
+def qkv(m, c, lin, mant, e, pos, slot, cache, int32=False):
+    """qkv linear output -> q int64 [N, HKV, G, HD]; K / V of the tokens are stored at slot in cache. int32=True: q as
+    int32 (the same values, |q| within three limbs), the type the attention kernels read: saves their conversion."""
     y = _y(m, c, lin, mant, e).contiguous()
     N = pos.shape[0]
     H, HKV, HD = m.H, m.HKV, m.HD
-    q = torch.empty(N, HKV, H // HKV, HD, dtype=torch.long, device=m.dev)
+    q = torch.empty(N, HKV, H // HKV, HD, dtype=torch.int32 if int32 else torch.long, device=m.dev)
     st, bs = (cache.stride()[:3], cache.shape[2]) if cache is not None else ((0, 0, 0), 1)
     rc = nv.lib().bx_int8_qkv(y.data_ptr(), m.cos.data_ptr(), m.sin.data_ptr(), pos.long().contiguous().data_ptr(),
                               nv.ptr(slot.long().contiguous() if slot is not None else None), nv.ptr(cache), *st, bs,
-                              q.data_ptr(), None, m.fl.data_ptr(), N, H, HKV, HD, nv.stream())
+                              None if int32 else q.data_ptr(), q.data_ptr() if int32 else None, m.fl.data_ptr(), N, H,
+                              HKV, HD, nv.stream())
     nv.check(rc, "bx_int8_qkv")
     return q
 
