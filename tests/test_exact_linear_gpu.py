@@ -145,6 +145,33 @@ def test_long_residual_lists_on_every_kernel_family():
         assert flag == wflag
 
 
+def test_random_shapes_on_random_kernels():
+    """Sixty seeded shapes (row counts around the 48 / 128 / 256 boundaries, ragged N and K, 0 .. N residual entries,
+    three ranges of row exponents), each on eight kernels drawn from all tile codes."""
+    rng = np.random.RandomState(4)
+    codes = [None, 16, 32, 48, 64, 80, -16, -32, -48, 216, 232, 264, 20264, 40232, 416, 448, 516, 548, 580, 616, 632,
+             648, 664, 680, 764, 20764, 40764]
+    for _ in range(60):
+        M = int(rng.choice([1, 3, 17, 48, 49, 64, 100, 127, 128, 129, 200, 255, 256, 257, 300, 385]))
+        N = int(rng.choice([8, 40, 63, 64, 65, 128, 130, 200, 512, 1000, 2050]))
+        K = int(rng.choice([16, 48, 128, 144, 256, 272, 1024, 2048, 4112]))
+        W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
+        q = rng.randint(-(1 << 22), (1 << 22) + 1, (M, K)).astype(np.int64)
+        nres = int(rng.choice([0, 1, max(1, N // 16), N]))
+        dec = {"limbs": np.stack([l.astype(np.int8) for l in ox.split_limbs(W, 3)[0]]),
+               "g": rng.randint(-34, -24, N).astype(np.int64), "d": rng.randint(0, 31, N).astype(np.int64),
+               "rr": np.sort(rng.randint(0, N, nres)).astype(np.int64), "rc": rng.randint(0, K, nres).astype(np.int64),
+               "rv": rng.randint(-(1 << 20), 1 << 20, nres).astype(np.int64)}
+        lo = int(rng.choice([-45, -25, -12]))
+        sh = rng.randint(lo, lo + 20, M).astype(np.int64)
+        want, wflag = ox.linear(q, sh, dec, checked=True)
+        fl = _lin(dec)
+        for ci in rng.choice(len(codes), 8, replace=False):
+            y, flag = _run(fl, q, sh, True, codes[ci])
+            assert np.array_equal(y, want), (M, N, K, codes[ci], nres, int((y != want).sum()))
+            assert flag == wflag, (M, N, K, codes[ci])
+
+
 def test_bf16_weights_config_one_shape():
     """q_proj shape of Llama-3.2-1B, M = 64, seed-0 N(0, 0.02^2) bf16 weights, uniform |q| <= 2^22."""
     from bitexact_llm_b200.exact.consts import decompose
