@@ -122,6 +122,28 @@ def test_rounding_rule_boundaries_of_the_short_form():
             assert flag == wflag, (s0, tile)
 
 
+def test_long_tile_lists_at_128_rows_and_more():
+    """Long tile lists of batches of 128 rows and more (several rounds of the persistent activation-major kernel, an
+    under-filled last round, a ragged last tile): the automatic choice, the activation-major kernel and the
+    weight-major persistent kernel give the oracle's integers."""
+    rng = np.random.RandomState(31)
+    for M, N, K in ((130, 10247, 1024), (256, 9480, 512), (128, 10240, 384)):
+        W = rng.randint(-8355711, 8355712, (N, K)).astype(np.int64)
+        q = rng.randint(-(1 << 22), (1 << 22) + 1, (M, K)).astype(np.int64)
+        nres = N // 16
+        dec = {"limbs": np.stack([l.astype(np.int8) for l in ox.split_limbs(W, 3)[0]]),
+               "g": rng.randint(-34, -24, N).astype(np.int64), "d": rng.randint(0, 31, N).astype(np.int64),
+               "rr": np.sort(rng.randint(0, N, nres)).astype(np.int64), "rc": rng.randint(0, K, nres).astype(np.int64),
+               "rv": rng.randint(-(1 << 20), 1 << 20, nres).astype(np.int64)}
+        sh = rng.randint(-30, -8, M).astype(np.int64)
+        want, wflag = ox.linear(q, sh, dec, checked=True)
+        fl = _lin(dec)
+        for tile in (None, 664, -48):
+            y, flag = _run(fl, q, sh, True, tile)
+            assert np.array_equal(y, want), (M, N, K, tile, int((y != want).sum()))
+            assert flag == wflag
+
+
 def test_long_residual_lists_on_every_kernel_family():
     """Weight rows with 1 .. 6 residual entries (the kernels keep the first one or two in registers and read the rest
     from the ELL arrays), whole warps of listed rows and warps without any, on every kernel family."""
